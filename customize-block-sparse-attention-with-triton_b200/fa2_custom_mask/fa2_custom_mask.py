@@ -1,0 +1,276 @@
+"""Host side of the block-sparse attention op: same Python surface as the reference's
+fa2_custom_mask/fa2_custom_mask.py, with every device step done by libbsattn (sm_100a CUDA).
+
+    flash_attention_custom_mask(q, k, v, mask, sm_scale)      # torch.autograd.Function.apply
+    build_groups_from_block_mask(mask) -> (groups, n_list) | (None, None)
+
+Differences from the reference that a caller can observe (all are supersets):
+  * `mask` may be the reference's block mask [B,H,N/64,N/64] (leading dims may be 1 or absent to
+    share one mask across batch/heads) or a dense boolean mask whose last two dims are [N,N]; a
+    dense mask is reduced to blocks on the GPU (a block is kept when any element is kept, and a
+    kept block is attended in full, as in the reference kernel);
+  * `mask=None` attends every block (the reference raises);
+  * rows of query blocks with no kept block get O = 0 (the reference leaves them unwritten);
+  * the backward is correct for any block mask and works for bf16 (the reference's is not);
+  * no host synchronisation happens anywhere in forward or backward.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+BLOCK = 64
+
+
+@dataclass
+class TileLists:
+    """Device-resident tile lists of one block mask of shape [Bm,Hm,nb,nb]."""
+    Bm: int
+    Hm: int
+    nb: int
+    qpair_ptr: Optional[torch.Tensor] = None
+    qpair_ent: Optional[torch.Tensor] = None
+    kpair_ptr: Optional[torch.Tensor] = None
+    kpair_ent: Optional[torch.Tensor] = None
+    row_ptr: Optional[torch.Tensor] = None
+    col_idx: Optional[torch.Tensor] = None
+    col_ptr: Optional[torch.Tensor] = None
+    row_idx: Optional[torch.Tensor] = None
+    groups: Optional[torch.Tensor] = None
+    meta: Optional[torch.Tensor] = None  # int32[8]: nnz, G, qpair entries, kpair entries
+
+    def list_strides(self, B: int, H: int):
+        """(list_b_stride, list_h_stride) so that head (b,h) uses list b*sb + h*sh."""
+        if self.Bm not in (1, B) or self.Hm not in (1, H):
+            raise ValueError(f"mask leading dims ({self.Bm},{self.Hm}) do not broadcast to ({B},{H})")
+        return (self.Hm if self.Bm > 1 else 0), (1 if self.Hm > 1 else 0)
+
+
+def _as_bytes(mask: torch.Tensor) -> torch.Tensor:
+    if mask.dtype == torch.bool:
+        return mask.view(torch.uint8)
+    if mask.dtype == torch.uint8:
+        return mask
+    raise AssertionError("mask must be a bool tensor")  # fa2_custom_mask.py:20 asserts bool
+
+
+def _as_4d(mask: torch.Tensor) -> torch.Tensor:
+    if mask.dim() > 4 or mask.dim() < 2:
+        raise ValueError("mask must have 2 to 4 dims")
+    while mask.dim() < 4:
+        mask = mask.unsqueeze(0)
+    return mask
+
+
+def reduce_dense_mask(dense: torch.Tensor, return_partial: bool = False):
+    """Dense boolean mask [..., N, N] -> block mask [..., N/64, N/64] (bool) on the GPU.
+
+    With return_partial=True also returns a one-element int32 device tensor counting the tiles
+    that are neither fully kept nor fully masked (reading it synchronises; the op never does)."""
+    lib = _lib.load()
+    d4 = _as_4d(_as_bytes(dense))
+    Bm, Hm, N, N2 = d4.shape
+    if N != N2 or N % BLOCK:
+        raise ValueError("dense mask must be [..., N, N] with N a multiple of 64")
+    if not d4.is_cuda:
+        raise ValueError("mask must be a CUDA tensor")
+    ok = (d4.stride(3) == 1 and d4.stride(2) % 16 == 0 and d4.data_ptr() % 16 == 0
+          and all(d4.stride(i) % 16 == 0 for i in (0, 1)))
+    if not ok:
+        d4 = d4.contiguous()
+    nb = N // BLOCK
+    block = torch.empty((Bm, Hm, nb, nb), dtype=torch.uint8, device=d4.device)
+    partial = torch.empty(1, dtype=torch.int32, device=d4.device) if return_partial else None
+    with torch.cuda.device(d4.device):
+        _lib.check("bsa_mask_reduce", lib.bsa_mask_reduce(
+            _lib.ptr(d4), _lib.strides4(d4), Bm, Hm, N, _lib.ptr(block), _lib.ptr(partial),
+            _lib.stream_ptr(d4.device)))
+    out = block.view(torch.bool).reshape(*dense.shape[:-2], nb, nb)
+    return (out, partial) if return_partial else out
+
+
+def build_tile_lists(block_mask: torch.Tensor, want_q: bool = True, want_k: bool = True,
+                     want_csr: bool = False, want_groups: bool = False) -> TileLists:
+    """Block mask [..,nb,nb] -> device tile lists (worst-case sized, no host synchronisation)."""
+    lib = _lib.load()
+    m4 = _as_4d(_as_bytes(block_mask))
+    if not m4.is_cuda:
+        raise ValueError("mask must be a CUDA tensor")
+    Bm, Hm, nb, nb2 = m4.shape
+    if nb != nb2:
+        raise ValueError("block mask must be square in its last two dims")
+    sizes = _lib.ListSizes()
+    _lib.check("bsa_tile_list_sizes", lib.bsa_tile_list_sizes(Bm, Hm, nb, ctypes.byref(sizes)))
+    dev = m4.device
+
+    def buf(n):
+        return torch.empty(int(n), dtype=torch.int32, device=dev)
+
+    tl = TileLists(Bm=Bm, Hm=Hm, nb=nb, meta=buf(sizes.meta))
+    want_csr = want_csr or want_groups
+    if want_q:
+        tl.qpair_ptr, tl.qpair_ent = buf(sizes.qpair_ptr), buf(sizes.qpair_ent)
+    if want_k:
+        tl.kpair_ptr, tl.kpair_ent = buf(sizes.kpair_ptr), buf(sizes.kpair_ent)
+    if want_csr:
+        tl.row_ptr, tl.col_idx = buf(sizes.row_ptr), buf(sizes.col_idx)
+        tl.col_ptr, tl.row_idx = buf(sizes.col_ptr), buf(sizes.row_idx)
+    if want_groups:
+        tl.groups = buf(sizes.groups)
+    with torch.cuda.device(dev):
+        _lib.check("bsa_tile_lists_build", lib.bsa_tile_lists_build(
+            _lib.ptr(m4), _lib.strides4(m4), Bm, Hm, nb,
+            _lib.ptr(tl.row_ptr), _lib.ptr(tl.col_idx), _lib.ptr(tl.col_ptr), _lib.ptr(tl.row_idx),
+            _lib.ptr(tl.qpair_ptr), _lib.ptr(tl.qpair_ent), _lib.ptr(tl.kpair_ptr),
+            _lib.ptr(tl.kpair_ent), _lib.ptr(tl.groups), _lib.ptr(tl.meta),
+            _lib.stream_ptr(dev)))
+    return tl
+
+
+def build_groups_from_block_mask(mask: torch.Tensor):
+    """Drop-in for the reference's build_groups_from_block_mask
+    (fa2_custom_mask/fa2_custom_mask.py:15-38): returns (groups int32 [G,5], n_list int32 [nnz])
+    on mask.device, or (None, None) when no block is kept.  Built on the GPU; the only host
+    synchronisation is the 8-byte read of (nnz, G) needed to size the returned tensors."""
+    assert mask.dtype == torch.bool
+    assert mask.dim() == 4
+    tl = build_tile_lists(mask, want_q=False, want_k=False, want_groups=True)
+    nnz, G = (int(x) for x in tl.meta[:2].tolist())
+    if G == 0:
+        return None, None
+    groups = tl.groups[: 5 * G].reshape(G, 5).clone()
+    n_list = tl.col_idx[:nnz].clone()
+    return groups.contiguous(), n_list.contiguous()
+
+
+def _tma_ready(t: torch.Tensor) -> torch.Tensor:
+    """TMA needs a unit inner stride, 16-byte aligned base and outer strides."""
+    ok = (t.stride(3) == 1 and t.data_ptr() % 16 == 0
+          and all(s > 0 and s % 8 == 0 for s in t.stride()[:3]))
+    return t if ok else t.contiguous()
+
+
+def _lists_for_mask(mask, B, H, N, device, need_k):
+    nb = N // BLOCK
+    if mask is None:
+        mask = torch.ones((1, 1, nb, nb), dtype=torch.bool, device=device)
+    if mask.device != device:
+        raise ValueError("mask must live on the same device as q")
+    if mask.shape[-1] == nb and mask.shape[-2] == nb:
+        block = mask
+    elif mask.shape[-1] == N and mask.shape[-2] == N:
+        block = reduce_dense_mask(mask)
+    else:
+        raise ValueError(
+            f"mask must be a block mask [..,{nb},{nb}] or a dense mask [..,{N},{N}], got {tuple(mask.shape)}")
+    return build_tile_lists(block, want_q=True, want_k=need_k)
+
+
+def new_status_word(device) -> torch.Tensor:
+    """A zeroed int32 device word for the kernels' bounded-wait reports (see check_status)."""
+    return torch.zeros(1, dtype=torch.int32, device=device)
+
+
+def check_status(status: torch.Tensor):
+    """Synchronises the current stream and raises if a kernel's bounded wait gave up."""
+    lib = _lib.load()
+    with torch.cuda.device(status.device):
+        _lib.check("bsa_check_status", lib.bsa_check_status(
+            _lib.ptr(status), _lib.stream_ptr(status.device)))
+
+
+def attention_forward(q, k, v, lists: TileLists, sm_scale: float, want_rowmax: bool = False,
+                      status: Optional[torch.Tensor] = None):
+    """Runs the forward kernel on prepared tile lists.  Returns (o, lse2, rowmax|None):
+    lse2 is the base-2 log-sum-exp of the logits scaled by sm_scale*log2(e)."""
+    lib = _lib.load()
+    B, H, N, D = q.shape
+    q, k, v = _tma_ready(q), _tma_ready(k), _tma_ready(v)
+    o = torch.empty((B, H, N, D), dtype=q.dtype, device=q.device)
+    lse2 = torch.empty((B, H, N), dtype=torch.float32, device=q.device)
+    rowmax = torch.empty_like(lse2) if want_rowmax else None
+    sb, sh = lists.list_strides(B, H)
+    with torch.cuda.device(q.device):
+        _lib.check("bsa_attn_fwd", lib.bsa_attn_fwd(
+            _lib.ptr(q), _lib.strides4(q), _lib.ptr(k), _lib.strides4(k), _lib.ptr(v),
+            _lib.strides4(v), _lib.ptr(o), _lib.strides4(o), _lib.ptr(lse2), _lib.ptr(rowmax),
+            _lib.ptr(lists.qpair_ptr), _lib.ptr(lists.qpair_ent), sb, sh, float(sm_scale),
+            _lib.dtype_code(q.dtype), B, H, N, D, _lib.ptr(status), _lib.stream_ptr(q.device)))
+    return o, lse2, rowmax
+
+
+def attention_backward(q, k, v, o, lse2, dout, lists: TileLists, sm_scale: float,
+                       status: Optional[torch.Tensor] = None):
+    """delta, then dK/dV over the key-pair lists and dQ over the query-pair lists."""
+    lib = _lib.load()
+    B, H, N, D = q.shape
+    # the three kernels take one stride set for q, k, v, o, dO and the gradients
+    same = q.stride() == k.stride() == v.stride() == o.stride() == dout.stride()
+    if not same or _tma_ready(q) is not q:
+        q, k, v, o, dout = (t.contiguous() for t in (q, k, v, o, dout))
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
+    delta = torch.empty((B, H, N), dtype=torch.float32, device=q.device)
+    sb, sh = lists.list_strides(B, H)
+    code = _lib.dtype_code(q.dtype)
+    st = _lib.strides4(q)
+    with torch.cuda.device(q.device):
+        stream = _lib.stream_ptr(q.device)
+        _lib.check("bsa_attn_bwd_delta", lib.bsa_attn_bwd_delta(
+            _lib.ptr(o), _lib.ptr(dout), st, _lib.ptr(delta), code, B, H, N, D, stream))
+        _lib.check("bsa_attn_bwd_dkdv", lib.bsa_attn_bwd_dkdv(
+            _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(dout), st, _lib.ptr(lse2),
+            _lib.ptr(delta), _lib.ptr(dk), _lib.ptr(dv), _lib.ptr(lists.kpair_ptr),
+            _lib.ptr(lists.kpair_ent), sb, sh, float(sm_scale), code, B, H, N, D,
+            _lib.ptr(status), stream))
+        _lib.check("bsa_attn_bwd_dq", lib.bsa_attn_bwd_dq(
+            _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(dout), st, _lib.ptr(lse2),
+            _lib.ptr(delta), _lib.ptr(dq), _lib.ptr(lists.qpair_ptr), _lib.ptr(lists.qpair_ent),
+            sb, sh, float(sm_scale), code, B, H, N, D, _lib.ptr(status), stream))
+    return dq, dk, dv
+
+
+class _attention(torch.autograd.Function):
+    """Same signature as the reference's _attention (fa2_custom_mask/fa2_custom_mask.py:40-155)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, mask=None, sm_scale=1.3):
+        if q.dim() != 4 or k.shape != q.shape or v.shape != q.shape:
+            raise AssertionError("q, k, v must share the shape [B, H, N, D]")
+        B, H, N, D = q.shape
+        assert q.shape[-1] == k.shape[-1] == v.shape[-1]
+        assert D in {16, 32, 64, 128, 256}  # the reference's own check (fa2_custom_mask.py:58)
+        if D != 64:
+            raise NotImplementedError("this build supports head dimension 64 only")
+        if N % BLOCK:
+            raise AssertionError("sequence length must be a multiple of 64")
+        if not q.is_cuda:
+            raise RuntimeError("flash_attention_custom_mask needs CUDA tensors; there is no CPU path")
+        if not (q.dtype == k.dtype == v.dtype) or q.dtype not in (torch.float16, torch.bfloat16):
+            raise TypeError("q, k, v must all be float16 or all bfloat16")
+        need_grad = any(ctx.needs_input_grad[:3])
+        lists = _lists_for_mask(mask, B, H, N, q.device, need_k=need_grad)
+        o, lse2, _ = attention_forward(q, k, v, lists, sm_scale)
+        ctx.save_for_backward(q, k, v, o, lse2, lists.qpair_ptr, lists.qpair_ent,
+                              lists.kpair_ptr, lists.kpair_ent)
+        ctx.lists_shape = (lists.Bm, lists.Hm, lists.nb)
+        ctx.sm_scale = sm_scale
+        ctx.HEAD_DIM = D
+        ctx.USE_MASK = mask is not None
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, lse2, qp, qe, kp, ke = ctx.saved_tensors
+        Bm, Hm, nb = ctx.lists_shape
+        lists = TileLists(Bm=Bm, Hm=Hm, nb=nb, qpair_ptr=qp, qpair_ent=qe, kpair_ptr=kp,
+                          kpair_ent=ke)
+        dq, dk, dv = attention_backward(q, k, v, o, lse2, do, lists, ctx.sm_scale)
+        return dq, dk, dv, None, None
+
+
+flash_attention_custom_mask = _attention.apply

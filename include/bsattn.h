@@ -1,0 +1,185 @@
+/*
+ * bsattn.h — C ABI of libbsattn: 64x64 block-sparse FlashAttention-2 for NVIDIA B200 (sm_100a).
+ *
+ * Every entry point
+ *   - takes plain device pointers, sizes and element strides (no torch types),
+ *   - borrows all buffers (the caller owns inputs, outputs and workspaces),
+ *   - enqueues its work on `stream` (a cudaStream_t passed as void*) of the CURRENT device and
+ *     returns without synchronising,
+ *   - returns BSA_OK (0) or a negative bsa_status; it never throws, exits or prints.
+ *
+ * The library replaces the device side of the reference's Python package `fa2_custom_mask`;
+ * each declaration cites the reference interface (path:line inside the reference project)
+ * whose work it takes over.
+ *
+ * Vocabulary: a "block" is 64 consecutive tokens; nb = N/64 blocks per sequence; a "tile" is one
+ * (query block m, key block n) pair that the block mask keeps.  Kernels work on PAIRS of adjacent
+ * blocks (128 rows of a tcgen05 accumulator): a "pair list" for pair p holds, ascending, every
+ * block index j of the other axis that is kept for block 2p or 2p+1, encoded as
+ *     entry = (j << 2) | flags,   flags bit0: block 2p keeps j,  bit1: block 2p+1 keeps j.
+ */
+#ifndef BSATTN_H_
+#define BSATTN_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BSA_VERSION 100
+
+typedef enum bsa_status {
+  BSA_OK = 0,
+  BSA_ERR_BAD_SHAPE = -1,      /* N not a multiple of 64, D != 64, non-positive sizes            */
+  BSA_ERR_BAD_DTYPE = -2,      /* dtype is neither BSA_F16 nor BSA_BF16                           */
+  BSA_ERR_BAD_STRIDE = -3,     /* innermost stride != 1, or an outer stride not 16-byte aligned   */
+  BSA_ERR_BAD_POINTER = -4,    /* null or misaligned pointer                                      */
+  BSA_ERR_CUDA = -5,           /* a CUDA runtime/driver call failed (launch, attribute, tensor map) */
+  BSA_ERR_NO_DRIVER = -6,      /* cuTensorMapEncodeTiled could not be resolved                    */
+  BSA_ERR_UNSUPPORTED_ARCH = -7, /* current device is not compute capability 10.x                 */
+  BSA_ERR_TOO_LARGE = -8,      /* problem exceeds a documented fixed capacity                     */
+  BSA_ERR_DEVICE_TIMEOUT = -9  /* reported by bsa_check_status: a bounded device wait gave up     */
+} bsa_status;
+
+typedef enum bsa_dtype { BSA_F16 = 0, BSA_BF16 = 1 } bsa_dtype;
+
+/* Library version (BSA_VERSION of the build). No reference counterpart. */
+int bsa_version(void);
+
+/* Static, human-readable text for a bsa_status. No reference counterpart
+ * (the reference raises Python AssertionErrors: fa2_custom_mask/fa2_custom_mask.py:57-58,99-100,113). */
+const char* bsa_strerror(int status);
+
+/*
+ * Dense boolean mask -> block mask.  block[b,h,i,j] = any(dense[b,h,64i:64i+64, 64j:64j+64]).
+ * Inverse of the expansion the reference uses for its naive check (kernel-test.py:18); the
+ * reference's op itself only accepts the block mask (fa2_custom_mask/fa2_custom_mask.py:17-21).
+ *   dense    : bytes (0 = masked, non-zero = kept), logical shape [B,H,N,N], element strides
+ *              dense_strides[4] (0 allowed for broadcast over b/h); last stride must be 1, the
+ *              row stride and base address multiples of 16.
+ *   block    : out, contiguous [B,H,nb,nb] bytes (0/1).
+ *   partial_tiles : optional out (may be NULL), one int32 that the call first zeroes and then
+ *              increments once per tile that is neither all-kept nor all-masked.
+ */
+int bsa_mask_reduce(const uint8_t* dense, const int64_t dense_strides[4], int B, int H, int N,
+                    uint8_t* block, int32_t* partial_tiles, void* stream);
+
+/* Number of int32 elements the caller must provide for each output of bsa_tile_lists_build. */
+typedef struct bsa_list_sizes {
+  int64_t row_ptr;    /* B*H*nb + 1                        */
+  int64_t col_idx;    /* worst case B*H*nb*nb              */
+  int64_t col_ptr;    /* B*H*nb + 1                        */
+  int64_t row_idx;    /* worst case B*H*nb*nb              */
+  int64_t qpair_ptr;  /* B*H*ceil(nb/2) + 1                */
+  int64_t qpair_ent;  /* worst case B*H*ceil(nb/2)*nb      */
+  int64_t kpair_ptr;  /* B*H*ceil(nb/2) + 1                */
+  int64_t kpair_ent;  /* worst case B*H*ceil(nb/2)*nb      */
+  int64_t groups;     /* worst case 5*B*H*nb               */
+  int64_t meta;       /* 8                                 */
+} bsa_list_sizes;
+int bsa_tile_list_sizes(int B, int H, int nb, bsa_list_sizes* out);
+
+/*
+ * Block mask -> tile lists, all built on the device with no host synchronisation.
+ * Replaces build_groups_from_block_mask (fa2_custom_mask/fa2_custom_mask.py:15-38), whose
+ * outputs are reproduced bit-exactly:  n_list == col_idx[0:nnz]  and  groups == groups[0:G].
+ *   block      : bytes, logical [B,H,nb,nb], element strides block_strides[4] (0 = broadcast).
+ *   row_ptr/col_idx : CSR over rows r=(b*H+h)*nb+m, empty rows kept, columns ascending.
+ *   col_ptr/row_idx : CSR of the transposed mask (per key block, query blocks ascending).
+ *   qpair_ptr/qpair_ent : pair lists over query-block pairs (forward and dQ kernels).
+ *   kpair_ptr/kpair_ent : pair lists over key-block pairs (dK/dV kernel).
+ *   groups     : rows (b,h,m,start,len) of the non-empty rows only, in row order.
+ *   meta       : int32[8] = {nnz, G, qpair entries, kpair entries, 0,0,0,0}.
+ * Any (ptr,idx) pair, and groups, may be NULL to skip that product; meta is required.
+ */
+int bsa_tile_lists_build(const uint8_t* block, const int64_t block_strides[4], int B, int H, int nb,
+                         int32_t* row_ptr, int32_t* col_idx, int32_t* col_ptr, int32_t* row_idx,
+                         int32_t* qpair_ptr, int32_t* qpair_ent, int32_t* kpair_ptr,
+                         int32_t* kpair_ent, int32_t* groups, int32_t* meta, void* stream);
+
+/*
+ * Forward attention over the listed tiles; replaces the _attn_fwd launch
+ * (fa2_custom_mask/fa2_custom_mask.py:77-87, kernel fa2_custom_mask/fa2_fwd.py:108-206).
+ *   q,k,v,o : [B,H,N,64] fp16/bf16, element strides *_strides[4]; last stride 1, others multiples
+ *             of 8 elements, base 16-byte aligned.
+ *   lse2    : out fp32 [B,H,N] contiguous: log2-sum-exp2 of the scaled logits
+ *             (natural-log LSE = lse2 * ln 2); -inf for rows of query blocks with no listed tile.
+ *   rowmax  : optional out fp32 [B,H,N] (may be NULL): running row maximum of the scaled logits in
+ *             the exp2 domain, the quantity the reference stores in its `M` buffer
+ *             (fa2_custom_mask/fa2_fwd.py:193-196).
+ *   qpair_ptr/qpair_ent : pair lists from bsa_tile_lists_build built for a mask of shape
+ *             [Bm,Hm,nb,nb]; list_b_stride/list_h_stride give the list index of head (b,h) as
+ *             b*list_b_stride + h*list_h_stride (0 for a broadcast axis).
+ *   Rows of query blocks without any listed tile get o = 0 (the reference leaves them unwritten).
+ *   status  : optional int32 device word (may be NULL); a non-zero value after the stream drains
+ *             means a bounded wait inside the kernel gave up (see bsa_check_status).
+ */
+int bsa_attn_fwd(const void* q, const int64_t q_strides[4], const void* k,
+                 const int64_t k_strides[4], const void* v, const int64_t v_strides[4], void* o,
+                 const int64_t o_strides[4], float* lse2, float* rowmax, const int32_t* qpair_ptr,
+                 const int32_t* qpair_ent, int list_b_stride, int list_h_stride, float sm_scale,
+                 int dtype, int B, int H, int N, int D, int32_t* status, void* stream);
+
+/*
+ * delta[b,h,i] = sum_d o[b,h,i,d] * do[b,h,i,d] in fp32; replaces _attn_bwd_preprocess
+ * (fa2_custom_mask/fa2_bwd.py:5-19, launch fa2_custom_mask/fa2_custom_mask.py:114-121).
+ * o and do share o_strides; delta is contiguous [B,H,N].
+ */
+int bsa_attn_bwd_delta(const void* o, const void* dout, const int64_t o_strides[4], float* delta,
+                       int dtype, int B, int H, int N, int D, void* stream);
+
+/*
+ * dK and dV over the key-pair lists; replaces _attn_bwd_dkdv
+ * (fa2_custom_mask/fa2_bwd.py:23-81, driven from fa2_custom_mask/fa2_bwd.py:199-234).
+ * All of q,k,v,dout,dk,dv share `strides`.  lse2 and delta are the outputs of bsa_attn_fwd and
+ * bsa_attn_bwd_delta.  Key blocks that no query block lists get dk = dv = 0.
+ */
+int bsa_attn_bwd_dkdv(const void* q, const void* k, const void* v, const void* dout,
+                      const int64_t strides[4], const float* lse2, const float* delta, void* dk,
+                      void* dv, const int32_t* kpair_ptr, const int32_t* kpair_ent,
+                      int list_b_stride, int list_h_stride, float sm_scale, int dtype, int B, int H,
+                      int N, int D, int32_t* status, void* stream);
+
+/*
+ * dQ over the query-pair lists; replaces _attn_bwd_dq
+ * (fa2_custom_mask/fa2_bwd.py:85-137, driven from fa2_custom_mask/fa2_bwd.py:237-285).
+ */
+int bsa_attn_bwd_dq(const void* q, const void* k, const void* v, const void* dout,
+                    const int64_t strides[4], const float* lse2, const float* delta, void* dq,
+                    const int32_t* qpair_ptr, const int32_t* qpair_ent, int list_b_stride,
+                    int list_h_stride, float sm_scale, int dtype, int B, int H, int N, int D,
+                    int32_t* status, void* stream);
+
+/*
+ * Head-wise token reorder; replaces reorder_kernel (fa2_custom_mask/permute.py:5-58, launched from
+ * fa2_custom_mask/functional.py:5-20).  For every head h with order (p0,p1,p2) = orders[3h..3h+2],
+ * a token at grid coordinate (f,y,x) of the F x Hh x W grid moves to the position it has when the
+ * grid axes are laid out in the order (p0,p1,p2).
+ *   in/out : [B,heads,T=F*Hh*W,D] with element strides `strides` (shared by in and out, as in the
+ *            reference); elem_bytes is 1, 2, 4 or 8.
+ *   orders : device int32 [heads,3].
+ */
+int bsa_reorder(const void* in, void* out, const int64_t strides[4], const int32_t* orders, int B,
+                int heads, int T, int D, int F, int Hh, int W, int elem_bytes, void* stream);
+
+/*
+ * Inverse of bsa_reorder; replaces inv_reorder_kernel (fa2_custom_mask/permute.py:60-126, launched
+ * from fa2_custom_mask/functional.py:46-62).  `orders` is the forward order that produced `in`,
+ * `inv_orders` its inverse-order table row per head, exactly as the reference passes them.
+ */
+int bsa_inv_reorder(const void* in, void* out, const int64_t strides[4], const int32_t* orders,
+                    const int32_t* inv_orders, int B, int heads, int T, int D, int F, int Hh, int W,
+                    int elem_bytes, void* stream);
+
+/*
+ * Synchronises `stream`, reads the device status word and returns BSA_OK, BSA_ERR_DEVICE_TIMEOUT
+ * or BSA_ERR_CUDA.  No reference counterpart.
+ */
+int bsa_check_status(const int32_t* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BSATTN_H_ */

@@ -1,0 +1,149 @@
+"""Forward kernel (through the C ABI) against the fp32 oracle and the reference's golden vectors.
+Tolerance (stated by the task): max-abs 2e-2 on O for fp16/bf16 inputs."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import golden_cases
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+O_TOL = 2e-2
+LSE_TOL = 2e-3
+DT = {0: torch.float32, 1: torch.float16, 2: torch.bfloat16}
+
+
+def _run(q, k, v, mask, sm_scale, want_rowmax=True):
+    from fa2_custom_mask import attention_forward, build_tile_lists
+    lists = build_tile_lists(mask.cuda(), want_q=True, want_k=False)
+    o, lse2, rowmax = attention_forward(q.cuda(), k.cuda(), v.cuda(), lists, sm_scale, want_rowmax)
+    torch.cuda.synchronize()
+    return o.float().cpu(), lse2.cpu(), (rowmax.cpu() if rowmax is not None else None)
+
+
+def _compare(q, k, v, mask, sm_scale, o, lse2):
+    o_ref, lse_ref = oracle.attn_forward(q, k, v, mask, sm_scale)
+    err = (o - o_ref).abs().max().item()
+    assert err <= O_TOL, f"O max-abs err {err}"
+    live = torch.isfinite(lse_ref)
+    assert torch.equal(torch.isfinite(lse2), live)
+    assert (lse2[~live] == -math.inf).all()
+    lerr = (lse2[live] * math.log(2.0) - lse_ref[live]).abs().max().item()
+    assert lerr <= LSE_TOL, f"LSE max-abs err {lerr}"
+    return err
+
+
+def test_golden_vectors_of_the_reference_kernel(lib, golden):
+    g = golden["fwd"]
+    for case in golden_cases(g):
+        dt = DT[int(g[case + "/meta"][0])]
+        run_dt = torch.float16 if dt == torch.float32 else dt   # the kernel is 16-bit only
+        q, k, v = (torch.from_numpy(g[case + "/" + n]).to(run_dt) for n in "qkv")
+        mask = torch.from_numpy(g[case + "/mask"])
+        sm_scale = float(g[case + "/sm_scale"][0])
+        o, lse2, rowmax = _run(q, k, v, mask, sm_scale)
+        o_ref = torch.from_numpy(g[case + "/o"])
+        m_ref = torch.from_numpy(g[case + "/M"])
+        written = ~torch.isnan(m_ref)
+        assert (o[written] - o_ref[written]).abs().max().item() <= O_TOL, case
+        # the reference's M buffer is the running row maximum in the exp2 domain
+        assert (rowmax[written] - m_ref[written]).abs().max().item() <= 2e-2, case
+        # rows the reference never writes: zeros and -inf here
+        assert (o[~written] == 0).all() and (lse2[~written] == -math.inf).all()
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("B,H,N,p,diag,causal", [
+    (1, 1, 64, 1.0, True, False),       # one tile, odd block count
+    (1, 1, 128, 1.0, True, False),      # one full pair
+    (1, 2, 192, 0.5, True, False),      # odd nb: last pair has one block
+    (2, 3, 256, 0.5, False, False),     # rows with no tile
+    (1, 1, 1024, 0.1, True, False),     # BASELINE config 1 shape
+    (1, 2, 1024, 1.0, True, False),     # dense
+    (2, 2, 512, 0.25, True, True),      # block-causal sparse
+])
+def test_forward_matches_oracle(lib, dtype, B, H, N, p, diag, causal):
+    q, k, v = oracle.make_qkv(B, H, N, 64, seed=N + B, dtype=dtype)
+    mask = oracle.make_block_mask(B, H, N // 64, p, seed=N, diagonal=diag, causal=causal)
+    o, lse2, _ = _run(q, k, v, mask, 0.125)
+    _compare(q, k, v, mask, 0.125, o, lse2)
+
+
+def test_single_tile_and_diagonal_only(lib):
+    q, k, v = oracle.make_qkv(1, 1, 384, 64, seed=3, dtype=torch.float16)
+    single = torch.zeros(1, 1, 6, 6, dtype=torch.bool)
+    single[0, 0, 4, 1] = True
+    o, lse2, _ = _run(q, k, v, single, 0.125)
+    _compare(q, k, v, single, 0.125, o, lse2)
+    diag = torch.eye(6, dtype=torch.bool)[None, None]
+    o, lse2, _ = _run(q, k, v, diag, 0.125)
+    _compare(q, k, v, diag, 0.125, o, lse2)
+
+
+def test_large_logits_trigger_the_lazy_rescale(lib):
+    # keys grow along the sequence so the running maximum rises by far more than 2^8 between tiles
+    q, k, v = oracle.make_qkv(1, 1, 512, 64, seed=4, dtype=torch.float16)
+    ramp = torch.linspace(0.2, 6.0, 512)[None, None, :, None]
+    k = (k.float() * ramp).half()
+    mask = torch.ones(1, 1, 8, 8, dtype=torch.bool)
+    for s in (0.125, 1.3):          # 1.3 is the reference's default sm_scale
+        o, lse2, _ = _run(q, k, v, mask, s)
+        _compare(q, k, v, mask, s, o, lse2)
+
+
+def test_public_op_block_and_dense_masks(lib):
+    from fa2_custom_mask import flash_attention_custom_mask
+    q, k, v = (t.cuda() for t in oracle.make_qkv(2, 2, 256, 64, seed=6, dtype=torch.bfloat16))
+    mask = oracle.make_block_mask(2, 2, 4, 0.5, seed=6)
+    o_ref, _ = oracle.attn_forward(q.cpu(), k.cpu(), v.cpu(), mask, 0.125)
+    o1 = flash_attention_custom_mask(q, k, v, mask.cuda(), 0.125)
+    assert o1.dtype == q.dtype and o1.shape == q.shape
+    assert (o1.float().cpu() - o_ref).abs().max() <= O_TOL
+    o2 = flash_attention_custom_mask(q, k, v, oracle.expand_block_mask(mask).cuda(), 0.125)
+    assert torch.equal(o1, o2)                       # dense mask reduces to the same block mask
+    shared = mask[:1, :1]
+    o3 = flash_attention_custom_mask(q, k, v, shared.cuda(), 0.125)     # broadcast over B, H
+    o3_ref, _ = oracle.attn_forward(q.cpu(), k.cpu(), v.cpu(), shared.expand(2, 2, 4, 4), 0.125)
+    assert (o3.float().cpu() - o3_ref).abs().max() <= O_TOL
+    empty = torch.zeros(2, 2, 4, 4, dtype=torch.bool).cuda()
+    assert (flash_attention_custom_mask(q, k, v, empty, 0.125) == 0).all()   # fa2_custom_mask.py:49-51
+    # non-contiguous inputs ([B,N,H,D] storage viewed as [B,H,N,D])
+    qt = q.transpose(1, 2).contiguous().transpose(1, 2)
+    o4 = flash_attention_custom_mask(qt, k, v, mask.cuda(), 0.125)
+    assert torch.equal(o4, o1)
+
+
+def test_run_to_run_determinism(lib):
+    q, k, v = oracle.make_qkv(1, 2, 1024, 64, seed=8, dtype=torch.float16)
+    mask = oracle.make_block_mask(1, 2, 16, 0.3, seed=8)
+    a = _run(q, k, v, mask, 0.125)
+    b = _run(q, k, v, mask, 0.125)
+    assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+
+
+@pytest.mark.parametrize("N,p,dtype", [(6400, 0.1, torch.float16), (17536, 0.1, torch.float16),
+                                       (6400, 1.0, torch.float16)])
+def test_baseline_sizes_against_gpu_fp32_reference(lib, N, p, dtype):
+    """Full BASELINE sizes: the same fp32 naive arithmetic as the oracle, evaluated on the GPU in
+    query-row chunks (the CPU oracle would need minutes), plus a linearity property in V."""
+    from fa2_custom_mask import attention_forward, build_tile_lists
+    q, k, v = (t.cuda() for t in oracle.make_qkv(1, 1, N, 64, seed=N, dtype=dtype))
+    mask = oracle.make_block_mask(1, 1, N // 64, p, seed=N).cuda()
+    lists = build_tile_lists(mask, want_k=False)
+    o, lse2, _ = attention_forward(q, k, v, lists, 0.125)
+    worst = 0.0
+    for r0 in range(0, N, 2048):
+        r1 = min(N, r0 + 2048)
+        s = (q[0, 0, r0:r1].float() @ k[0, 0].float().T) * 0.125
+        dense = mask[0, 0, r0 // 64:(r1 + 63) // 64].repeat_interleave(64, 0).repeat_interleave(64, 1)
+        s = s.masked_fill(~dense[: r1 - r0], float("-inf"))
+        ref = torch.softmax(s, -1) @ v[0, 0].float()
+        worst = max(worst, (o[0, 0, r0:r1].float() - ref).abs().max().item())
+        lerr = (lse2[0, 0, r0:r1] * math.log(2.0) - torch.logsumexp(s, -1)).abs().max().item()
+        assert lerr <= LSE_TOL
+    assert worst <= O_TOL, worst
+    # attention is linear in V: O(2V) == 2 O(V) up to output rounding
+    o2, _, _ = attention_forward(q, k, (v.float() * 2).to(dtype), lists, 0.125)
+    assert (o2.float() - 2 * o.float()).abs().max().item() <= 2e-2
