@@ -1,0 +1,302 @@
+"""Benchmark of the block-sparse attention forward path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (`config.workload`): the forward of B=1, H=1, N=17536, D=64, fp16, 64x64 block mask with
+Bernoulli(0.1) blocks plus the diagonal, q,k,v ~ N(0,1), sm_scale = 1/8 — synthetic, seeded,
+standing in for the reference's kernel-test.py inputs.  At N GPUs every rank runs its own head of
+that shape (weak scaling, no collective on the data path).
+
+One step = the whole public path on resident inputs: block mask -> tile lists (3 kernels) -> forward
+kernel.  `value` is active-tile TFLOP/s = listed tiles * 4*64*64*64 FLOP / step time; L2 is flushed
+(untimed) between steps because the inputs are smaller than L2.  `roofline` times the forward
+kernel alone with its own CUDA events inside the same steps.  `e2e` runs the public op
+flash_attention_custom_mask from pinned host buffers (H2D of q,k,v,mask and D2H of O inside the
+timed region).  `cpu_baseline` / `--impl reference` time the reference's naive
+matmul + masked softmax arithmetic (kernel-test.py:37-40) on the host cores.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+PKG = os.path.join(ROOT, "customize-block-sparse-attention-with-triton_b200")
+for _p in (PKG, ROOT):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import torch  # noqa: E402
+
+N_CTX, HEAD_DIM, DENSITY, SM_SCALE = 17536, 64, 0.1, 0.125
+FLOP_PER_TILE = 4 * 64 * 64 * HEAD_DIM
+WORKLOAD = "fwd fp16 B=1,H=1,N=17536,D=64, 64x64 block mask Bernoulli(0.1)+diagonal (per GPU)"
+METRIC = "fwd_active_tile_tflops_N17536_d64_p0.1"
+# DRAM bytes (read + write) of one forward-kernel launch on this workload from the ncu capture
+# summarised in profiles/attn_fwd_kernel_N17536_p0.1.md; None until a capture exists.
+FWD_KERNEL_DRAM_BYTES = None
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            d = json.load(fh)
+        return float(d["bf16_tflops"]), float(d["hbm_gbs"]), "measured"
+    return 1590.0, 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(index), f"--query-gpu={self.QUERY}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def make_inputs(seed, device=None, pinned=False):
+    from oracle import oracle
+    q, k, v = oracle.make_qkv(1, 1, N_CTX, HEAD_DIM, seed=seed, dtype=torch.float16)
+    mask = oracle.make_block_mask(1, 1, N_CTX // 64, DENSITY, seed=seed)
+    tiles = int(mask.sum())
+    if pinned:
+        return [t.pin_memory() for t in (q, k, v, mask)], tiles
+    if device is not None:
+        return [t.to(device) for t in (q, k, v, mask)], tiles
+    return [q, k, v, mask], tiles
+
+
+CPU_SAMPLE_ROWS = 4096  # query rows of the workload that one CPU step computes (all keys)
+CPU_SAMPLE = ("first 4096 of the 17536 query rows against all keys, fp32 naive matmul + "
+              "masked softmax (kernel-test.py:37-40)")
+
+
+def cpu_sample(q, k, v, mask):
+    """fp32 host tensors of the bounded CPU sample and the number of listed tiles it covers."""
+    from oracle import oracle
+    rows = CPU_SAMPLE_ROWS
+    sub = mask[:, :, : rows // 64].cpu()
+    dense = oracle.expand_block_mask(sub)
+    return (q[:, :, :rows].float().cpu(), k.float().cpu(), v.float().cpu(), dense), int(sub.sum())
+
+
+def cpu_reference_step(q, k, v, dense, threads):
+    """One pass of the reference's naive path on the host cores over the sample."""
+    from oracle import oracle
+    torch.set_num_threads(threads)
+    t0 = time.perf_counter()
+    out = oracle.naive_cpu_forward(q, k, v, dense, SM_SCALE)
+    dt = time.perf_counter() - t0
+    return dt, out
+
+
+def run_reference(args, rank, world):
+    """--impl reference: the naive matmul + masked softmax on the host cores, rank 0 only."""
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    (q, k, v, mask), _ = make_inputs(seed=2)
+    (q, k, v, dense), tiles = cpu_sample(q, k, v, mask)
+    for _ in range(args.warmup):
+        cpu_reference_step(q, k, v, dense, threads)
+    times = [cpu_reference_step(q, k, v, dense, threads)[0] for _ in range(args.steps)]
+    total = sum(times)
+    value = tiles * FLOP_PER_TILE * args.steps / total / 1e12
+    sample = CPU_SAMPLE + ", one sample per step"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * total / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "path": "naive matmul + masked softmax on host cores"},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+    }))
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch.distributed as dist
+    from fa2_custom_mask import (attention_forward, build_tile_lists, check_status,
+                                 flash_attention_custom_mask, new_status_word)
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    (q, k, v, mask), tiles = make_inputs(seed=2 + rank, device=dev)
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    status = new_status_word(dev)
+
+    def step():
+        lists = build_tile_lists(mask, want_q=True, want_k=False)
+        a = torch.cuda.Event(enable_timing=True)
+        b = torch.cuda.Event(enable_timing=True)
+        a.record()
+        out = attention_forward(q, k, v, lists, SM_SCALE, status=status)
+        b.record()
+        return out, a, b
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    for _ in range(args.warmup):
+        flush.zero_()
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    step_ev, kern_ev = [], []
+    for _ in range(args.steps):
+        flush.zero_()
+        s0 = torch.cuda.Event(enable_timing=True)
+        s1 = torch.cuda.Event(enable_timing=True)
+        s0.record()
+        _, a, b = step()
+        s1.record()
+        step_ev.append((s0, s1))
+        kern_ev.append((a, b))
+    barrier()
+    check_status(status)
+    step_ms = sum(a.elapsed_time(b) for a, b in step_ev)
+    kern_ms = sum(a.elapsed_time(b) for a, b in kern_ev)
+
+    # ---- end to end: public op, pinned host inputs, D2H of the output ----
+    (hq, hk, hv, hmask), _ = make_inputs(seed=2 + rank, pinned=True)
+    h_out = torch.empty_like(hq).pin_memory()
+
+    def e2e_step():
+        dq, dk, dv, dm = (t.to(dev, non_blocking=True) for t in (hq, hk, hv, hmask))
+        o = flash_attention_custom_mask(dq, dk, dv, dm, SM_SCALE)
+        h_out.copy_(o, non_blocking=True)
+
+    for _ in range(args.warmup):
+        e2e_step()
+    barrier()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if sampler else None
+
+    red = torch.tensor([step_ms, kern_ms, e2e_ms], dtype=torch.float64, device=dev)
+    tl = torch.tensor([float(tiles)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(red, op=dist.ReduceOp.MAX)
+        dist.all_reduce(tl, op=dist.ReduceOp.SUM)
+    step_ms, kern_ms, e2e_ms = red.tolist()
+    total_tiles = tl.item()
+    if rank != 0:
+        return
+
+    peak_tf, peak_gbs, peak_kind = measured_peaks()
+    value = total_tiles * FLOP_PER_TILE * args.steps / (step_ms * 1e-3) / 1e12
+    # per-GPU kernel figure: this rank's tiles over its own mean kernel time (max over ranks)
+    achieved = (total_tiles / world) * FLOP_PER_TILE * args.steps / (kern_ms * 1e-3) / 1e12
+    h2d = sum(t.numel() * t.element_size() for t in (hq, hk, hv, hmask))
+    d2h = h_out.numel() * h_out.element_size()
+    line = {
+        "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_ms / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
+        "data": "synthetic",
+        "config": {"workload": WORKLOAD, "step": "block mask -> tile lists -> forward kernel",
+                   "tiles_per_gpu": total_tiles / world, "sharding": "one head per GPU",
+                   "l2": "flushed between steps (256 MiB write, untimed)"},
+        "fwd_kernel_ms": kern_ms / args.steps,
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s",
+                     "frac": achieved / peak_tf, "traffic": FWD_KERNEL_DRAM_BYTES,
+                     "kernel": "attn_fwd_kernel", "peak_kind": peak_kind + " (burst bf16 GEMM)"},
+        "e2e": {"value": total_tiles * FLOP_PER_TILE * args.steps / (e2e_ms * 1e-3) / 1e12,
+                "unit": "TFLOP/s", "ms_per_step": e2e_ms / args.steps,
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": 4 * args.steps,
+        "clocks": clocks,
+    }
+    if world == 1:
+        threads = os.cpu_count() or 1
+        (cq, ck, cv, dense), sample_tiles = cpu_sample(q, k, v, mask)
+        cpu_reference_step(cq, ck, cv, dense, threads)
+        times = [cpu_reference_step(cq, ck, cv, dense, threads)[0] for _ in range(7)]
+        line["cpu_baseline"] = {
+            "value": sample_tiles * FLOP_PER_TILE / statistics.median(times) / 1e12,
+            "unit": "TFLOP/s", "cores": threads, "kind": "port",
+            "sample": CPU_SAMPLE + ", 1 warm-up + median of 7"}
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback for the product path")
+    import __graft_entry__
+    if rank == 0:
+        __graft_entry__.build()
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        dist.barrier()
+    try:
+        run_ours(args, rank, world, local_rank)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
