@@ -11,11 +11,49 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
+// One lane of a converged warp; the same lane on every call.  Code that feeds tcgen05 / TMA
+// instructions runs warp-wide (so addresses and descriptors stay warp-uniform) and only the issue
+// itself is guarded by this predicate.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "elect.sync _|P, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+__device__ __forceinline__ int uniform_warp_index() {
+  return __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
+}
+__device__ __forceinline__ void named_barrier_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
 __device__ __forceinline__ uint64_t global_timer_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Optional timeline trace (builds with -DBSA_TRACE only): one CTA records clock64() at chosen
+// points into a device array that a debug entry point copies out.  Compiled out otherwise.
+// ---------------------------------------------------------------------------------------------
+#ifdef BSA_TRACE
+#ifndef BSA_TRACE_CTA
+#define BSA_TRACE_CTA 0
+#endif
+constexpr int kTraceRoles = 8, kTraceSteps = 96, kTraceSlots = 4;
+static __device__ long long g_bsa_trace[kTraceRoles * kTraceSteps * kTraceSlots];  // per file
+#define BSA_TR(role, step, slot)                                                       \
+  do {                                                                                 \
+    if (blockIdx.x == BSA_TRACE_CTA && (step) < bsa::kTraceSteps)                      \
+      bsa::g_bsa_trace[((role) * bsa::kTraceSteps + (step)) * bsa::kTraceSlots + (slot)] = clock64(); \
+  } while (0)
+#else
+#define BSA_TR(role, step, slot) ((void)0)
+#endif
 
 // ---------------------------------------------------------------------------------------------
 // mbarrier
