@@ -1,17 +1,24 @@
 // Forward block-sparse attention for sm_100a.
 //
 // One CTA owns one PAIR of adjacent query blocks (128 query rows = the 128 lanes of a tcgen05
-// accumulator) of one (batch, head) and walks that pair's list of key blocks ("steps"):
-//   warp 8  : TMA producer — Q once, then only the listed K/V tiles into an 8-stage smem ring
-//   warp 9  : tcgen05.mma issuer and TMEM owner — S_j = Q K_j^T into a ring of 4 TMEM slots, issued
-//             up to 4 steps ahead; O_g += P_j V_j with P read from TMEM and V as an MN-major
-//             smem operand, into the accumulator of softmax group g = j mod 2
-//   warps 0..3 (group 0, even steps) and 4..7 (group 1, odd steps): online softmax, one thread
-//             per query row (TMEM lane): tcgen05.ld of S, exp2, P written back over S as 16-bit,
-//             lazy rescale of the group's own O.  Two groups give every SM sub-partition two
-//             softmax warps to interleave, and let the two halves of the pair drift apart.
+// accumulator) of one (batch, head) and walks that pair's list of key blocks two at a time
+// ("supersteps" of up to 128 keys):
+//   warp 8   : TMA producer — Q once, then only the listed K/V tiles into a 4-deep ring of
+//              superstages (2 K tiles + 2 V tiles each)
+//   warp 9   : S issuer and TMEM owner — S_u = Q [K_a;K_b]^T as four M=128,N=128,K=16 MMAs into a
+//              ring of 3 TMEM slots (an N=128 instruction keeps the tensor pipe at full rate; an
+//              N=64 one occupies it just as long)
+//   warp 10  : P V issuer — O_g += P_u[:, keys of group g] V[keys of group g] with P read from
+//              TMEM and V as an MN-major smem operand.  S and P V are issued by different warps so
+//              that neither waits behind the other's barrier round trips.
+//   warps 0..3 (group 0: keys 0..31 of every tile) and 4..7 (group 1: keys 32..63): online
+//              softmax, one thread per query row (TMEM lane) and group: tcgen05.ld of S, exp2, P
+//              written back over the group's own S columns as 16-bit, lazy rescale of the group's
+//              own O.  The groups never talk to each other during the loop: each keeps its own
+//              running maximum, row sum and accumulator, and every SM sub-partition always has
+//              two equally loaded softmax warps.
 // The two partial results (m, l, O) of a row are merged in the epilogue.
-// A key block listed by only one of the two query blocks still runs as an M=128 MMA; the warps of
+// A key block listed by only one of the two query blocks still runs as M=128 MMAs; the warps of
 // the other half store P = 0 for it and skip the exponentials.
 //
 // Numerics follow the reference's loop (fa2_custom_mask/fa2_fwd.py:150-196): logits scaled by
@@ -25,23 +32,23 @@
 
 namespace bsa {
 
-constexpr int kFwdStages = 8;   // K/V tiles in flight in shared memory
-constexpr int kFwdSlots = 4;    // S/P tiles in flight in TMEM
-constexpr int kFwdThreads = 320;
+constexpr int kFwdStages = 4;   // superstages (2 K + 2 V tiles) in flight in shared memory
+constexpr int kFwdSlots = 3;    // S/P supertiles (128 TMEM columns) in flight
+constexpr int kFwdThreads = 352;
 constexpr uint32_t kTileBytes = 64 * 64 * 2;       // one K or V tile
 constexpr uint32_t kQBytes = 128 * 64 * 2;         // one query-pair tile
 constexpr uint32_t kFwdTmemCols = 512;
-constexpr uint32_t kTmemO = 256;                   // O of group g at kTmemO + 64 g; slot r at 64 r
+constexpr uint32_t kTmemO = 384;                   // O of group g at kTmemO + 64 g; slot r at 128 r
 constexpr float kRescaleThreshold = 8.0f;
 
 struct FwdSmem {
   uint8_t q[kQBytes];
-  uint8_t k[kFwdStages][kTileBytes];
-  uint8_t v[kFwdStages][kTileBytes];
+  uint8_t k[kFwdStages][2][kTileBytes];
+  uint8_t v[kFwdStages][2][kTileBytes];
   float stats[2][128][2];  // (m_ref, l) of every row, per softmax group, for the final merge
   uint64_t q_full;
   uint64_t kv_full[kFwdStages];
-  uint64_t kv_empty[kFwdStages];
+  uint64_t kv_empty[kFwdStages];  // P V of the superstep done: stage free, S slot free, O updated
   uint64_t s_full[kFwdSlots];
   uint64_t p_full[kFwdSlots];
   uint32_t tmem_base;
@@ -68,6 +75,41 @@ __device__ __forceinline__ void fwd_give_up(FwdSmem* sm, int32_t* status, int co
   if (status) atomicCAS(status, 0, code);
 }
 
+// exp2 of one 32-column chunk of S against the row's reference maximum; returns the packed
+// 16-bit probabilities and adds their fp32 sum to l.
+template <bool kBf16>
+__device__ __forceinline__ void exp_chunk(const uint32_t* sr, float c, float neg_m, uint32_t* pk,
+                                          float& l) {
+  float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+#pragma unroll
+  for (int i = 0; i < 32; i += 4) {
+    const float p0 = ex2_approx(fmaf(__uint_as_float(sr[i]), c, neg_m));
+    const float p1 = ex2_approx(fmaf(__uint_as_float(sr[i + 1]), c, neg_m));
+    const float p2 = ex2_approx(fmaf(__uint_as_float(sr[i + 2]), c, neg_m));
+    const float p3 = ex2_approx(fmaf(__uint_as_float(sr[i + 3]), c, neg_m));
+    l0 += p0;
+    l1 += p1;
+    l2 += p2;
+    l3 += p3;
+    pk[i / 2] = pack_2x16<kBf16>(p0, p1);
+    pk[i / 2 + 1] = pack_2x16<kBf16>(p2, p3);
+  }
+  l += (l0 + l1) + (l2 + l3);
+}
+
+__device__ __forceinline__ float max_chunk(const uint32_t* sr) {
+  float mx0 = __uint_as_float(sr[0]), mx1 = __uint_as_float(sr[1]);
+  float mx2 = __uint_as_float(sr[2]), mx3 = __uint_as_float(sr[3]);
+#pragma unroll
+  for (int i = 4; i < 32; i += 4) {
+    mx0 = fmaxf(mx0, __uint_as_float(sr[i]));
+    mx1 = fmaxf(mx1, __uint_as_float(sr[i + 1]));
+    mx2 = fmaxf(mx2, __uint_as_float(sr[i + 2]));
+    mx3 = fmaxf(mx3, __uint_as_float(sr[i + 3]));
+  }
+  return fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+}
+
 template <bool kBf16>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -86,7 +128,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int h = bh % p.H;
   const int64_t li = static_cast<int64_t>(b * p.list_b_stride + h * p.list_h_stride) * p.npair + pr;
   const int beg = __ldg(p.pair_ptr + li);
-  const int n_steps = __ldg(p.pair_ptr + li + 1) - beg;
+  const int n_tiles = __ldg(p.pair_ptr + li + 1) - beg;
+  const int n_super = (n_tiles + 1) >> 1;
   const int32_t* ents = p.pair_ent + beg;
 
   // ---- set-up ----
@@ -98,7 +141,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
     for (int i = 0; i < kFwdSlots; ++i) {
       mbar_init(smem_u32(&sm->s_full[i]), 1);
-      mbar_init(smem_u32(&sm->p_full[i]), 4);  // one arrival per warp of the step's group
+      mbar_init(smem_u32(&sm->p_full[i]), 8);  // one arrival per softmax warp
     }
     sm->abort_flag = 0;
     mbar_fence_init();
@@ -120,82 +163,108 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
   if (warp == 8) {
     // =========================== TMA producer ===========================
-    if (n_steps > 0) {
+    if (n_super > 0) {
       const bool leader = elect_one();
       if (leader) {
         mbar_expect_tx(smem_u32(&sm->q_full), kQBytes);
         tma_load_4d(smem_u32(sm->q), &tm_q, smem_u32(&sm->q_full), 0, pr * 128, h, b);
       }
-      for (int j = 0; j < n_steps; ++j) {
-        const int s = j % kFwdStages;
-        const uint32_t ph = (j / kFwdStages) & 1;
-        if (!mbar_wait_warp(smem_u32(&sm->kv_empty[s]), ph ^ 1, abort_flag)) {
+      for (int u = 0; u < n_super; ++u) {
+        const int ss = u % kFwdStages;
+        const int nt = min(2, n_tiles - 2 * u);
+        const int n0 = __ldg(ents + 2 * u) >> 2;
+        const int n1 = nt == 2 ? (__ldg(ents + 2 * u + 1) >> 2) : 0;
+        if (!mbar_wait_warp(smem_u32(&sm->kv_empty[ss]), ((u / kFwdStages) & 1) ^ 1, abort_flag)) {
           fwd_give_up(sm, p.status, kFailProducer);
           break;
         }
-        if (lane == 0) BSA_TR(0, j, 0);
-        const int nblk = __ldg(ents + j) >> 2;
         if (leader) {
-          const uint32_t bar = smem_u32(&sm->kv_full[s]);
-          mbar_expect_tx(bar, 2 * kTileBytes);
-          tma_load_4d(smem_u32(sm->k[s]), &tm_k, bar, 0, nblk * 64, h, b);
-          tma_load_4d(smem_u32(sm->v[s]), &tm_v, bar, 0, nblk * 64, h, b);
-          BSA_TR(0, j, 1);
+          BSA_TR(0, u, 0);
+          const uint32_t bar = smem_u32(&sm->kv_full[ss]);
+          mbar_expect_tx(bar, 2 * kTileBytes * nt);
+          tma_load_4d(smem_u32(sm->k[ss][0]), &tm_k, bar, 0, n0 * 64, h, b);
+          tma_load_4d(smem_u32(sm->v[ss][0]), &tm_v, bar, 0, n0 * 64, h, b);
+          if (nt == 2) {
+            tma_load_4d(smem_u32(sm->k[ss][1]), &tm_k, bar, 0, n1 * 64, h, b);
+            tma_load_4d(smem_u32(sm->v[ss][1]), &tm_v, bar, 0, n1 * 64, h, b);
+          }
+          BSA_TR(0, u, 1);
         }
       }
     }
   } else if (warp == 9) {
-    // =========================== MMA issuer ===========================
-    if (n_steps > 0) {
-      constexpr uint32_t idesc_s = umma_idesc(kBf16, 0, 0, 128, 64);   // Q (K-major) x K (K-major)
-      constexpr uint32_t idesc_pv = umma_idesc(kBf16, 0, 1, 128, 64);  // P (TMEM) x V (MN-major)
+    // =========================== S issuer ===========================
+    if (n_super > 0) {
+      constexpr uint32_t idesc_s128 = umma_idesc(kBf16, 0, 0, 128, 128);  // Q x [K_a;K_b]
+      constexpr uint32_t idesc_s64 = umma_idesc(kBf16, 0, 0, 128, 64);    // odd tail: one tile
       const bool leader = elect_one();
       const uint64_t desc_q = smem_desc_sw128(smem_u32(sm->q), 16, 1024);
-      const uint64_t desc_k0 = smem_desc_sw128(smem_u32(sm->k[0]), 16, 1024);
-      const uint64_t desc_v0 = smem_desc_sw128(smem_u32(sm->v[0]), 8192, 1024);
+      const uint64_t desc_k0 = smem_desc_sw128(smem_u32(sm->k[0][0]), 16, 1024);
       bool ok = mbar_wait_warp(smem_u32(&sm->q_full), 0, abort_flag);
-      int s_next = 0;  // next S tile to issue
-      for (int j = 0; ok && j < n_steps; ++j) {
-        const int limit = min(n_steps, j + kFwdSlots);
-        while (s_next < limit) {
-          const int st = s_next % kFwdStages;
-          ok = mbar_wait_warp(smem_u32(&sm->kv_full[st]), (s_next / kFwdStages) & 1, abort_flag);
-          if (!ok) break;
-          if (leader) {
-            BSA_TR(1, s_next, 0);
-            const int slot = s_next % kFwdSlots;
-            const uint64_t desc_k = desc_k0 + static_cast<uint64_t>(st * (kTileBytes >> 4));
-#pragma unroll
-            for (int kk = 0; kk < 4; ++kk)
-              umma_ss(tmem + 64 * slot, desc_q + 2 * kk, desc_k + 2 * kk, idesc_s, kk > 0);
-            tc_commit(smem_u32(&sm->s_full[slot]));
-            BSA_TR(1, s_next, 1);
-          }
-          ++s_next;
-        }
+      for (int u = 0; ok && u < n_super; ++u) {
+        const int ss = u % kFwdStages;
+        const int slot = u % kFwdSlots;
+        const int nt = min(2, n_tiles - 2 * u);
+        ok = mbar_wait_warp(smem_u32(&sm->kv_full[ss]), (u / kFwdStages) & 1, abort_flag);
         if (!ok) break;
-        const int slot = j % kFwdSlots;
-        ok = mbar_wait_warp(smem_u32(&sm->p_full[slot]), (j / kFwdSlots) & 1, abort_flag);
+        if (u >= kFwdSlots) {
+          // the slot still holds P of superstep u-3 until that superstep's P V is complete
+          const int up = u - kFwdSlots;
+          ok = mbar_wait_warp(smem_u32(&sm->kv_empty[up % kFwdStages]), (up / kFwdStages) & 1,
+                              abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+        }
+        if (leader) {
+          BSA_TR(1, u, 0);
+          const uint64_t desc_k = desc_k0 + static_cast<uint64_t>(ss * ((2 * kTileBytes) >> 4));
+          const uint32_t idesc = nt == 2 ? idesc_s128 : idesc_s64;
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            umma_ss(tmem + 128 * slot, desc_q + 2 * kk, desc_k + 2 * kk, idesc, kk > 0);
+          tc_commit(smem_u32(&sm->s_full[slot]));
+          BSA_TR(1, u, 1);
+        }
+      }
+      if (!ok) fwd_give_up(sm, p.status, kFailMma);
+    }
+  } else if (warp == 10) {
+    // =========================== P V issuer ===========================
+    if (n_super > 0) {
+      constexpr uint32_t idesc_pv = umma_idesc(kBf16, 0, 1, 128, 64);  // P (TMEM) x V (MN-major)
+      const bool leader = elect_one();
+      const uint64_t desc_v0 = smem_desc_sw128(smem_u32(sm->v[0][0]), 8192, 1024);
+      bool ok = true;
+      for (int u = 0; ok && u < n_super; ++u) {
+        const int ss = u % kFwdStages;
+        const int slot = u % kFwdSlots;
+        const int nt = min(2, n_tiles - 2 * u);
+        ok = mbar_wait_warp(smem_u32(&sm->p_full[slot]), (u / kFwdSlots) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
         if (leader) {
-          BSA_TR(1, j, 2);
-          const int st = j % kFwdStages;
-          const int g = j & 1;
-          const uint64_t desc_v = desc_v0 + static_cast<uint64_t>(st * (kTileBytes >> 4));
+          BSA_TR(7, u, 0);
+          // P of the slot: columns [32 g + 16 t, +16) hold keys [32 g, 32 g + 32) of tile t
+          for (int g = 0; g < 2; ++g) {
+            const uint32_t d_o = tmem + kTmemO + 64 * g;
+            for (int t = 0; t < nt; ++t) {
+              const uint64_t desc_v =
+                  desc_v0 + static_cast<uint64_t>((ss * 2 + t) * (kTileBytes >> 4));
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk)
-            umma_ts(tmem + kTmemO + 64 * g, tmem + 64 * slot + 8 * kk, desc_v + 128 * kk, idesc_pv,
-                    (j >= 2) || (kk > 0));
-          tc_commit(smem_u32(&sm->kv_empty[st]));  // frees the stage and marks P V of step j done
-          BSA_TR(1, j, 3);
+              for (int k2 = 0; k2 < 2; ++k2)
+                umma_ts(d_o, tmem + 128 * slot + 32 * g + 16 * t + 8 * k2,
+                        desc_v + 128 * (2 * g + k2), idesc_pv, (u > 0) || (t > 0) || (k2 > 0));
+            }
+          }
+          tc_commit(smem_u32(&sm->kv_empty[ss]));
+          BSA_TR(7, u, 1);
         }
       }
       if (!ok) fwd_give_up(sm, p.status, kFailMma);
     }
   } else {
     // =========================== softmax + epilogue ===========================
-    const int g = warp >> 2;          // softmax group: steps j = g, g+2, ...
+    const int g = warp >> 2;          // softmax group: keys [32 g, 32 g + 32) of every tile
     const int quarter = warp & 3;     // TMEM lane quarter this warp may touch
     const int half = quarter >> 1;    // which query block of the pair
     const int r_cta = quarter * 32 + lane;
@@ -205,35 +274,34 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const float c = p.scale_log2;
     float m_ref = -INFINITY, m_true = -INFINITY, l = 0.f;
     bool ok = true;
-    int ent_next = g < n_steps ? __ldg(ents + g) : 0;
+    int e0 = n_tiles > 0 ? __ldg(ents) : 0;
+    int e1 = n_tiles > 1 ? __ldg(ents + 1) : 0;
 
-    for (int j = g; j < n_steps; j += 2) {
-      const int ent = ent_next;
-      if (j + 2 < n_steps) ent_next = __ldg(ents + j + 2);
-      const int slot = j % kFwdSlots;
-      const bool listed = (ent >> half) & 1;
-      ok = mbar_wait_warp(smem_u32(&sm->s_full[slot]), (j / kFwdSlots) & 1, abort_flag);
+    for (int u = 0; u < n_super; ++u) {
+      const int slot = u % kFwdSlots;
+      const int nt = min(2, n_tiles - 2 * u);
+      const bool listed0 = ((e0 >> half) & 1) != 0;
+      const bool listed1 = nt == 2 && ((e1 >> half) & 1) != 0;
+      if (2 * u + 2 < n_tiles) e0 = __ldg(ents + 2 * u + 2);
+      if (2 * u + 3 < n_tiles) e1 = __ldg(ents + 2 * u + 3);
+      ok = mbar_wait_warp(smem_u32(&sm->s_full[slot]), (u / kFwdSlots) & 1, abort_flag);
       if (!ok) break;
-      if (lane == 0 && !(warp & 1)) BSA_TR(2 + (warp >> 1), j, 0);
+      if (lane == 0 && !(warp & 1)) BSA_TR(2 + (warp >> 1), u, 0);
       tc_fence_after();
-      const uint32_t s_addr = tmem + lane_base + 64 * slot;
-      uint32_t pk[32];
-      if (listed) {
-        uint32_t sr[64];
-        tmem_ld_32x32b_x32(s_addr, sr);
-        tmem_ld_32x32b_x32(s_addr + 32, sr + 32);
+      // S of tile t, this group's keys: columns [64 t + 32 g, +32) of the slot; the group's P goes
+      // over its own tile-a columns: [32 g + 16 t, +16)
+      const uint32_t s_addr = tmem + lane_base + 128 * slot + 32 * g;
+      uint32_t pk0[16], pk1[16];
+      if (listed0 || listed1) {
+        uint32_t sr0[32], sr1[32];
+        if (listed0) tmem_ld_32x32b_x32(s_addr, sr0);
+        if (listed1) tmem_ld_32x32b_x32(s_addr + 64, sr1);
         tc_wait_ld();
-        if (lane == 0 && !(warp & 1)) BSA_TR(2 + (warp >> 1), j, 1);
-        float mx0 = __uint_as_float(sr[0]), mx1 = __uint_as_float(sr[1]);
-        float mx2 = __uint_as_float(sr[2]), mx3 = __uint_as_float(sr[3]);
-#pragma unroll
-        for (int i = 4; i < 64; i += 4) {
-          mx0 = fmaxf(mx0, __uint_as_float(sr[i]));
-          mx1 = fmaxf(mx1, __uint_as_float(sr[i + 1]));
-          mx2 = fmaxf(mx2, __uint_as_float(sr[i + 2]));
-          mx3 = fmaxf(mx3, __uint_as_float(sr[i + 3]));
-        }
-        const float zmax = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * c;
+        if (lane == 0 && !(warp & 1)) BSA_TR(2 + (warp >> 1), u, 1);
+        float mx = -INFINITY;
+        if (listed0) mx = max_chunk(sr0);
+        if (listed1) mx = fmaxf(mx, max_chunk(sr1));
+        const float zmax = mx * c;
         m_true = fmaxf(m_true, zmax);
         float alpha = 1.f;
         bool rescale = false;
@@ -246,11 +314,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           rescale = true;
         }
         if (__any_sync(0xffffffffu, rescale)) {
-          // The group's O must hold its previous step's product (step j-2 >= 0) before it is
-          // scaled.  kv_empty of that step's stage completes exactly then; its next phase belongs
-          // to step j+6, which cannot complete before this warp has delivered P_j.
-          ok = mbar_wait_warp(smem_u32(&sm->kv_empty[(j - 2) % kFwdStages]),
-                              ((j - 2) / kFwdStages) & 1, abort_flag);
+          // The group's O must hold the previous superstep's product (u >= 1 here) before it is
+          // scaled.  P V of superstep u-1 completing frees that superstep's stage; S_u being
+          // complete implies P V of u-3 and earlier are complete, and P V of u+3 cannot complete
+          // before this warp delivers P_u, so the awaited phase is unambiguous.
+          ok = mbar_wait_warp(smem_u32(&sm->kv_empty[(u - 1) % kFwdStages]),
+                              ((u - 1) / kFwdStages) & 1, abort_flag);
           if (!ok) break;
           tc_fence_after();
 #pragma unroll
@@ -265,40 +334,40 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           }
         }
         const float neg_m = -m_ref;
-        float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+        if (listed0) {
+          exp_chunk<kBf16>(sr0, c, neg_m, pk0, l);
+        } else {
 #pragma unroll
-        for (int i = 0; i < 64; i += 4) {
-          const float p0 = ex2_approx(fmaf(__uint_as_float(sr[i]), c, neg_m));
-          const float p1 = ex2_approx(fmaf(__uint_as_float(sr[i + 1]), c, neg_m));
-          const float p2 = ex2_approx(fmaf(__uint_as_float(sr[i + 2]), c, neg_m));
-          const float p3 = ex2_approx(fmaf(__uint_as_float(sr[i + 3]), c, neg_m));
-          l0 += p0;
-          l1 += p1;
-          l2 += p2;
-          l3 += p3;
-          pk[i / 2] = pack_2x16<kBf16>(p0, p1);
-          pk[i / 2 + 1] = pack_2x16<kBf16>(p2, p3);
+          for (int i = 0; i < 16; ++i) pk0[i] = 0u;
         }
-        l += (l0 + l1) + (l2 + l3);
+        if (listed1) {
+          exp_chunk<kBf16>(sr1, c, neg_m, pk1, l);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) pk1[i] = 0u;
+        }
       } else {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) pk[i] = 0u;
+        for (int i = 0; i < 16; ++i) {
+          pk0[i] = 0u;
+          pk1[i] = 0u;
+        }
       }
-      if (lane == 0 && !(warp & 1)) BSA_TR(2 + (warp >> 1), j, 2);
-      tmem_st_32x32b_x32(s_addr, pk);  // P over the first 32 columns of the S slot
+      if (lane == 0 && !(warp & 1)) BSA_TR(2 + (warp >> 1), u, 2);
+      tmem_st_32x32b_x16(s_addr, pk0);
+      if (nt == 2) tmem_st_32x32b_x16(s_addr + 16, pk1);
       tc_wait_st();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&sm->p_full[slot]));
-      if (lane == 0 && !(warp & 1)) BSA_TR(2 + (warp >> 1), j, 3);
+      if (lane == 0 && !(warp & 1)) BSA_TR(2 + (warp >> 1), u, 3);
     }
 
     // ---- epilogue: merge the two groups' partial results of every row ----
-    // the last P V frees the last stage; S of this warp's last step being complete implies every
-    // P V more than four steps back is complete, so the awaited phase cannot be mistaken
-    if (ok && n_steps > 0)
-      ok = mbar_wait_warp(smem_u32(&sm->kv_empty[(n_steps - 1) % kFwdStages]),
-                          ((n_steps - 1) / kFwdStages) & 1, abort_flag);
+    // The last P V frees the last stage; every earlier phase of that barrier is long complete.
+    if (ok && n_super > 0)
+      ok = mbar_wait_warp(smem_u32(&sm->kv_empty[(n_super - 1) % kFwdStages]),
+                          ((n_super - 1) / kFwdStages) & 1, abort_flag);
     if (!ok) fwd_give_up(sm, p.status, kFailSoftmax);
     sm->stats[g][r_cta][0] = m_ref;
     sm->stats[g][r_cta][1] = l;
@@ -321,23 +390,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const float w_ot = m_o == -INFINITY ? 0.f : ex2_approx(m_o - m_all);
       const float l_all = w_me * l + w_ot * l_o;
       const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
-      // weights of accumulator 0 / 1; an accumulator that no step ever wrote is never read
+      // weights of accumulator 0 / 1 (both are written by every superstep)
       const float w0 = (g == 0 ? w_me : w_ot) * inv;
       const float w1 = (g == 0 ? w_ot : w_me) * inv;
       uint32_t packed[16];
-      if (n_steps > 0) {
+      if (n_super > 0) {
         tc_fence_after();
         uint32_t a0[32], a1[32];
         tmem_ld_32x32b_x32(tmem + lane_base + kTmemO + 32 * g, a0);
-        if (n_steps > 1) tmem_ld_32x32b_x32(tmem + lane_base + kTmemO + 64 + 32 * g, a1);
+        tmem_ld_32x32b_x32(tmem + lane_base + kTmemO + 64 + 32 * g, a1);
         tc_wait_ld();
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
           float x0 = __uint_as_float(a0[i]) * w0, x1 = __uint_as_float(a0[i + 1]) * w0;
-          if (n_steps > 1) {
-            x0 = fmaf(__uint_as_float(a1[i]), w1, x0);
-            x1 = fmaf(__uint_as_float(a1[i + 1]), w1, x1);
-          }
+          x0 = fmaf(__uint_as_float(a1[i]), w1, x0);
+          x1 = fmaf(__uint_as_float(a1[i + 1]), w1, x1);
           packed[i / 2] = pack_2x16<kBf16>(x0, x1);
         }
       } else {
