@@ -166,7 +166,7 @@ def run_ours(args, rank, world, local_rank):
     status = new_status_word(dev)
 
     def step():
-        lists = build_tile_lists(mask, want_q=True, want_k=False)
+        lists = build_tile_lists(mask, want_q=False, want_k=False)
         a = torch.cuda.Event(enable_timing=True)
         b = torch.cuda.Event(enable_timing=True)
         a.record()

@@ -46,6 +46,11 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 #endif
 constexpr int kTraceRoles = 8, kTraceSteps = 96, kTraceSlots = 4;
 static __device__ long long g_bsa_trace[kTraceRoles * kTraceSteps * kTraceSlots];  // per file
+static __device__ unsigned long long g_bsa_cta_times[4096 * 4];  // start, end (ns), smid, steps
+#define BSA_TR_CTA(idx, val)                                                           \
+  do {                                                                                 \
+    if (blockIdx.x < 4096) bsa::g_bsa_cta_times[blockIdx.x * 4 + (idx)] = (val);       \
+  } while (0)
 #define BSA_TR(role, step, slot)                                                       \
   do {                                                                                 \
     if (blockIdx.x == BSA_TRACE_CTA && (step) < bsa::kTraceSteps)                      \
@@ -53,6 +58,7 @@ static __device__ long long g_bsa_trace[kTraceRoles * kTraceSteps * kTraceSlots]
   } while (0)
 #else
 #define BSA_TR(role, step, slot) ((void)0)
+#define BSA_TR_CTA(idx, val) ((void)0)
 #endif
 
 // ---------------------------------------------------------------------------------------------
@@ -111,6 +117,29 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity,
                                                volatile int* abort_flag) {
   const bool ok = mbar_wait(bar, parity, abort_flag);
   return __all_sync(0xffffffffu, ok);
+}
+
+// Bounded wait of a whole warp until a shared-memory counter (written by another warp after a
+// __threadfence_block) reaches `target`.  Same give-up rules as mbar_wait.
+__device__ __forceinline__ bool flag_wait_warp(const int* flag, int target,
+                                               volatile int* abort_flag) {
+  const volatile int* f = flag;
+  bool ok = true;
+  if (*f < target) {
+    uint64_t t0 = 0;
+    uint32_t spins = 0;
+    while (*f < target) {
+      if ((++spins & 255u) == 0u) {
+        if (*abort_flag) { ok = false; break; }
+        const uint64_t now = global_timer_ns();
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > BSA_WAIT_LIMIT_NS) { ok = false; break; }
+      }
+    }
+  }
+  ok = __all_sync(0xffffffffu, ok);
+  __threadfence_block();
+  return ok;
 }
 
 // ---------------------------------------------------------------------------------------------

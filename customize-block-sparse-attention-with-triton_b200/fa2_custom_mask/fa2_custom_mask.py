@@ -95,8 +95,11 @@ def reduce_dense_mask(dense: torch.Tensor, return_partial: bool = False):
 
 
 def build_tile_lists(block_mask: torch.Tensor, want_q: bool = True, want_k: bool = True,
-                     want_csr: bool = False, want_groups: bool = False) -> TileLists:
-    """Block mask [..,nb,nb] -> device tile lists (worst-case sized, no host synchronisation)."""
+                     want_csr: bool = True, want_groups: bool = False,
+                     want_csc: bool = False) -> TileLists:
+    """Block mask [..,nb,nb] -> device tile lists (worst-case sized, no host synchronisation).
+    want_csr: row lists (forward kernel); want_q / want_k: query- and key-pair lists (backward
+    kernels); want_csc: transposed CSR; want_groups: the reference's groups layout."""
     lib = _lib.load()
     m4 = _as_4d(_as_bytes(block_mask))
     if not m4.is_cuda:
@@ -113,12 +116,14 @@ def build_tile_lists(block_mask: torch.Tensor, want_q: bool = True, want_k: bool
 
     tl = TileLists(Bm=Bm, Hm=Hm, nb=nb, meta=buf(sizes.meta))
     want_csr = want_csr or want_groups
+    want_csc = want_csc or want_groups
     if want_q:
         tl.qpair_ptr, tl.qpair_ent = buf(sizes.qpair_ptr), buf(sizes.qpair_ent)
     if want_k:
         tl.kpair_ptr, tl.kpair_ent = buf(sizes.kpair_ptr), buf(sizes.kpair_ent)
     if want_csr:
         tl.row_ptr, tl.col_idx = buf(sizes.row_ptr), buf(sizes.col_idx)
+    if want_csc:
         tl.col_ptr, tl.row_idx = buf(sizes.col_ptr), buf(sizes.row_idx)
     if want_groups:
         tl.groups = buf(sizes.groups)
@@ -168,7 +173,7 @@ def _lists_for_mask(mask, B, H, N, device, need_k):
     else:
         raise ValueError(
             f"mask must be a block mask [..,{nb},{nb}] or a dense mask [..,{N},{N}], got {tuple(mask.shape)}")
-    return build_tile_lists(block, want_q=True, want_k=need_k)
+    return build_tile_lists(block, want_csr=True, want_q=need_k, want_k=need_k)
 
 
 def new_status_word(device) -> torch.Tensor:
@@ -199,7 +204,7 @@ def attention_forward(q, k, v, lists: TileLists, sm_scale: float, want_rowmax: b
         _lib.check("bsa_attn_fwd", lib.bsa_attn_fwd(
             _lib.ptr(q), _lib.strides4(q), _lib.ptr(k), _lib.strides4(k), _lib.ptr(v),
             _lib.strides4(v), _lib.ptr(o), _lib.strides4(o), _lib.ptr(lse2), _lib.ptr(rowmax),
-            _lib.ptr(lists.qpair_ptr), _lib.ptr(lists.qpair_ent), sb, sh, float(sm_scale),
+            _lib.ptr(lists.row_ptr), _lib.ptr(lists.col_idx), sb, sh, float(sm_scale),
             _lib.dtype_code(q.dtype), B, H, N, D, _lib.ptr(status), _lib.stream_ptr(q.device)))
     return o, lse2, rowmax
 
@@ -256,7 +261,7 @@ class _attention(torch.autograd.Function):
         lists = _lists_for_mask(mask, B, H, N, q.device, need_k=need_grad)
         o, lse2, _ = attention_forward(q, k, v, lists, sm_scale)
         ctx.save_for_backward(q, k, v, o, lse2, lists.qpair_ptr, lists.qpair_ent,
-                              lists.kpair_ptr, lists.kpair_ent)
+                              lists.kpair_ptr, lists.kpair_ent)  # row lists are forward-only
         ctx.lists_shape = (lists.Bm, lists.Hm, lists.nb)
         ctx.sm_scale = sm_scale
         ctx.HEAD_DIM = D

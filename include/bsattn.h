@@ -86,9 +86,10 @@ int bsa_tile_list_sizes(int B, int H, int nb, bsa_list_sizes* out);
  * Replaces build_groups_from_block_mask (fa2_custom_mask/fa2_custom_mask.py:15-38), whose
  * outputs are reproduced bit-exactly:  n_list == col_idx[0:nnz]  and  groups == groups[0:G].
  *   block      : bytes, logical [B,H,nb,nb], element strides block_strides[4] (0 = broadcast).
- *   row_ptr/col_idx : CSR over rows r=(b*H+h)*nb+m, empty rows kept, columns ascending.
+ *   row_ptr/col_idx : CSR over rows r=(b*H+h)*nb+m, empty rows kept, columns ascending
+ *                     (forward kernel).
  *   col_ptr/row_idx : CSR of the transposed mask (per key block, query blocks ascending).
- *   qpair_ptr/qpair_ent : pair lists over query-block pairs (forward and dQ kernels).
+ *   qpair_ptr/qpair_ent : pair lists over query-block pairs (dQ kernel).
  *   kpair_ptr/kpair_ent : pair lists over key-block pairs (dK/dV kernel).
  *   groups     : rows (b,h,m,start,len) of the non-empty rows only, in row order.
  *   meta       : int32[8] = {nnz, G, qpair entries, kpair entries, 0,0,0,0}.
@@ -109,7 +110,7 @@ int bsa_tile_lists_build(const uint8_t* block, const int64_t block_strides[4], i
  *   rowmax  : optional out fp32 [B,H,N] (may be NULL): running row maximum of the scaled logits in
  *             the exp2 domain, the quantity the reference stores in its `M` buffer
  *             (fa2_custom_mask/fa2_fwd.py:193-196).
- *   qpair_ptr/qpair_ent : pair lists from bsa_tile_lists_build built for a mask of shape
+ *   row_ptr/col_idx : CSR row lists from bsa_tile_lists_build built for a mask of shape
  *             [Bm,Hm,nb,nb]; list_b_stride/list_h_stride give the list index of head (b,h) as
  *             b*list_b_stride + h*list_h_stride (0 for a broadcast axis).
  *   Rows of query blocks without any listed tile get o = 0 (the reference leaves them unwritten).
@@ -118,8 +119,8 @@ int bsa_tile_lists_build(const uint8_t* block, const int64_t block_strides[4], i
  */
 int bsa_attn_fwd(const void* q, const int64_t q_strides[4], const void* k,
                  const int64_t k_strides[4], const void* v, const int64_t v_strides[4], void* o,
-                 const int64_t o_strides[4], float* lse2, float* rowmax, const int32_t* qpair_ptr,
-                 const int32_t* qpair_ent, int list_b_stride, int list_h_stride, float sm_scale,
+                 const int64_t o_strides[4], float* lse2, float* rowmax, const int32_t* row_ptr,
+                 const int32_t* col_idx, int list_b_stride, int list_h_stride, float sm_scale,
                  int dtype, int B, int H, int N, int D, int32_t* status, void* stream);
 
 /*

@@ -17,7 +17,7 @@ DT = {0: torch.float32, 1: torch.float16, 2: torch.bfloat16}
 
 def _run(q, k, v, mask, sm_scale, want_rowmax=True):
     from fa2_custom_mask import attention_forward, build_tile_lists
-    lists = build_tile_lists(mask.cuda(), want_q=True, want_k=False)
+    lists = build_tile_lists(mask.cuda(), want_q=False, want_k=False)
     o, lse2, rowmax = attention_forward(q.cuda(), k.cuda(), v.cuda(), lists, sm_scale, want_rowmax)
     torch.cuda.synchronize()
     return o.float().cpu(), lse2.cpu(), (rowmax.cpu() if rowmax is not None else None)
@@ -131,7 +131,7 @@ def test_baseline_sizes_against_gpu_fp32_reference(lib, N, p, dtype):
     from fa2_custom_mask import attention_forward, build_tile_lists
     q, k, v = (t.cuda() for t in oracle.make_qkv(1, 1, N, 64, seed=N, dtype=dtype))
     mask = oracle.make_block_mask(1, 1, N // 64, p, seed=N).cuda()
-    lists = build_tile_lists(mask, want_k=False)
+    lists = build_tile_lists(mask, want_q=False, want_k=False)
     o, lse2, _ = attention_forward(q, k, v, lists, 0.125)
     worst = 0.0
     for r0 in range(0, N, 2048):
