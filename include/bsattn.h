@@ -175,6 +175,32 @@ int bsa_inv_reorder(const void* in, void* out, const int64_t strides[4], const i
                     int elem_bytes, void* stream);
 
 /*
+ * Forward attention directly from a block mask, allocating nothing.  It has no counterpart in the
+ * reference; it exists for hosts that cannot hand the library device buffers at call time, such as
+ * an inference-engine plugin whose workspace was sized when the engine was built, or a process
+ * whose device memory already belongs in full to another pool.  The row lists that
+ * bsa_tile_lists_build would write into caller memory go into a fixed array inside the library
+ * image instead (BSA_STATIC_SCRATCH_INTS 32-bit words, held by every GPU that loads the library
+ * until the process exits); the result equals bsa_tile_lists_build followed by bsa_attn_fwd.
+ *   block : bytes, logical [Bm,Hm,nb,nb] with element strides block_strides[4]; Bm is 1 or B, Hm is
+ *           1 or H.  All other arguments as in bsa_attn_fwd (rowmax and the status word are not
+ *           offered here).
+ * Limit: 8 + Bm*Hm*nb + 1 + Bm*Hm*nb*nb <= BSA_STATIC_SCRATCH_INTS, else BSA_ERR_TOO_LARGE
+ * (one shared mask up to N = 92,000; eight per-head masks up to N = 32,000).
+ * The first call on each device looks up the array's device address; make that call outside any
+ * stream capture.  The call makes no cudaMalloc/cudaFree and calls no allocating library routine.
+ * All calls on a device share the one array: two calls whose GPU work may overlap (different
+ * streams, or different host threads) race on it and must be serialised by the caller.
+ */
+#define BSA_STATIC_SCRATCH_INTS (2 * 1024 * 1024)
+int bsa_attn_fwd_block_mask_static(const void* q, const int64_t q_strides[4], const void* k,
+                                   const int64_t k_strides[4], const void* v,
+                                   const int64_t v_strides[4], void* o, const int64_t o_strides[4],
+                                   float* lse2, const uint8_t* block,
+                                   const int64_t block_strides[4], int Bm, int Hm, float sm_scale,
+                                   int dtype, int B, int H, int N, int D, void* stream);
+
+/*
  * Synchronises `stream`, reads the device status word and returns BSA_OK, BSA_ERR_DEVICE_TIMEOUT
  * or BSA_ERR_CUDA.  No reference counterpart.
  */
