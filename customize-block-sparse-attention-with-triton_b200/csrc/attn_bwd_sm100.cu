@@ -14,8 +14,10 @@
 // reference's causal loops.  dK and dQ carry the factor sm_scale.
 //
 // Roles: warps 0..7 compute (lane quarter = warp % 4, column half = warp / 4), warp 8 TMA
-// producer, warp 9 MMA issuer and TMEM owner.  A block of the pair that does not list the current
-// step's tile stores zeros for P/dS and skips the exponentials.
+// producer, warp 9 issues the S/dP MMAs and owns TMEM, warp 10 issues the accumulating MMAs (two
+// issuers, so neither waits behind the other's barrier round trips; both run warp-wide with one
+// elected lane issuing).  A block of the pair that does not list the current step's tile stores
+// zeros for P/dS and skips the exponentials.
 #include <math.h>
 
 #include "host_common.h"
@@ -24,7 +26,7 @@
 namespace bsa {
 
 constexpr int kBwdStages = 4;
-constexpr int kBwdThreads = 320;
+constexpr int kBwdThreads = 352;
 constexpr uint32_t kBwdTile = 64 * 64 * 2;
 constexpr uint32_t kBwdPairTile = 128 * 64 * 2;
 constexpr uint32_t kBwdTmemCols = 512;
@@ -44,7 +46,6 @@ struct BwdSmem {
   uint64_t in_empty[kBwdStages];
   uint64_t x_full[2];
   uint64_t d_full[2];
-  uint64_t acc_final;
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -94,7 +95,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
   BwdSmem* sm = reinterpret_cast<BwdSmem*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
 
-  const int warp = threadIdx.x >> 5;
+  const int warp = uniform_warp_index();
   const int lane = threadIdx.x & 31;
 
   const int bh = blockIdx.x / p.npair;
@@ -118,7 +119,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
       mbar_init(smem_u32(&sm->x_full[i]), 1);
       mbar_init(smem_u32(&sm->d_full[i]), 8);  // one arrival per compute warp
     }
-    mbar_init(smem_u32(&sm->acc_final), 1);
     sm->abort_flag = 0;
     mbar_fence_init();
   }
@@ -140,82 +140,100 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
 
   if (warp == 8) {
     // =========================== TMA producer ===========================
-    if (lane == 0 && n_steps > 0) {
-      mbar_expect_tx(smem_u32(&sm->stat_full), 2 * kBwdPairTile);
-      tma_load_4d(smem_u32(sm->stat0), &tm_stat0, smem_u32(&sm->stat_full), 0, pr * 128, h, b);
-      tma_load_4d(smem_u32(sm->stat1), &tm_stat1, smem_u32(&sm->stat_full), 0, pr * 128, h, b);
+    if (n_steps > 0) {
+      const bool leader = elect_one();
+      if (leader) {
+        mbar_expect_tx(smem_u32(&sm->stat_full), 2 * kBwdPairTile);
+        tma_load_4d(smem_u32(sm->stat0), &tm_stat0, smem_u32(&sm->stat_full), 0, pr * 128, h, b);
+        tma_load_4d(smem_u32(sm->stat1), &tm_stat1, smem_u32(&sm->stat_full), 0, pr * 128, h, b);
+      }
       for (int j = 0; j < n_steps; ++j) {
         const int s = j % kBwdStages;
         const uint32_t ph = (j / kBwdStages) & 1;
-        if (!mbar_wait(smem_u32(&sm->in_empty[s]), ph ^ 1, abort_flag)) {
+        const int blk = __ldg(ents + j) >> 2;
+        if (!mbar_wait_warp(smem_u32(&sm->in_empty[s]), ph ^ 1, abort_flag)) {
           bwd_give_up(sm, p.status, 1);
           break;
         }
-        const int blk = __ldg(ents + j) >> 2;
-        const uint32_t bar = smem_u32(&sm->in_full[s]);
-        mbar_expect_tx(bar, 2 * kBwdTile + (kDKDV ? 512u : 0u));
-        tma_load_4d(smem_u32(sm->str0[s]), &tm_str0, bar, 0, blk * 64, h, b);
-        tma_load_4d(smem_u32(sm->str1[s]), &tm_str1, bar, 0, blk * 64, h, b);
-        if constexpr (kDKDV) {
-          bulk_load_1d(smem_u32(sm->lse[s]), p.lse2 + vec_base + blk * 64, 256, bar);
-          bulk_load_1d(smem_u32(sm->delta[s]), p.delta + vec_base + blk * 64, 256, bar);
+        if (leader) {
+          const uint32_t bar = smem_u32(&sm->in_full[s]);
+          mbar_expect_tx(bar, 2 * kBwdTile + (kDKDV ? 512u : 0u));
+          tma_load_4d(smem_u32(sm->str0[s]), &tm_str0, bar, 0, blk * 64, h, b);
+          tma_load_4d(smem_u32(sm->str1[s]), &tm_str1, bar, 0, blk * 64, h, b);
+          if constexpr (kDKDV) {
+            bulk_load_1d(smem_u32(sm->lse[s]), p.lse2 + vec_base + blk * 64, 256, bar);
+            bulk_load_1d(smem_u32(sm->delta[s]), p.delta + vec_base + blk * 64, 256, bar);
+          }
         }
       }
     }
   } else if (warp == 9) {
-    // =========================== MMA issuer ===========================
-    if (lane == 0 && n_steps > 0) {
+    // =========================== S / dP issuer ===========================
+    if (n_steps > 0) {
       constexpr uint32_t idesc_x = umma_idesc(kBf16, 0, 0, 128, 64);
-      constexpr uint32_t idesc_acc = umma_idesc(kBf16, 0, 1, 128, 64);
+      const bool leader = elect_one();
       const uint64_t desc_a0 = smem_desc_sw128(smem_u32(sm->stat0), 16, 1024);
       const uint64_t desc_a1 = smem_desc_sw128(smem_u32(sm->stat1), 16, 1024);
-      auto issue_x = [&](int buf, int s) {
-        const uint64_t b0 = smem_desc_sw128(smem_u32(sm->str0[s]), 16, 1024);
-        const uint64_t b1 = smem_desc_sw128(smem_u32(sm->str1[s]), 16, 1024);
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          umma_ss(tmem + kTmX0 + 64 * buf, desc_a0 + 2 * kk, b0 + 2 * kk, idesc_x, kk > 0);
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          umma_ss(tmem + kTmX1 + 64 * buf, desc_a1 + 2 * kk, b1 + 2 * kk, idesc_x, kk > 0);
-        tc_commit(smem_u32(&sm->x_full[buf]));
-      };
-      bool ok = mbar_wait(smem_u32(&sm->stat_full), 0, abort_flag);
-      ok = ok && mbar_wait(smem_u32(&sm->in_full[0]), 0, abort_flag);
-      if (ok) {
-        tc_fence_after();
-        issue_x(0, 0);
-      }
+      const uint64_t desc_b0 = smem_desc_sw128(smem_u32(sm->str0[0]), 16, 1024);
+      const uint64_t desc_b1 = smem_desc_sw128(smem_u32(sm->str1[0]), 16, 1024);
+      bool ok = mbar_wait_warp(smem_u32(&sm->stat_full), 0, abort_flag);
       for (int j = 0; ok && j < n_steps; ++j) {
         const int s = j % kBwdStages;
         const int buf = j & 1;
-        if (j + 1 < n_steps) {
-          const int s1 = (j + 1) % kBwdStages;
-          ok = mbar_wait(smem_u32(&sm->in_full[s1]), ((j + 1) / kBwdStages) & 1, abort_flag);
+        ok = mbar_wait_warp(smem_u32(&sm->in_full[s]), (j / kBwdStages) & 1, abort_flag);
+        if (!ok) break;
+        if (j >= 2) {
+          // buffer `buf` still feeds the accumulating MMAs of step j-2 (P, dS live there too)
+          const int jp = j - 2;
+          ok = mbar_wait_warp(smem_u32(&sm->in_empty[jp % kBwdStages]), (jp / kBwdStages) & 1,
+                              abort_flag);
           if (!ok) break;
           tc_fence_after();
-          issue_x(buf ^ 1, s1);
         }
-        ok = mbar_wait(smem_u32(&sm->d_full[buf]), (j >> 1) & 1, abort_flag);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t acc_on = (j > 0) ? 1u : 0u;
-        if constexpr (kDKDV) {
-          const uint64_t bmn = smem_desc_sw128(smem_u32(sm->str1[s]), 8192, 1024);
+        if (leader) {
+          const uint64_t b0 = desc_b0 + static_cast<uint64_t>(s * (kBwdTile >> 4));
+          const uint64_t b1 = desc_b1 + static_cast<uint64_t>(s * (kBwdTile >> 4));
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            umma_ts(tmem + kTmAcc0, tmem + kTmP + 32 * buf + 8 * kk, bmn + 128 * kk, idesc_acc,
-                    acc_on | (kk > 0));
+            umma_ss(tmem + kTmX0 + 64 * buf, desc_a0 + 2 * kk, b0 + 2 * kk, idesc_x, kk > 0);
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            umma_ss(tmem + kTmX1 + 64 * buf, desc_a1 + 2 * kk, b1 + 2 * kk, idesc_x, kk > 0);
+          tc_commit(smem_u32(&sm->x_full[buf]));
         }
-        {
-          const uint64_t bmn = smem_desc_sw128(smem_u32(sm->str0[s]), 8192, 1024);
+      }
+      if (!ok) bwd_give_up(sm, p.status, 2);
+    }
+  } else if (warp == 10) {
+    // =========================== accumulating-MMA issuer ===========================
+    if (n_steps > 0) {
+      constexpr uint32_t idesc_acc = umma_idesc(kBf16, 0, 1, 128, 64);
+      const bool leader = elect_one();
+      const uint64_t desc_m0 = smem_desc_sw128(smem_u32(sm->str0[0]), 8192, 1024);
+      const uint64_t desc_m1 = smem_desc_sw128(smem_u32(sm->str1[0]), 8192, 1024);
+      bool ok = true;
+      for (int j = 0; ok && j < n_steps; ++j) {
+        const int s = j % kBwdStages;
+        const int buf = j & 1;
+        ok = mbar_wait_warp(smem_u32(&sm->d_full[buf]), (j >> 1) & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        if (leader) {
+          const uint32_t acc_on = (j > 0) ? 1u : 0u;
+          if constexpr (kDKDV) {
+            const uint64_t bmn = desc_m1 + static_cast<uint64_t>(s * (kBwdTile >> 4));
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk)
+              umma_ts(tmem + kTmAcc0, tmem + kTmP + 32 * buf + 8 * kk, bmn + 128 * kk, idesc_acc,
+                      acc_on | (kk > 0));
+          }
+          const uint64_t bmn = desc_m0 + static_cast<uint64_t>(s * (kBwdTile >> 4));
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
             umma_ts(tmem + kTmAcc1, tmem + kTmDS + 32 * buf + 8 * kk, bmn + 128 * kk, idesc_acc,
                     acc_on | (kk > 0));
+          tc_commit(smem_u32(&sm->in_empty[s]));  // stage free; X/P/dS buffer free; acc updated
         }
-        tc_commit(smem_u32(&sm->in_empty[s]));
-        if (j == n_steps - 1) tc_commit(smem_u32(&sm->acc_final));
       }
       if (!ok) bwd_give_up(sm, p.status, 2);
     }
@@ -299,7 +317,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
       bwd_give_up(sm, p.status, 3);
     } else {
       if (n_steps > 0) {
-        ok = mbar_wait_warp(smem_u32(&sm->acc_final), 0, abort_flag);
+        ok = mbar_wait_warp(smem_u32(&sm->in_empty[(n_steps - 1) % kBwdStages]),
+                            ((n_steps - 1) / kBwdStages) & 1, abort_flag);
         if (!ok) bwd_give_up(sm, p.status, 3);
       }
       if (ok) {
