@@ -155,6 +155,65 @@ def run_reference(args, rank, world):
     }))
 
 
+def extra_measurements(dev, peak_tf, peak_gbs):
+    """Other BASELINE.json configurations, kernels timed alone (CUDA events over back-to-back
+    launches, inputs resident, no L2 flush).  Reported next to the headline, never as `value`."""
+    from fa2_custom_mask import (attention_backward, attention_forward, build_tile_lists,
+                                 reduce_dense_mask)
+
+    def timed(fn, iters):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize(dev)
+        a = torch.cuda.Event(enable_timing=True)
+        b = torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            fn()
+        b.record()
+        torch.cuda.synchronize(dev)
+        return a.elapsed_time(b) / iters
+
+    def problem(B, H, N, p, dtype, seed, causal=False):
+        g = torch.Generator(device=dev).manual_seed(seed)
+        t = [torch.randn(B, H, N, HEAD_DIM, generator=g, device=dev).to(dtype) for _ in range(4)]
+        nb = N // 64
+        m = torch.rand(B, H, nb, nb, generator=g, device=dev) < p
+        if causal:
+            m = torch.tril(m, -1)
+        m |= torch.eye(nb, dtype=torch.bool, device=dev)
+        return t, m
+
+    out = {}
+    specs = [("fwd_kernel_test_shape_H8_N17536_p0.1_f16", 1, 8, 17536, 0.1, torch.float16, False, False),
+             ("fwd_N17536_dense_f16", 1, 1, 17536, 1.0, torch.float16, False, False),
+             ("fwd_cfg4_H32_N32000_p0.1_bf16", 1, 32, 32000, 0.1, torch.bfloat16, False, False),
+             ("fwd_bwd_cfg5_B2_H16_N16384_causal_p0.25_bf16", 2, 16, 16384, 0.25, torch.bfloat16, True, True)]
+    for name, B, H, N, p, dtype, causal, with_bwd in specs:
+        (q, k, v, do), m = problem(B, H, N, p, dtype, seed=len(name), causal=causal)
+        lists = build_tile_lists(m, want_q=with_bwd, want_k=with_bwd)
+        tiles = int(m.sum())
+        iters = 20 if tiles < 100000 else 5
+        ms = timed(lambda: attention_forward(q, k, v, lists, SM_SCALE), iters)
+        tf = tiles * FLOP_PER_TILE / (ms * 1e-3) / 1e12
+        rec = {"tiles": tiles, "fwd_ms": ms, "fwd_tflops": tf, "fwd_frac_of_measured_peak": tf / peak_tf}
+        if with_bwd:
+            o, lse2, _ = attention_forward(q, k, v, lists, SM_SCALE)
+            bms = timed(lambda: attention_backward(q, k, v, o, lse2, do, lists, SM_SCALE), iters)
+            btf = tiles * 10 * 64 * 64 * HEAD_DIM / (bms * 1e-3) / 1e12
+            rec.update({"bwd_ms": bms, "bwd_tflops": btf, "bwd_frac_of_measured_peak": btf / peak_tf})
+        out[name] = rec
+        del q, k, v, do, m, lists
+    for N in (17536, 32000):
+        from oracle import oracle
+        dense = oracle.expand_block_mask(oracle.make_block_mask(1, 1, N // 64, DENSITY, seed=N).to(dev))
+        ms = timed(lambda: reduce_dense_mask(dense), 20)
+        gbs = N * N / (ms * 1e-3) / 1e9
+        out[f"mask_reduce_N{N}"] = {"ms": ms, "GBps": gbs, "frac_of_measured_hbm": gbs / peak_gbs}
+        del dense
+    return out
+
+
 def run_ours(args, rank, world, local_rank):
     import torch.distributed as dist
     from fa2_custom_mask import (attention_forward, build_tile_lists, check_status,
@@ -260,6 +319,7 @@ def run_ours(args, rank, world, local_rank):
         (cq, ck, cv, dense), sample_tiles = cpu_sample(q, k, v, mask)
         cpu_reference_step(cq, ck, cv, dense, threads)
         times = [cpu_reference_step(cq, ck, cv, dense, threads)[0] for _ in range(7)]
+        line["extra"] = extra_measurements(dev, peak_tf, peak_gbs)
         line["cpu_baseline"] = {
             "value": sample_tiles * FLOP_PER_TILE / statistics.median(times) / 1e12,
             "unit": "TFLOP/s", "cores": threads, "kind": "port",

@@ -409,11 +409,8 @@ static int launch_bwd(const void* q, const void* k, const void* v, const void* d
 
   const size_t smem_bytes = sizeof(BwdSmem) + 1024;
   auto kern = dtype == BSA_BF16 ? attn_bwd_kernel<true, kDKDV> : attn_bwd_kernel<false, kDKDV>;
-  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           static_cast<int>(smem_bytes)) != cudaSuccess) {
-    (void)cudaGetLastError();
-    return BSA_ERR_CUDA;
-  }
+  if ((rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes)) != BSA_OK)
+    return rc;
   const dim3 grid(static_cast<unsigned>(B * H * npair));
   kern<<<grid, kBwdThreads, smem_bytes, static_cast<cudaStream_t>(stream)>>>(tm_a0, tm_a1, tm_b0,
                                                                              tm_b1, prm);

@@ -490,11 +490,8 @@ extern "C" int bsa_attn_fwd(const void* q, const int64_t q_strides[4], const voi
 
   const size_t smem_bytes = sizeof(FwdSmem) + 1024;
   auto kern = dtype == BSA_BF16 ? attn_fwd_kernel<true> : attn_fwd_kernel<false>;
-  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           static_cast<int>(smem_bytes)) != cudaSuccess) {
-    (void)cudaGetLastError();
-    return BSA_ERR_CUDA;
-  }
+  if ((rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes)) != BSA_OK)
+    return rc;
   const dim3 grid(static_cast<unsigned>(B * H * nb));
   kern<<<grid, kFwdThreads, smem_bytes, static_cast<cudaStream_t>(stream)>>>(tm_q, tm_k, tm_v, prm);
   if (cudaGetLastError() != cudaSuccess) return BSA_ERR_CUDA;

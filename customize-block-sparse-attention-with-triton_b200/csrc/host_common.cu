@@ -29,6 +29,33 @@ int check_qkv_operand(const void* p, const int64_t s[4]) {
   return BSA_OK;
 }
 
+int ensure_dynamic_smem(const void* kernel, size_t bytes) {
+  // a handful of kernels x devices: a small fixed table guarded by a spin flag is enough
+  struct Entry { const void* k; int dev; };
+  static Entry table[128];
+  static std::atomic<int> count{0};
+  static std::atomic_flag lock = ATOMIC_FLAG_INIT;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) return BSA_ERR_CUDA;
+  const int n = count.load(std::memory_order_acquire);
+  for (int i = 0; i < n; ++i)
+    if (table[i].k == kernel && table[i].dev == dev) return BSA_OK;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(bytes)) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return BSA_ERR_CUDA;
+  }
+  while (lock.test_and_set(std::memory_order_acquire)) {
+  }
+  const int m = count.load(std::memory_order_relaxed);
+  if (m < 128) {
+    table[m] = Entry{kernel, dev};
+    count.store(m + 1, std::memory_order_release);
+  }
+  lock.clear(std::memory_order_release);
+  return BSA_OK;
+}
+
 typedef CUresult (*encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                     const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                     const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,

@@ -27,4 +27,7 @@ int check_qkv_operand(const void* p, const int64_t s[4]);
 int make_qkv_tmap(CUtensorMap* out, const void* base, const int64_t s[4], int B, int H, int N,
                   int dtype, int box_rows);
 
+// Raises a kernel's dynamic shared-memory limit; done once per (kernel, device) and remembered.
+int ensure_dynamic_smem(const void* kernel, size_t bytes);
+
 }  // namespace bsa

@@ -278,6 +278,100 @@ __global__ void __launch_bounds__(kScanThreads) lists_scan_kernel(const ListArgs
   }
 }
 
+// Small masks, row lists only: one CTA stages the whole mask in shared memory with coalesced
+// independent loads, then counts, scans and fills from there in a single launch (the launch
+// latencies and dependent global reads of the general path cost more than the work itself here).
+constexpr int kSmallRows = 4096;
+constexpr int kSmallBytes = 160 * 1024;
+
+__global__ void __launch_bounds__(kScanThreads) lists_rows_small_kernel(const ListArgs a) {
+  extern __shared__ __align__(16) uint8_t s_mask[];  // rows * nb bytes, row-major
+  __shared__ int s_cnt[kSmallRows];
+  __shared__ int s_warp[33];
+  const int rows = a.B * a.H * a.nb;
+  const int total = rows * a.nb;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool contiguous = a.s3 == 1 && a.s2 == a.nb && (a.H == 1 || a.s1 == a.nb * a.nb) &&
+                          (a.B == 1 || a.s0 == static_cast<int64_t>(a.H) * a.nb * a.nb) &&
+                          (reinterpret_cast<uintptr_t>(a.block) & 15) == 0;
+  if (contiguous) {
+    const uint4* src = reinterpret_cast<const uint4*>(a.block);
+    uint4* dst = reinterpret_cast<uint4*>(s_mask);
+    for (int i = threadIdx.x; i < total / 16; i += kScanThreads) dst[i] = __ldg(src + i);
+    for (int i = (total / 16) * 16 + threadIdx.x; i < total; i += kScanThreads)
+      s_mask[i] = a.block[i];
+  } else {
+    for (int i = threadIdx.x; i < total; i += kScanThreads) {
+      const int r = i / a.nb, c = i - r * a.nb;
+      const int bh = r / a.nb, m = r - bh * a.nb;
+      s_mask[i] = a.block[(bh / a.H) * a.s0 + (bh % a.H) * a.s1 + m * a.s2 + c * a.s3];
+    }
+  }
+  __syncthreads();
+  for (int r = warp; r < rows; r += kScanThreads / 32) {
+    const uint8_t* row = s_mask + r * a.nb;
+    int count = 0;
+    for (int c0 = 0; c0 < a.nb; c0 += 32) {
+      const int c = c0 + lane;
+      const bool f = c < a.nb && row[c] != 0;
+      count += __popc(__ballot_sync(0xffffffffu, f));
+    }
+    if (lane == 0) s_cnt[r] = count;
+  }
+  __syncthreads();
+  constexpr int kPer = kSmallRows / kScanThreads;
+  const int i0 = threadIdx.x * kPer;
+  int sum = 0, nonempty = 0;
+#pragma unroll
+  for (int i = 0; i < kPer; ++i) {
+    const int c = (i0 + i < rows) ? s_cnt[i0 + i] : 0;
+    sum += c;
+    nonempty += c > 0;
+  }
+  int total_nnz = 0, gtotal = 0;
+  int run = block_exclusive_scan(sum, s_warp, &total_nnz);
+  int grun = block_exclusive_scan(nonempty, s_warp, &gtotal);
+#pragma unroll
+  for (int i = 0; i < kPer; ++i) {
+    const int r = i0 + i;
+    if (r < rows) {
+      const int c = s_cnt[r];
+      s_cnt[r] = run;
+      a.ptr[0][r] = run;
+      if (a.groups != nullptr && c > 0) {
+        int32_t* gr = a.groups + static_cast<int64_t>(grun) * 5;
+        const int bh = r / a.nb;
+        gr[0] = bh / a.H;
+        gr[1] = bh % a.H;
+        gr[2] = r % a.nb;
+        gr[3] = run;
+        gr[4] = c;
+        ++grun;
+      }
+      run += c;
+    }
+  }
+  if (threadIdx.x == 0) {
+    a.ptr[0][rows] = total_nnz;
+    a.meta[0] = total_nnz;
+    a.meta[1] = gtotal;
+  }
+  if (threadIdx.x >= 2 && threadIdx.x < 8) a.meta[threadIdx.x] = 0;
+  __syncthreads();
+  for (int r = warp; r < rows; r += kScanThreads / 32) {
+    const uint8_t* row = s_mask + r * a.nb;
+    int32_t* out = a.ent[0] + s_cnt[r];
+    int count = 0;
+    for (int c0 = 0; c0 < a.nb; c0 += 32) {
+      const int c = c0 + lane;
+      const bool f = c < a.nb && row[c] != 0;
+      const unsigned mk = __ballot_sync(0xffffffffu, f);
+      if (f) out[count + __popc(mk & ((1u << lane) - 1u))] = c;
+      count += __popc(mk);
+    }
+  }
+}
+
 }  // namespace bsa
 
 extern "C" int bsa_mask_reduce(const uint8_t* dense, const int64_t s[4], int B, int H, int N,
@@ -365,6 +459,15 @@ extern "C" int bsa_tile_lists_build(const uint8_t* block, const int64_t s[4], in
   if (blocks > 0x7fffffffLL) return BSA_ERR_TOO_LARGE;
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (row_ptr && !col_ptr && !qpair_ptr && !kpair_ptr && bh * nb <= kSmallRows &&
+      bh * nb * nb <= kSmallBytes) {
+    const size_t smem = static_cast<size_t>((bh * nb * nb + 15) & ~15LL);
+    int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(lists_rows_small_kernel),
+                                 kSmallBytes);
+    if (rc != BSA_OK) return rc;
+    lists_rows_small_kernel<<<1, kScanThreads, smem, st>>>(a);
+    return cudaGetLastError() == cudaSuccess ? BSA_OK : BSA_ERR_CUDA;
+  }
   if (cudaMemsetAsync(meta, 0, 8 * sizeof(int32_t), st) != cudaSuccess) return BSA_ERR_CUDA;
   const dim3 grid(static_cast<unsigned>(blocks), 4);
   lists_pass_kernel<false><<<grid, kListThreads, 0, st>>>(a);

@@ -89,7 +89,9 @@ def ptr(t):
 
 
 def stream_ptr(device=None):
-    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+    """The current stream of `device` as a cudaStream_t."""
+    idx = -1 if device is None or device.index is None else device.index
+    return ctypes.c_void_p(torch._C._cuda_getCurrentRawStream(idx))
 
 
 def dtype_code(dt: torch.dtype) -> int:

@@ -51,6 +51,24 @@ class TileLists:
         return (self.Hm if self.Bm > 1 else 0), (1 if self.Hm > 1 else 0)
 
 
+class _NoSwitch:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_SWITCH = _NoSwitch()
+
+
+def _on_device(dev):
+    """Context that makes `dev` current; free when it already is (the common case)."""
+    if torch.cuda.current_device() == dev.index:
+        return _NO_SWITCH
+    return torch.cuda.device(dev)
+
+
 def _as_bytes(mask: torch.Tensor) -> torch.Tensor:
     if mask.dtype == torch.bool:
         return mask.view(torch.uint8)
@@ -86,7 +104,7 @@ def reduce_dense_mask(dense: torch.Tensor, return_partial: bool = False):
     nb = N // BLOCK
     block = torch.empty((Bm, Hm, nb, nb), dtype=torch.uint8, device=d4.device)
     partial = torch.empty(1, dtype=torch.int32, device=d4.device) if return_partial else None
-    with torch.cuda.device(d4.device):
+    with _on_device(d4.device):
         _lib.check("bsa_mask_reduce", lib.bsa_mask_reduce(
             _lib.ptr(d4), _lib.strides4(d4), Bm, Hm, N, _lib.ptr(block), _lib.ptr(partial),
             _lib.stream_ptr(d4.device)))
@@ -107,27 +125,27 @@ def build_tile_lists(block_mask: torch.Tensor, want_q: bool = True, want_k: bool
     Bm, Hm, nb, nb2 = m4.shape
     if nb != nb2:
         raise ValueError("block mask must be square in its last two dims")
-    sizes = _lib.ListSizes()
-    _lib.check("bsa_tile_list_sizes", lib.bsa_tile_list_sizes(Bm, Hm, nb, ctypes.byref(sizes)))
     dev = m4.device
+    # worst-case sizes, the same numbers bsa_tile_list_sizes reports
+    rows, pairs = Bm * Hm * nb, Bm * Hm * ((nb + 1) // 2)
 
     def buf(n):
-        return torch.empty(int(n), dtype=torch.int32, device=dev)
+        return torch.empty(n, dtype=torch.int32, device=dev)
 
-    tl = TileLists(Bm=Bm, Hm=Hm, nb=nb, meta=buf(sizes.meta))
+    tl = TileLists(Bm=Bm, Hm=Hm, nb=nb, meta=buf(8))
     want_csr = want_csr or want_groups
     want_csc = want_csc or want_groups
     if want_q:
-        tl.qpair_ptr, tl.qpair_ent = buf(sizes.qpair_ptr), buf(sizes.qpair_ent)
+        tl.qpair_ptr, tl.qpair_ent = buf(pairs + 1), buf(pairs * nb)
     if want_k:
-        tl.kpair_ptr, tl.kpair_ent = buf(sizes.kpair_ptr), buf(sizes.kpair_ent)
+        tl.kpair_ptr, tl.kpair_ent = buf(pairs + 1), buf(pairs * nb)
     if want_csr:
-        tl.row_ptr, tl.col_idx = buf(sizes.row_ptr), buf(sizes.col_idx)
+        tl.row_ptr, tl.col_idx = buf(rows + 1), buf(rows * nb)
     if want_csc:
-        tl.col_ptr, tl.row_idx = buf(sizes.col_ptr), buf(sizes.row_idx)
+        tl.col_ptr, tl.row_idx = buf(rows + 1), buf(rows * nb)
     if want_groups:
-        tl.groups = buf(sizes.groups)
-    with torch.cuda.device(dev):
+        tl.groups = buf(rows * 5)
+    with _on_device(dev):
         _lib.check("bsa_tile_lists_build", lib.bsa_tile_lists_build(
             _lib.ptr(m4), _lib.strides4(m4), Bm, Hm, nb,
             _lib.ptr(tl.row_ptr), _lib.ptr(tl.col_idx), _lib.ptr(tl.col_ptr), _lib.ptr(tl.row_idx),
@@ -184,7 +202,7 @@ def new_status_word(device) -> torch.Tensor:
 def check_status(status: torch.Tensor):
     """Synchronises the current stream and raises if a kernel's bounded wait gave up."""
     lib = _lib.load()
-    with torch.cuda.device(status.device):
+    with _on_device(status.device):
         _lib.check("bsa_check_status", lib.bsa_check_status(
             _lib.ptr(status), _lib.stream_ptr(status.device)))
 
@@ -200,7 +218,7 @@ def attention_forward(q, k, v, lists: TileLists, sm_scale: float, want_rowmax: b
     lse2 = torch.empty((B, H, N), dtype=torch.float32, device=q.device)
     rowmax = torch.empty_like(lse2) if want_rowmax else None
     sb, sh = lists.list_strides(B, H)
-    with torch.cuda.device(q.device):
+    with _on_device(q.device):
         _lib.check("bsa_attn_fwd", lib.bsa_attn_fwd(
             _lib.ptr(q), _lib.strides4(q), _lib.ptr(k), _lib.strides4(k), _lib.ptr(v),
             _lib.strides4(v), _lib.ptr(o), _lib.strides4(o), _lib.ptr(lse2), _lib.ptr(rowmax),
@@ -223,7 +241,7 @@ def attention_backward(q, k, v, o, lse2, dout, lists: TileLists, sm_scale: float
     sb, sh = lists.list_strides(B, H)
     code = _lib.dtype_code(q.dtype)
     st = _lib.strides4(q)
-    with torch.cuda.device(q.device):
+    with _on_device(q.device):
         stream = _lib.stream_ptr(q.device)
         _lib.check("bsa_attn_bwd_delta", lib.bsa_attn_bwd_delta(
             _lib.ptr(o), _lib.ptr(dout), st, _lib.ptr(delta), code, B, H, N, D, stream))
