@@ -7,8 +7,8 @@ Bernoulli(0.1) blocks plus the diagonal, q,k,v ~ N(0,1), sm_scale = 1/8 — synt
 standing in for the reference's kernel-test.py inputs.  At N GPUs every rank runs its own head of
 that shape (weak scaling, no collective on the data path).
 
-One step = the whole public path on resident inputs: block mask -> tile lists (3 kernels) -> forward
-kernel.  `value` is active-tile TFLOP/s = listed tiles * 4*64*64*64 FLOP / step time; L2 is flushed
+One step = the whole forward path on resident inputs: one launch of the forward kernel, which
+lists the kept key blocks of each mask row itself (no separate list kernel).  `value` is active-tile TFLOP/s = listed tiles * 4*64*64*64 FLOP / step time; L2 is flushed
 (untimed) between steps because the inputs are smaller than L2.  `roofline` times the forward
 kernel alone with its own CUDA events inside the same steps.  `e2e` runs the public op
 flash_attention_custom_mask from pinned host buffers (H2D of q,k,v,mask and D2H of O inside the
@@ -36,8 +36,8 @@ FLOP_PER_TILE = 4 * 64 * 64 * HEAD_DIM
 WORKLOAD = "fwd fp16 B=1,H=1,N=17536,D=64, 64x64 block mask Bernoulli(0.1)+diagonal (per GPU)"
 METRIC = "fwd_active_tile_tflops_N17536_d64_p0.1"
 # DRAM bytes (read + write) of one forward-kernel launch on this workload from the ncu capture
-# summarised in profiles/attn_fwd_kernel_N17536_p0.1.md; None until a capture exists.
-FWD_KERNEL_DRAM_BYTES = None
+# summarised in profiles/attn_fwd_kernel_N17536_p0.1.md.
+FWD_KERNEL_DRAM_BYTES = 6_799_104
 
 
 def measured_peaks():
@@ -216,7 +216,7 @@ def extra_measurements(dev, peak_tf, peak_gbs):
 
 def run_ours(args, rank, world, local_rank):
     import torch.distributed as dist
-    from fa2_custom_mask import (attention_forward, build_tile_lists, check_status,
+    from fa2_custom_mask import (attention_forward_masked, check_status,
                                  flash_attention_custom_mask, new_status_word)
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
@@ -225,11 +225,10 @@ def run_ours(args, rank, world, local_rank):
     status = new_status_word(dev)
 
     def step():
-        lists = build_tile_lists(mask, want_q=False, want_k=False)
         a = torch.cuda.Event(enable_timing=True)
         b = torch.cuda.Event(enable_timing=True)
         a.record()
-        out = attention_forward(q, k, v, lists, SM_SCALE, status=status)
+        out = attention_forward_masked(q, k, v, mask, SM_SCALE, status=status)
         b.record()
         return out, a, b
 
@@ -301,7 +300,7 @@ def run_ours(args, rank, world, local_rank):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_ms / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
         "data": "synthetic",
-        "config": {"workload": WORKLOAD, "step": "block mask -> tile lists -> forward kernel",
+        "config": {"workload": WORKLOAD, "step": "forward kernel with in-kernel tile listing from the block mask",
                    "tiles_per_gpu": total_tiles / world, "sharding": "one head per GPU",
                    "l2": "flushed between steps (256 MiB write, untimed)"},
         "fwd_kernel_ms": kern_ms / args.steps,
@@ -311,7 +310,7 @@ def run_ours(args, rank, world, local_rank):
         "e2e": {"value": total_tiles * FLOP_PER_TILE * args.steps / (e2e_ms * 1e-3) / 1e12,
                 "unit": "TFLOP/s", "ms_per_step": e2e_ms / args.steps,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-        "gpu_launches": 4 * args.steps,
+        "gpu_launches": args.steps,
         "clocks": clocks,
     }
     if world == 1:

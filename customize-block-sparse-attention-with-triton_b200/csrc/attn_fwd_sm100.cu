@@ -41,6 +41,7 @@ constexpr uint32_t kTileBytes = 64 * 64 * 2;       // one Q, K or V tile
 constexpr uint32_t kFwdTmemCols = 512;
 constexpr uint32_t kTmemO = 256;                   // O[t][g] at 256 + 64 (2 t + g); slot r at 128 r
 constexpr float kRescaleThreshold = 8.0f;
+constexpr int kFwdMaxTiles = 2048;                 // key blocks per row that a CTA can list (N <= 131072)
 
 struct FwdSmem {
   union {
@@ -51,6 +52,8 @@ struct FwdSmem {
     } t;
     float part[4][64][65];                      // epilogue: weighted partial O, [col][row] + pad
   } u;
+  int32_t cols[kFwdMaxTiles];  // this query block's key-block list
+  int wsum[kFwdThreads / 32];  // list building: kept blocks seen by each warp
   float mref[2][128];      // epilogue: reference maximum per key group and lane
   float lsum[2][128];      // epilogue: row sums
   float mtrue[2][128];     // epilogue: true running maxima
@@ -64,8 +67,10 @@ struct FwdSmem {
 };
 
 struct FwdParams {
-  const int32_t* row_ptr;
+  const int32_t* row_ptr;   // list mode: CSR row lists
   const int32_t* col_idx;
+  const uint8_t* block;     // mask mode (block != nullptr): the CTA lists its own mask row
+  int64_t ms0, ms1, ms2, ms3;
   void* o;
   int64_t o_sb, o_sh, o_sn;
   float* lse2;
@@ -137,11 +142,38 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int mb = p.nb - 1 - (blockIdx.x % p.nb);  // late (long, if causal) rows first
   const int b = bh / p.H;
   const int h = bh % p.H;
-  const int64_t li = static_cast<int64_t>(b * p.list_b_stride + h * p.list_h_stride) * p.nb + mb;
-  const int beg = __ldg(p.row_ptr + li);
-  const int n_tiles = __ldg(p.row_ptr + li + 1) - beg;
+  // ---- this query block's key-block list, into shared memory ----
+  int n_tiles = 0;
+  if (p.block != nullptr) {
+    // mask mode: ordered compaction of the kept blocks of mask row (b, h, mb); list_*_stride are
+    // 0 for a broadcast axis and 1 otherwise here
+    const uint8_t* mrow = p.block + (b * p.list_b_stride) * p.ms0 + (h * p.list_h_stride) * p.ms1 +
+                          static_cast<int64_t>(mb) * p.ms2;
+    for (int c0 = 0; c0 < p.nb; c0 += kFwdThreads) {
+      const int c = c0 + static_cast<int>(threadIdx.x);
+      const bool keep = c < p.nb && mrow[c * p.ms3] != 0;
+      const unsigned bal = __ballot_sync(0xffffffffu, keep);
+      if (lane == 0) sm->wsum[warp] = __popc(bal);
+      __syncthreads();
+      int before = 0, total = 0;
+#pragma unroll
+      for (int w = 0; w < kFwdThreads / 32; ++w) {
+        const int cnt = sm->wsum[w];
+        before += w < warp ? cnt : 0;
+        total += cnt;
+      }
+      if (keep) sm->cols[n_tiles + before + __popc(bal & ((1u << lane) - 1u))] = c;
+      n_tiles += total;
+      __syncthreads();
+    }
+  } else {
+    const int64_t li = static_cast<int64_t>(b * p.list_b_stride + h * p.list_h_stride) * p.nb + mb;
+    const int beg = __ldg(p.row_ptr + li);
+    n_tiles = __ldg(p.row_ptr + li + 1) - beg;
+    for (int i = threadIdx.x; i < n_tiles; i += kFwdThreads) sm->cols[i] = __ldg(p.col_idx + beg + i);
+  }
   const int n_super = (n_tiles + 1) >> 1;
-  const int32_t* cols = p.col_idx + beg;
+  const int32_t* cols = sm->cols;  // visible to every role after the set-up barrier
 
   // ---- set-up ----
   if (threadIdx.x == 0) {
@@ -192,8 +224,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       for (int u = 0; u < n_super; ++u) {
         const int ss = u % kFwdStages;
         const int nt = min(2, n_tiles - 2 * u);
-        const int n0 = __ldg(cols + 2 * u);
-        const int n1 = nt == 2 ? __ldg(cols + 2 * u + 1) : 0;
+        const int n0 = cols[2 * u];
+        const int n1 = nt == 2 ? cols[2 * u + 1] : 0;
         if (!mbar_wait_warp(smem_u32(&sm->kv_empty[ss]), ((u / kFwdStages) & 1) ^ 1, abort_flag)) {
           fwd_give_up(sm, p.status, kFailProducer);
           break;
@@ -445,16 +477,18 @@ extern "C" int bsa_debug_copy_trace(long long* host) {
 }
 #endif
 
-extern "C" int bsa_attn_fwd(const void* q, const int64_t q_strides[4], const void* k,
-                            const int64_t k_strides[4], const void* v, const int64_t v_strides[4],
-                            void* o, const int64_t o_strides[4], float* lse2, float* rowmax,
-                            const int32_t* row_ptr, const int32_t* col_idx, int list_b_stride,
-                            int list_h_stride, float sm_scale, int dtype, int B, int H, int N,
-                            int D, int32_t* status, void* stream) {
-  using namespace bsa;
+namespace bsa {
+
+static int launch_fwd(const void* q, const int64_t q_strides[4], const void* k,
+                      const int64_t k_strides[4], const void* v, const int64_t v_strides[4], void* o,
+                      const int64_t o_strides[4], float* lse2, float* rowmax,
+                      const int32_t* row_ptr, const int32_t* col_idx, const uint8_t* block,
+                      const int64_t* block_strides, int list_b_stride, int list_h_stride,
+                      float sm_scale, int dtype, int B, int H, int N, int D, int32_t* status,
+                      void* stream) {
   if (B <= 0 || H <= 0 || N <= 0 || (N % kBlock) != 0 || D != kHeadDim) return BSA_ERR_BAD_SHAPE;
   if (dtype != BSA_F16 && dtype != BSA_BF16) return BSA_ERR_BAD_DTYPE;
-  if (!lse2 || !row_ptr || !col_idx) return BSA_ERR_BAD_POINTER;
+  if (!lse2 || (block == nullptr && (!row_ptr || !col_idx))) return BSA_ERR_BAD_POINTER;
   int rc;
   if ((rc = check_qkv_operand(q, q_strides)) != BSA_OK) return rc;
   if ((rc = check_qkv_operand(k, k_strides)) != BSA_OK) return rc;
@@ -463,6 +497,7 @@ extern "C" int bsa_attn_fwd(const void* q, const int64_t q_strides[4], const voi
   if ((rc = check_device_sm100()) != BSA_OK) return rc;
 
   const int nb = N / kBlock;
+  if (nb > kFwdMaxTiles) return BSA_ERR_TOO_LARGE;
   if (static_cast<int64_t>(B) * H * nb > 0x7fffffffLL) return BSA_ERR_TOO_LARGE;
 
   CUtensorMap tm_q, tm_k, tm_v;
@@ -473,6 +508,11 @@ extern "C" int bsa_attn_fwd(const void* q, const int64_t q_strides[4], const voi
   FwdParams prm;
   prm.row_ptr = row_ptr;
   prm.col_idx = col_idx;
+  prm.block = block;
+  prm.ms0 = block ? block_strides[0] : 0;
+  prm.ms1 = block ? block_strides[1] : 0;
+  prm.ms2 = block ? block_strides[2] : 0;
+  prm.ms3 = block ? block_strides[3] : 0;
   prm.o = o;
   prm.o_sb = o_strides[0];
   prm.o_sh = o_strides[1];
@@ -496,4 +536,34 @@ extern "C" int bsa_attn_fwd(const void* q, const int64_t q_strides[4], const voi
   kern<<<grid, kFwdThreads, smem_bytes, static_cast<cudaStream_t>(stream)>>>(tm_q, tm_k, tm_v, prm);
   if (cudaGetLastError() != cudaSuccess) return BSA_ERR_CUDA;
   return BSA_OK;
+}
+
+}  // namespace bsa
+
+extern "C" int bsa_attn_fwd(const void* q, const int64_t q_strides[4], const void* k,
+                            const int64_t k_strides[4], const void* v, const int64_t v_strides[4],
+                            void* o, const int64_t o_strides[4], float* lse2, float* rowmax,
+                            const int32_t* row_ptr, const int32_t* col_idx, int list_b_stride,
+                            int list_h_stride, float sm_scale, int dtype, int B, int H, int N,
+                            int D, int32_t* status, void* stream) {
+  if (!row_ptr || !col_idx) return BSA_ERR_BAD_POINTER;
+  return bsa::launch_fwd(q, q_strides, k, k_strides, v, v_strides, o, o_strides, lse2, rowmax,
+                         row_ptr, col_idx, nullptr, nullptr, list_b_stride, list_h_stride, sm_scale,
+                         dtype, B, H, N, D, status, stream);
+}
+
+extern "C" int bsa_attn_fwd_block_mask(const void* q, const int64_t q_strides[4], const void* k,
+                                       const int64_t k_strides[4], const void* v,
+                                       const int64_t v_strides[4], void* o,
+                                       const int64_t o_strides[4], float* lse2, float* rowmax,
+                                       const uint8_t* block, const int64_t block_strides[4],
+                                       int Bm, int Hm, float sm_scale, int dtype, int B, int H,
+                                       int N, int D, int32_t* status, void* stream) {
+  if (!block || !block_strides) return BSA_ERR_BAD_POINTER;
+  if ((Bm != 1 && Bm != B) || (Hm != 1 && Hm != H)) return BSA_ERR_BAD_SHAPE;
+  for (int i = 0; i < 4; ++i)
+    if (block_strides[i] < 0) return BSA_ERR_BAD_STRIDE;
+  return bsa::launch_fwd(q, q_strides, k, k_strides, v, v_strides, o, o_strides, lse2, rowmax,
+                         nullptr, nullptr, block, block_strides, Bm > 1 ? 1 : 0, Hm > 1 ? 1 : 0,
+                         sm_scale, dtype, B, H, N, D, status, stream);
 }

@@ -4,6 +4,7 @@ from .fa2_custom_mask import (  # noqa: F401
     TileLists,
     attention_backward,
     attention_forward,
+    attention_forward_masked,
     build_groups_from_block_mask,
     build_tile_lists,
     check_status,

@@ -178,7 +178,8 @@ def _tma_ready(t: torch.Tensor) -> torch.Tensor:
     return t if ok else t.contiguous()
 
 
-def _lists_for_mask(mask, B, H, N, device, need_k):
+def _block_mask_for(mask, B, H, N, device):
+    """The op's `mask` argument as a block mask [..,nb,nb] on `device`."""
     nb = N // BLOCK
     if mask is None:
         mask = torch.ones((1, 1, nb, nb), dtype=torch.bool, device=device)
@@ -191,7 +192,10 @@ def _lists_for_mask(mask, B, H, N, device, need_k):
     else:
         raise ValueError(
             f"mask must be a block mask [..,{nb},{nb}] or a dense mask [..,{N},{N}], got {tuple(mask.shape)}")
-    return build_tile_lists(block, want_csr=True, want_q=need_k, want_k=need_k)
+    m4 = _as_4d(block)
+    if m4.shape[0] not in (1, B) or m4.shape[1] not in (1, H):
+        raise ValueError(f"mask leading dims {tuple(m4.shape[:2])} do not broadcast to ({B},{H})")
+    return block
 
 
 def new_status_word(device) -> torch.Tensor:
@@ -223,6 +227,26 @@ def attention_forward(q, k, v, lists: TileLists, sm_scale: float, want_rowmax: b
             _lib.ptr(q), _lib.strides4(q), _lib.ptr(k), _lib.strides4(k), _lib.ptr(v),
             _lib.strides4(v), _lib.ptr(o), _lib.strides4(o), _lib.ptr(lse2), _lib.ptr(rowmax),
             _lib.ptr(lists.row_ptr), _lib.ptr(lists.col_idx), sb, sh, float(sm_scale),
+            _lib.dtype_code(q.dtype), B, H, N, D, _lib.ptr(status), _lib.stream_ptr(q.device)))
+    return o, lse2, rowmax
+
+
+def attention_forward_masked(q, k, v, block_mask: torch.Tensor, sm_scale: float,
+                             want_rowmax: bool = False, status: Optional[torch.Tensor] = None):
+    """Forward straight from a block mask [..,nb,nb]: every CTA lists its own mask row, no tile
+    lists are built.  Returns (o, lse2, rowmax|None) like attention_forward."""
+    lib = _lib.load()
+    B, H, N, D = q.shape
+    m4 = _as_4d(_as_bytes(block_mask))
+    q, k, v = _tma_ready(q), _tma_ready(k), _tma_ready(v)
+    o = torch.empty((B, H, N, D), dtype=q.dtype, device=q.device)
+    lse2 = torch.empty((B, H, N), dtype=torch.float32, device=q.device)
+    rowmax = torch.empty_like(lse2) if want_rowmax else None
+    with _on_device(q.device):
+        _lib.check("bsa_attn_fwd_block_mask", lib.bsa_attn_fwd_block_mask(
+            _lib.ptr(q), _lib.strides4(q), _lib.ptr(k), _lib.strides4(k), _lib.ptr(v),
+            _lib.strides4(v), _lib.ptr(o), _lib.strides4(o), _lib.ptr(lse2), _lib.ptr(rowmax),
+            _lib.ptr(m4), _lib.strides4(m4), m4.shape[0], m4.shape[1], float(sm_scale),
             _lib.dtype_code(q.dtype), B, H, N, D, _lib.ptr(status), _lib.stream_ptr(q.device)))
     return o, lse2, rowmax
 
@@ -275,12 +299,14 @@ class _attention(torch.autograd.Function):
             raise RuntimeError("flash_attention_custom_mask needs CUDA tensors; there is no CPU path")
         if not (q.dtype == k.dtype == v.dtype) or q.dtype not in (torch.float16, torch.bfloat16):
             raise TypeError("q, k, v must all be float16 or all bfloat16")
-        need_grad = any(ctx.needs_input_grad[:3])
-        lists = _lists_for_mask(mask, B, H, N, q.device, need_k=need_grad)
-        o, lse2, _ = attention_forward(q, k, v, lists, sm_scale)
-        ctx.save_for_backward(q, k, v, o, lse2, lists.qpair_ptr, lists.qpair_ent,
-                              lists.kpair_ptr, lists.kpair_ent)  # row lists are forward-only
-        ctx.lists_shape = (lists.Bm, lists.Hm, lists.nb)
+        block = _block_mask_for(mask, B, H, N, q.device)
+        # the forward lists each mask row inside the kernel; only the backward needs pair lists
+        o, lse2, _ = attention_forward_masked(q, k, v, block, sm_scale)
+        if any(ctx.needs_input_grad[:3]):
+            lists = build_tile_lists(block, want_csr=False, want_q=True, want_k=True)
+            ctx.save_for_backward(q, k, v, o, lse2, lists.qpair_ptr, lists.qpair_ent,
+                                  lists.kpair_ptr, lists.kpair_ent)
+            ctx.lists_shape = (lists.Bm, lists.Hm, lists.nb)
         ctx.sm_scale = sm_scale
         ctx.HEAD_DIM = D
         ctx.USE_MASK = mask is not None

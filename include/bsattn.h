@@ -124,6 +124,22 @@ int bsa_attn_fwd(const void* q, const int64_t q_strides[4], const void* k,
                  int dtype, int B, int H, int N, int D, int32_t* status, void* stream);
 
 /*
+ * The same forward with the list building fused in: every CTA lists the kept key blocks of its own
+ * mask row, so no tile lists (and no list kernel) are needed for a forward-only call.  Replaces
+ * build_groups_from_block_mask + the _attn_fwd launch together
+ * (fa2_custom_mask/fa2_custom_mask.py:48 and :77-87).
+ *   block : bytes, logical [Bm,Hm,nb,nb] with element strides block_strides[4]; Bm is 1 or B, Hm is
+ *           1 or H.  Other arguments and results as in bsa_attn_fwd.  Both forward entry points
+ *           need N <= 131072.
+ */
+int bsa_attn_fwd_block_mask(const void* q, const int64_t q_strides[4], const void* k,
+                            const int64_t k_strides[4], const void* v, const int64_t v_strides[4],
+                            void* o, const int64_t o_strides[4], float* lse2, float* rowmax,
+                            const uint8_t* block, const int64_t block_strides[4], int Bm, int Hm,
+                            float sm_scale, int dtype, int B, int H, int N, int D, int32_t* status,
+                            void* stream);
+
+/*
  * delta[b,h,i] = sum_d o[b,h,i,d] * do[b,h,i,d] in fp32; replaces _attn_bwd_preprocess
  * (fa2_custom_mask/fa2_bwd.py:5-19, launch fa2_custom_mask/fa2_custom_mask.py:114-121).
  * o and do share o_strides; delta is contiguous [B,H,N].

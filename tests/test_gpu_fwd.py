@@ -15,8 +15,14 @@ LSE_TOL = 2e-3
 DT = {0: torch.float32, 1: torch.float16, 2: torch.bfloat16}
 
 
-def _run(q, k, v, mask, sm_scale, want_rowmax=True):
-    from fa2_custom_mask import attention_forward, build_tile_lists
+def _run(q, k, v, mask, sm_scale, want_rowmax=True, mode="lists"):
+    """mode "lists": bsa_tile_lists_build + bsa_attn_fwd; mode "mask": bsa_attn_fwd_block_mask."""
+    from fa2_custom_mask import attention_forward, attention_forward_masked, build_tile_lists
+    if mode == "mask":
+        o, lse2, rowmax = attention_forward_masked(q.cuda(), k.cuda(), v.cuda(), mask.cuda(),
+                                                   sm_scale, want_rowmax)
+        torch.cuda.synchronize()
+        return o.float().cpu(), lse2.cpu(), (rowmax.cpu() if rowmax is not None else None)
     lists = build_tile_lists(mask.cuda(), want_q=False, want_k=False)
     o, lse2, rowmax = attention_forward(q.cuda(), k.cuda(), v.cuda(), lists, sm_scale, want_rowmax)
     torch.cuda.synchronize()
@@ -43,7 +49,9 @@ def test_golden_vectors_of_the_reference_kernel(lib, golden):
         q, k, v = (torch.from_numpy(g[case + "/" + n]).to(run_dt) for n in "qkv")
         mask = torch.from_numpy(g[case + "/mask"])
         sm_scale = float(g[case + "/sm_scale"][0])
-        o, lse2, rowmax = _run(q, k, v, mask, sm_scale)
+        o, lse2, rowmax = _run(q, k, v, mask, sm_scale, mode="mask")
+        o_l, lse2_l, rowmax_l = _run(q, k, v, mask, sm_scale, mode="lists")
+        assert torch.equal(o, o_l) and torch.equal(lse2, lse2_l) and torch.equal(rowmax, rowmax_l)
         o_ref = torch.from_numpy(g[case + "/o"])
         m_ref = torch.from_numpy(g[case + "/M"])
         written = ~torch.isnan(m_ref)
@@ -54,6 +62,7 @@ def test_golden_vectors_of_the_reference_kernel(lib, golden):
         assert (o[~written] == 0).all() and (lse2[~written] == -math.inf).all()
 
 
+@pytest.mark.parametrize("mode", ["lists", "mask"])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("B,H,N,p,diag,causal", [
     (1, 1, 64, 1.0, True, False),       # one tile, odd block count
@@ -64,10 +73,10 @@ def test_golden_vectors_of_the_reference_kernel(lib, golden):
     (1, 2, 1024, 1.0, True, False),     # dense
     (2, 2, 512, 0.25, True, True),      # block-causal sparse
 ])
-def test_forward_matches_oracle(lib, dtype, B, H, N, p, diag, causal):
+def test_forward_matches_oracle(lib, mode, dtype, B, H, N, p, diag, causal):
     q, k, v = oracle.make_qkv(B, H, N, 64, seed=N + B, dtype=dtype)
     mask = oracle.make_block_mask(B, H, N // 64, p, seed=N, diagonal=diag, causal=causal)
-    o, lse2, _ = _run(q, k, v, mask, 0.125)
+    o, lse2, _ = _run(q, k, v, mask, 0.125, mode=mode)
     _compare(q, k, v, mask, 0.125, o, lse2)
 
 
@@ -113,6 +122,22 @@ def test_public_op_block_and_dense_masks(lib):
     qt = q.transpose(1, 2).contiguous().transpose(1, 2)
     o4 = flash_attention_custom_mask(qt, k, v, mask.cuda(), 0.125)
     assert torch.equal(o4, o1)
+
+
+def test_mask_mode_strided_and_wide_masks(lib):
+    # a mask row wider than one pass of the in-kernel lister (nb > 352) and a non-contiguous mask
+    q, k, v = oracle.make_qkv(1, 1, 64 * 400, 64, seed=31, dtype=torch.float16)
+    wide = oracle.make_block_mask(1, 1, 400, 0.02, seed=31)
+    a = _run(q, k, v, wide, 0.125, mode="mask")
+    b = _run(q, k, v, wide, 0.125, mode="lists")
+    assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+    from fa2_custom_mask import attention_forward_masked
+    q, k, v = (t.cuda() for t in oracle.make_qkv(1, 2, 512, 64, seed=32, dtype=torch.bfloat16))
+    big = oracle.make_block_mask(1, 2, 20, 0.4, seed=32).cuda()
+    sl = big[:, :, 3:11, 5:13]                      # strided view, 8 x 8 blocks
+    o, lse2, _ = attention_forward_masked(q, k, v, sl, 0.125)
+    o_ref, _ = oracle.attn_forward(q.cpu(), k.cpu(), v.cpu(), sl.cpu(), 0.125)
+    assert (o.float().cpu() - o_ref).abs().max() <= O_TOL
 
 
 def test_run_to_run_determinism(lib):
