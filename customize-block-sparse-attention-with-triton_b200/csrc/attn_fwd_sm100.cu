@@ -9,12 +9,13 @@
 //   warp 8   : TMA producer — Q (twice) once, then only the listed K/V tiles into a 4-deep ring of
 //              superstages (2 K tiles + 2 V tiles each)
 //   warp 9   : S issuer and TMEM owner — S_u = [Q;Q] [K_a;K_b]^T as four M=128,N=128,K=16 MMAs into
-//              one of 2 TMEM slots (lanes 0..63 use columns 0..63, lanes 64..127 columns 64..127;
+//              one of 3 TMEM slots (lanes 0..63 use columns 0..63, lanes 64..127 columns 64..127;
 //              an N=128 instruction occupies the tensor pipe no longer than an N=64 one)
-//   warp 10  : P V issuer — O[t][g] += P_t[:, keys of group g] V_t[keys of group g] for tile t in
-//              {a, b} and key group g in {0, 1}: four accumulators, P read from TMEM, V an MN-major
-//              smem operand; only lanes 0..63 of the tile-a accumulators and lanes 64..127 of the
-//              tile-b ones are meaningful.  S and P V are issued by different warps so that
+//   warp 10  : P V issuer — O[g] += P_a[:, keys of group g] V_a[..] + P_b[:, keys of group g] V_b[..]
+//              for key group g in {0, 1}: two accumulators, P read from TMEM, V an MN-major smem
+//              operand.  Lanes 64..127 store zeros where tile a's P lives and lanes 0..63 where
+//              tile b's does, so row r of an accumulator only ever sums tile-a products and row
+//              r + 64 only tile-b products.  S and P V are issued by different warps so that
 //              neither waits behind the other's barrier round trips.
 //   warps 0..7 : online softmax.  Warp w works on TMEM lane quarter w % 4 and on key group
 //              g = w / 4 (keys [32 g, +32) of its tile): tcgen05.ld of S, exp2, P written back over
@@ -35,11 +36,11 @@
 namespace bsa {
 
 constexpr int kFwdStages = 4;   // superstages (2 K + 2 V tiles) in flight in shared memory
-constexpr int kFwdSlots = 2;    // S/P supertiles (128 TMEM columns) in flight
+constexpr int kFwdSlots = 3;    // S/P supertiles (128 TMEM columns) in flight
 constexpr int kFwdThreads = 352;
 constexpr uint32_t kTileBytes = 64 * 64 * 2;       // one Q, K or V tile
 constexpr uint32_t kFwdTmemCols = 512;
-constexpr uint32_t kTmemO = 256;                   // O[t][g] at 256 + 64 (2 t + g); slot r at 128 r
+constexpr uint32_t kTmemO = 384;                   // O[g] at 384 + 64 g; slot r at 128 r
 constexpr float kRescaleThreshold = 8.0f;
 constexpr int kFwdMaxTiles = 2048;                 // key blocks per row that a CTA can list (N <= 131072)
 
@@ -50,7 +51,7 @@ struct FwdSmem {
       uint8_t k[kFwdStages][2][kTileBytes];
       uint8_t v[kFwdStages][2][kTileBytes];
     } t;
-    float part[4][64][65];                      // epilogue: weighted partial O, [col][row] + pad
+    float xfer[64][65];                         // epilogue: lanes 64..127 hand over, [col][row]
   } u;
   int32_t cols[kFwdMaxTiles];  // this query block's key-block list
   int wsum[kFwdThreads / 32];  // list building: kept blocks seen by each warp
@@ -142,6 +143,40 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int mb = p.nb - 1 - (blockIdx.x % p.nb);  // late (long, if causal) rows first
   const int b = bh / p.H;
   const int h = bh % p.H;
+  if (threadIdx.x == 0) BSA_TR(6, 0, 0);
+  // ---- set-up; the Q load needs no list, so it starts first and overlaps the list building ----
+  if (warp == 8 && lane == 0) {
+#ifdef BSA_TRACE
+    unsigned smid;
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+    BSA_TR_CTA(0, global_timer_ns());
+    BSA_TR_CTA(2, smid);
+#endif
+    mbar_init(smem_u32(&sm->q_full), 1);
+    for (int s = 0; s < kFwdStages; ++s) {
+      mbar_init(smem_u32(&sm->kv_full[s]), 1);
+      mbar_init(smem_u32(&sm->kv_empty[s]), 1);
+    }
+    for (int i = 0; i < kFwdSlots; ++i) {
+      mbar_init(smem_u32(&sm->s_full[i]), 1);
+      mbar_init(smem_u32(&sm->p_full[i]), 8);  // one arrival per softmax warp
+    }
+    sm->abort_flag = 0;
+    mbar_fence_init();
+    fence_proxy_async_smem();
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+    const uint32_t bar = smem_u32(&sm->q_full);
+    mbar_expect_tx(bar, 2 * kTileBytes);
+    tma_load_4d(smem_u32(sm->u.t.q[0]), &tm_q, bar, 0, mb * 64, h, b);
+    tma_load_4d(smem_u32(sm->u.t.q[1]), &tm_q, bar, 0, mb * 64, h, b);
+  }
+  if (warp == 9) {
+    tmem_alloc(smem_u32(&sm->tmem_base), kFwdTmemCols);
+    tmem_relinquish();
+  }
+
   // ---- this query block's key-block list, into shared memory ----
   int n_tiles = 0;
   if (p.block != nullptr) {
@@ -174,53 +209,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   }
   const int n_super = (n_tiles + 1) >> 1;
   const int32_t* cols = sm->cols;  // visible to every role after the set-up barrier
-
-  // ---- set-up ----
-  if (threadIdx.x == 0) {
-#ifdef BSA_TRACE
-    unsigned smid;
-    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-    BSA_TR_CTA(0, global_timer_ns());
-    BSA_TR_CTA(2, smid);
-    BSA_TR_CTA(3, n_tiles);
-#endif
-    mbar_init(smem_u32(&sm->q_full), 1);
-    for (int s = 0; s < kFwdStages; ++s) {
-      mbar_init(smem_u32(&sm->kv_full[s]), 1);
-      mbar_init(smem_u32(&sm->kv_empty[s]), 1);
-    }
-    for (int i = 0; i < kFwdSlots; ++i) {
-      mbar_init(smem_u32(&sm->s_full[i]), 1);
-      mbar_init(smem_u32(&sm->p_full[i]), 8);  // one arrival per softmax warp
-    }
-    sm->abort_flag = 0;
-    mbar_fence_init();
-  }
-  if (warp == 9) {
-    tmem_alloc(smem_u32(&sm->tmem_base), kFwdTmemCols);
-    tmem_relinquish();
-  }
-  if (warp == 8 && lane == 0) {
-    tma_prefetch_desc(&tm_q);
-    tma_prefetch_desc(&tm_k);
-    tma_prefetch_desc(&tm_v);
-  }
+  if (threadIdx.x == 0) BSA_TR(6, 0, 1);
+  if (threadIdx.x == 0) BSA_TR_CTA(3, n_tiles);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = sm->tmem_base;
   volatile int* abort_flag = &sm->abort_flag;
+  if (threadIdx.x == 0) BSA_TR(6, 0, 2);
 
   if (warp == 8) {
     // =========================== TMA producer ===========================
-    if (n_super > 0) {
+    if (n_super == 0) {
+      // nobody consumes Q then, but its copy must have landed before shared memory is given back
+      if (!mbar_wait_warp(smem_u32(&sm->q_full), 0, abort_flag))
+        fwd_give_up(sm, p.status, kFailProducer);
+    } else {
       const bool leader = elect_one();
-      if (leader) {
-        const uint32_t bar = smem_u32(&sm->q_full);
-        mbar_expect_tx(bar, 2 * kTileBytes);
-        tma_load_4d(smem_u32(sm->u.t.q[0]), &tm_q, bar, 0, mb * 64, h, b);
-        tma_load_4d(smem_u32(sm->u.t.q[1]), &tm_q, bar, 0, mb * 64, h, b);
-      }
       for (int u = 0; u < n_super; ++u) {
         const int ss = u % kFwdStages;
         const int nt = min(2, n_tiles - 2 * u);
@@ -260,7 +265,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         ok = mbar_wait_warp(smem_u32(&sm->kv_full[ss]), (u / kFwdStages) & 1, abort_flag);
         if (!ok) break;
         if (u >= kFwdSlots) {
-          // the slot still holds P of superstep u-2 until that superstep's P V is complete
+          // the slot still holds P of superstep u-3 until that superstep's P V is complete
           const int up = u - kFwdSlots;
           ok = mbar_wait_warp(smem_u32(&sm->kv_empty[up % kFwdStages]), (up / kFwdStages) & 1,
                               abort_flag);
@@ -297,15 +302,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if (leader) {
           BSA_TR(7, u, 0);
           // P of tile t sits over that tile's own S columns: keys [32 g + 16 k2, +16) of tile t at
-          // slot column 64 t + 32 g + 8 k2
-          for (int t = 0; t < nt; ++t) {
-            const uint64_t desc_v =
-                desc_v0 + static_cast<uint64_t>((ss * 2 + t) * (kTileBytes >> 4));
+          // slot column 64 t + 32 g + 8 k2; the other half of the lanes holds zeros there
+          for (int g = 0; g < 2; ++g) {
+            for (int t = 0; t < nt; ++t) {
+              const uint64_t desc_v =
+                  desc_v0 + static_cast<uint64_t>((ss * 2 + t) * (kTileBytes >> 4));
 #pragma unroll
-            for (int kk = 0; kk < 4; ++kk)
-              umma_ts(tmem + kTmemO + 64 * (2 * t + (kk >> 1)),
-                      tmem + 128 * slot + 64 * t + 32 * (kk >> 1) + 8 * (kk & 1),
-                      desc_v + 128 * kk, idesc_pv, (u > 0) || ((kk & 1) != 0));
+              for (int k2 = 0; k2 < 2; ++k2)
+                umma_ts(tmem + kTmemO + 64 * g, tmem + 128 * slot + 64 * t + 32 * g + 8 * k2,
+                        desc_v + 128 * (2 * g + k2), idesc_pv, (u > 0) || (t > 0) || (k2 > 0));
+            }
           }
           tc_commit(smem_u32(&sm->kv_empty[ss]));
           BSA_TR(7, u, 1);
@@ -322,7 +328,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const int r_blk = (quarter & 1) * 32 + lane;       // row of the query block
     const int row = mb * 64 + r_blk;
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
-    const uint32_t o_addr = tmem + lane_base + kTmemO + 64 * (2 * t_mine + g);
+    const uint32_t o_addr = tmem + lane_base + kTmemO + 64 * g;
     const float c = p.scale_log2;
     float m_ref = -INFINITY, m_true = -INFINITY, l = 0.f;
     bool ok = true;
@@ -333,6 +339,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       ok = mbar_wait_warp(smem_u32(&sm->s_full[slot]), (u / kFwdSlots) & 1, abort_flag);
       if (!ok) break;
       if (lane == 0 && !(warp & 1)) BSA_TR(2 + (warp >> 1), u, 0);
+      if (1 - t_mine < nt) {
+        // the other tile's P V also sweeps these lanes: give it zeros where that tile's P lives
+        uint32_t z[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) z[i] = 0u;
+        tc_fence_after();
+        tmem_st_32x32b_x16(tmem + lane_base + 128 * slot + 64 * (1 - t_mine) + 32 * g, z);
+        if (t_mine >= nt) {
+          tc_wait_st();
+          tc_fence_before();
+        }
+      }
       if (t_mine < nt) {
         tc_fence_after();
         // this warp's S: columns [64 t + 32 g, +32) of the slot; its P goes over the first 16
@@ -356,7 +374,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if (__any_sync(0xffffffffu, rescale)) {
           // This warp's O must hold the previous superstep's product (u >= 1 here) first: P V of
           // superstep u-1 completing frees that superstep's stage.  S_u being complete implies
-          // P V of u-2 and earlier are complete, and P V of u+3 cannot complete before this warp
+          // P V of u-3 and earlier are complete, and P V of u+3 cannot complete before this warp
           // delivers P_u, so the awaited phase is unambiguous.
           ok = mbar_wait_warp(smem_u32(&sm->kv_empty[(u - 1) % kFwdStages]),
                               ((u - 1) / kFwdStages) & 1, abort_flag);
@@ -385,45 +403,66 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
 
     // ---- epilogue: merge the four partial results of every query row ----
-    // The last P V frees the last stage; every earlier phase of that barrier is long complete.
+    // (key groups 0/1 x lanes r / r + 64).  A warp reads both accumulators of its own lanes
+    // straight from TMEM; only the hand-over from lanes 64..127 to lanes 0..63 goes through
+    // shared memory (the K/V ring, dead once the last P V is complete).
     if (ok && n_super > 0)
       ok = mbar_wait_warp(smem_u32(&sm->kv_empty[(n_super - 1) % kFwdStages]),
                           ((n_super - 1) / kFwdStages) & 1, abort_flag);
     if (!ok) fwd_give_up(sm, p.status, kFailSoftmax);
+    if (threadIdx.x == 0) BSA_TR(6, 1, 0);
     sm->mref[g][lane_row] = m_ref;
     sm->lsum[g][lane_row] = l;
     sm->mtrue[g][lane_row] = m_true;
     named_barrier_sync(1, 256);  // every softmax warp arrives at each of these, also after a give-up
     const bool live = !*abort_flag;
-    {
-      // the row's four partials live in lanes r_blk and r_blk + 64, key groups 0 and 1
-      float m_all = -INFINITY;
+    if (threadIdx.x == 0) BSA_TR(6, 1, 1);
+    float m_all = -INFINITY;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) m_all = fmaxf(m_all, sm->mref[i & 1][r_blk + 64 * (i >> 1)]);
-      float l_all = 0.f;
+    for (int i = 0; i < 4; ++i) m_all = fmaxf(m_all, sm->mref[i & 1][r_blk + 64 * (i >> 1)]);
+    float l_all = 0.f;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float mi = sm->mref[i & 1][r_blk + 64 * (i >> 1)];
-        if (mi != -INFINITY) l_all += ex2_approx(mi - m_all) * sm->lsum[i & 1][r_blk + 64 * (i >> 1)];
-      }
-      const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
-      const float w = m_ref == -INFINITY ? 0.f : ex2_approx(m_ref - m_all) * inv;
-      // the K/V ring is dead now (all MMAs complete): every thread drops its weighted share there
-      float (*mine)[65] = sm->u.part[2 * t_mine + g];
+    for (int i = 0; i < 4; ++i) {
+      const float mi = sm->mref[i & 1][r_blk + 64 * (i >> 1)];
+      if (mi != -INFINITY) l_all += ex2_approx(mi - m_all) * sm->lsum[i & 1][r_blk + 64 * (i >> 1)];
+    }
+    const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+    // weights of this lane's two accumulator rows; this warp merges columns [32 g, +32) of both
+    const float m0 = sm->mref[0][lane_row], m1 = sm->mref[1][lane_row];
+    const float w0 = m0 == -INFINITY ? 0.f : ex2_approx(m0 - m_all) * inv;
+    const float w1 = m1 == -INFINITY ? 0.f : ex2_approx(m1 - m_all) * inv;
+    float acc[32];
+    if (live && n_super > 0) {  // warp-uniform
+      uint32_t a0[32], a1[32];
+      tc_fence_after();
+      tmem_ld_32x32b_x32(tmem + lane_base + kTmemO + 32 * g, a0);
+      tmem_ld_32x32b_x32(tmem + lane_base + kTmemO + 64 + 32 * g, a1);
+      tc_wait_ld();
 #pragma unroll
-      for (int part = 0; part < 2; ++part) {
-        uint32_t raw[32];
-        if (live) {  // warp-uniform; lanes that never saw a tile discard what they read
-          tc_fence_after();
-          tmem_ld_32x32b_x32(o_addr + 32 * part, raw);
-          tc_wait_ld();
-        }
+      for (int i = 0; i < 32; ++i)
+        acc[i] = fmaf(__uint_as_float(a1[i]), w1, __uint_as_float(a0[i]) * w0);
+    } else {
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          mine[32 * part + i][r_blk] =
-              (live && m_ref != -INFINITY) ? __uint_as_float(raw[i]) * w : 0.f;
-      }
-      if (live && t_mine == 0 && g == 0) {
+      for (int i = 0; i < 32; ++i) acc[i] = 0.f;
+    }
+    if (t_mine == 1) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) sm->u.xfer[32 * g + i][r_blk] = acc[i];
+    }
+    named_barrier_sync(1, 256);
+    if (threadIdx.x == 0) BSA_TR(6, 1, 2);
+    if (t_mine == 0 && live) {
+      uint32_t packed[16];
+#pragma unroll
+      for (int i = 0; i < 32; i += 2)
+        packed[i / 2] = pack_2x16<kBf16>(acc[i] + sm->u.xfer[32 * g + i][r_blk],
+                                         acc[i + 1] + sm->u.xfer[32 * g + i + 1][r_blk]);
+      uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.o) + b * p.o_sb + h * p.o_sh +
+                                            static_cast<int64_t>(row) * p.o_sn + 32 * g);
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+      if (g == 0) {
         const int64_t ri = (static_cast<int64_t>(b) * p.H + h) * p.N + row;
         p.lse2[ri] = l_all > 0.f ? m_all + lg2_approx(l_all) : -INFINITY;
         if (p.rowmax)
@@ -431,28 +470,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                                fmaxf(sm->mtrue[0][r_blk + 64], sm->mtrue[1][r_blk + 64]));
       }
     }
-    named_barrier_sync(1, 256);
-    if (live) {
-      // thread -> (row, 16-column segment) of the output block
-      const int tid = threadIdx.x;
-      const int orow = tid & 63;
-      const int seg = tid >> 6;
-      uint32_t packed[8];
-#pragma unroll
-      for (int i = 0; i < 16; i += 2) {
-        const int c0 = 16 * seg + i;
-        const float x0 = (sm->u.part[0][c0][orow] + sm->u.part[1][c0][orow]) +
-                         (sm->u.part[2][c0][orow] + sm->u.part[3][c0][orow]);
-        const float x1 = (sm->u.part[0][c0 + 1][orow] + sm->u.part[1][c0 + 1][orow]) +
-                         (sm->u.part[2][c0 + 1][orow] + sm->u.part[3][c0 + 1][orow]);
-        packed[i / 2] = pack_2x16<kBf16>(x0, x1);
-      }
-      uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.o) + b * p.o_sb + h * p.o_sh +
-                                            static_cast<int64_t>(mb * 64 + orow) * p.o_sn +
-                                            16 * seg);
-      dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-      dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-    }
+    if (threadIdx.x == 0) BSA_TR(6, 1, 3);
   }
 
   // ---- tear-down: every role arrives here, also after a give-up ----
@@ -463,6 +481,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     tc_fence_after();
     tmem_dealloc(tmem, kFwdTmemCols);
   }
+  if (threadIdx.x == 0) BSA_TR(6, 2, 0);
   if (threadIdx.x == 0) BSA_TR_CTA(1, global_timer_ns());
 }
 
