@@ -1,33 +1,40 @@
 // Forward block-sparse attention for sm_100a.
 //
-// One CTA owns ONE query block (64 rows) of one (batch, head) and walks that block's list of key
-// blocks two at a time ("supersteps").  The 64 query rows are loaded twice, as rows 0..63 and
-// 64..127 of the tcgen05 A operand, so that the 128 TMEM lanes split the two key tiles of a
-// superstep between them: lanes 0..63 own tile a, lanes 64..127 own tile b.  Every SM sub-partition
-// (32 lanes) therefore always has the same amount of exp2 work, whatever the sparsity pattern —
-// the exponentials, not the tensor pipe, bound this kernel at head dimension 64.
-//   warp 8   : TMA producer — Q (twice) once, then only the listed K/V tiles into a 4-deep ring of
-//              superstages (2 K tiles + 2 V tiles each)
-//   warp 9   : S issuer and TMEM owner — S_u = [Q;Q] [K_a;K_b]^T as four M=128,N=128,K=16 MMAs into
-//              one of 3 TMEM slots (lanes 0..63 use columns 0..63, lanes 64..127 columns 64..127;
-//              an N=128 instruction occupies the tensor pipe no longer than an N=64 one)
-//   warp 10  : P V issuer — O[g] += P_a[:, keys of group g] V_a[..] + P_b[:, keys of group g] V_b[..]
-//              for key group g in {0, 1}: two accumulators, P read from TMEM, V an MN-major smem
-//              operand.  Lanes 64..127 store zeros where tile a's P lives and lanes 0..63 where
-//              tile b's does, so row r of an accumulator only ever sums tile-a products and row
-//              r + 64 only tile-b products.  S and P V are issued by different warps so that
-//              neither waits behind the other's barrier round trips.
-//   warps 0..7 : online softmax.  Warp w works on TMEM lane quarter w % 4 and on key group
-//              g = w / 4 (keys [32 g, +32) of its tile): tcgen05.ld of S, exp2, P written back over
-//              the warp's own S columns as 16-bit, lazy rescale of its own accumulator.  The warps
-//              never talk to each other inside the loop, so the two warps of a sub-partition
-//              drift out of phase and overlap each other's exp2 and non-exp2 work.
-// Each query row thus has four partial results (m, l, O) that the epilogue merges.
+// Persistent kernel: one CTA per SM walks a strided sequence of work items, each item being ONE
+// query block (64 rows) of one (batch, head) with its list of key blocks, taken two at a time
+// ("supersteps").  The 64 query rows are loaded twice, as rows 0..63 and 64..127 of the tcgen05 A
+// operand, so that the 128 TMEM lanes split the two key tiles of a superstep between them: lanes
+// 0..63 own tile a, lanes 64..127 own tile b.  Every SM sub-partition (32 lanes) therefore always
+// has the same amount of exp2 work, whatever the sparsity pattern — the exponentials, not the
+// tensor pipe, bound this kernel at head dimension 64.
+//
+// Roles (15 warps); every role walks the same item sequence, so set-up of item i+1 and write-out
+// of item i-1 overlap the arithmetic of item i:
+//   warp 8      : producer — lists the item's key blocks (from the mask row, or copies the CSR row),
+//                 TMA-loads Q (twice) and only the listed K/V tiles into a 4-deep ring of
+//                 superstages (2 K tiles + 2 V tiles each)
+//   warp 9      : S issuer and TMEM owner — S = [Q;Q] [K_a;K_b]^T as four M=128,N=128,K=16 MMAs
+//                 into one of 2 TMEM slots (lanes 0..63 use columns 0..63, lanes 64..127 columns
+//                 64..127; an N=128 instruction occupies the tensor pipe no longer than an N=64 one)
+//   warp 10     : P V issuer — O[g] += P_a[:, keys of group g] V_a[..] + P_b[:, keys of group g] V_b[..]
+//                 for key group g in {0,1}, P read from TMEM, V an MN-major smem operand.  Lanes
+//                 64..127 store zeros where tile a's P lives and lanes 0..63 where tile b's does,
+//                 so row r of an accumulator only sums tile-a products and row r+64 only tile-b
+//                 products.  Accumulators are double-buffered by item parity.
+//   warps 0..7  : online softmax.  Warp w works on TMEM lane quarter w % 4 and key group g = w / 4
+//                 (keys [32 g, +32) of its tile): tcgen05.ld of S, exp2, P written back over the
+//                 warp's own S columns as 16-bit, lazy rescale of its own accumulator rows.  No
+//                 communication between these warps inside an item.
+//   warps 11..14: write-out — merge the four partial results (m, l, O) of every query row (key
+//                 groups 0/1 x lanes r / r+64), normalise, store O, LSE and the row maximum.
 //
 // Numerics follow the reference's loop (fa2_custom_mask/fa2_fwd.py:150-196): logits scaled by
 // sm_scale*log2(e), exp2 domain, fp32 row sums of the fp32 probabilities, P rounded to the input
 // dtype before P V.  The running maximum is only advanced when it grew by more than 8 (a factor
 // 256), which leaves O = acc / l unchanged because both use the same reference maximum.
+//
+// Every wait is bounded; a wait that gives up raises a CTA-wide flag, every role then falls
+// through its loops without touching barriers' data again, and TMEM is always released.
 #include <math.h>
 
 #include "host_common.h"
@@ -36,33 +43,34 @@
 namespace bsa {
 
 constexpr int kFwdStages = 4;   // superstages (2 K + 2 V tiles) in flight in shared memory
-constexpr int kFwdSlots = 3;    // S/P supertiles (128 TMEM columns) in flight
-constexpr int kFwdThreads = 352;
+constexpr int kFwdSlots = 2;    // S/P supertiles (128 TMEM columns) in flight
+constexpr int kFwdThreads = 480;
+constexpr int kSoftmaxWarps = 8, kProducerWarp = 8, kSWarp = 9, kPvWarp = 10, kOutWarp0 = 11;
 constexpr uint32_t kTileBytes = 64 * 64 * 2;       // one Q, K or V tile
 constexpr uint32_t kFwdTmemCols = 512;
-constexpr uint32_t kTmemO = 384;                   // O[g] at 384 + 64 g; slot r at 128 r
+constexpr uint32_t kTmemO = 256;   // accumulator of item parity a, key group g at 256 + 128 a + 64 g
 constexpr float kRescaleThreshold = 8.0f;
-constexpr int kFwdMaxTiles = 2048;                 // key blocks per row that a CTA can list (N <= 131072)
+constexpr int kFwdMaxTiles = 2048;  // key blocks per row that a CTA can list (N <= 131072)
 
 struct FwdSmem {
-  union {
-    struct {
-      uint8_t q[2][kTileBytes];                 // the query block, twice
-      uint8_t k[kFwdStages][2][kTileBytes];
-      uint8_t v[kFwdStages][2][kTileBytes];
-    } t;
-    float xfer[64][65];                         // epilogue: lanes 64..127 hand over, [col][row]
-  } u;
-  int32_t cols[kFwdMaxTiles];  // this query block's key-block list
-  int wsum[kFwdThreads / 32];  // list building: kept blocks seen by each warp
-  float mref[2][128];      // epilogue: reference maximum per key group and lane
-  float lsum[2][128];      // epilogue: row sums
-  float mtrue[2][128];     // epilogue: true running maxima
-  uint64_t q_full;
+  uint8_t q[2][2][kTileBytes];                // by item parity: the query block, twice
+  uint8_t k[kFwdStages][2][kTileBytes];
+  uint8_t v[kFwdStages][2][kTileBytes];
+  float xfer[64][65];                         // write-out: lanes 64..127 hand over, [col][row]
+  int32_t cols[2][kFwdMaxTiles];              // by item parity: the item's key-block list
+  int ntiles[2];
+  float mref[2][2][128];                      // by item parity, key group, lane
+  float lsum[2][2][128];
+  float mtrue[2][2][128];
+  uint64_t list_full[2];                      // producer -> everyone: list and tile count ready
+  uint64_t q_full[2], q_free[2];
   uint64_t kv_full[kFwdStages];
-  uint64_t kv_empty[kFwdStages];  // P V of the superstep done: stage free, S slot free, O updated
+  uint64_t kv_empty[kFwdStages];              // P V of the superstep done: stage and S slot free
   uint64_t s_full[kFwdSlots];
   uint64_t p_full[kFwdSlots];
+  uint64_t o_full[2];                         // last P V of the item done
+  uint64_t stats_full[2];                     // softmax warps published (m, l) of the item
+  uint64_t o_free[2];                         // write-out done with accumulators/stats/list
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -70,7 +78,7 @@ struct FwdSmem {
 struct FwdParams {
   const int32_t* row_ptr;   // list mode: CSR row lists
   const int32_t* col_idx;
-  const uint8_t* block;     // mask mode (block != nullptr): the CTA lists its own mask row
+  const uint8_t* block;     // mask mode (block != nullptr): the producer lists the mask row
   int64_t ms0, ms1, ms2, ms3;
   void* o;
   int64_t o_sb, o_sh, o_sn;
@@ -78,11 +86,12 @@ struct FwdParams {
   float* rowmax;
   int B, H, N, nb;
   int list_b_stride, list_h_stride;
+  int items;                // B * H * nb
   float scale_log2;
   int32_t* status;
 };
 
-enum FwdFail : int { kFailProducer = 1, kFailMma = 2, kFailSoftmax = 3 };
+enum FwdFail : int { kFailProducer = 1, kFailMma = 2, kFailSoftmax = 3, kFailOut = 4 };
 
 __device__ __forceinline__ void fwd_give_up(FwdSmem* sm, int32_t* status, int code) {
   sm->abort_flag = 1;
@@ -127,6 +136,19 @@ __device__ __forceinline__ float max_chunk(const uint32_t* sr) {
   return max3(mx0, mx1, fmaxf(__uint_as_float(sr[30]), __uint_as_float(sr[31])));
 }
 
+// Work item w -> (batch, head, query block); late (long, if causal) query blocks of a head first.
+struct FwdItem {
+  int b, h, mb;
+};
+__device__ __forceinline__ FwdItem fwd_item(int w, const FwdParams& p) {
+  const int bh = w / p.nb;
+  FwdItem it;
+  it.mb = p.nb - 1 - (w - bh * p.nb);
+  it.b = bh / p.H;
+  it.h = bh - it.b * p.H;
+  return it;
+}
+
 template <bool kBf16>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -137,170 +159,199 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
   const int warp = uniform_warp_index();
   const int lane = threadIdx.x & 31;
+  const int stride = gridDim.x;
 
-  // ---- which query block ----
-  const int bh = blockIdx.x / p.nb;
-  const int mb = p.nb - 1 - (blockIdx.x % p.nb);  // late (long, if causal) rows first
-  const int b = bh / p.H;
-  const int h = bh % p.H;
-  if (threadIdx.x == 0) BSA_TR(6, 0, 0);
-  // ---- set-up; the Q load needs no list, so it starts first and overlaps the list building ----
-  if (warp == 8 && lane == 0) {
-#ifdef BSA_TRACE
-    unsigned smid;
-    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+  // ---- set-up ----
+  if (threadIdx.x == 0) {
     BSA_TR_CTA(0, global_timer_ns());
-    BSA_TR_CTA(2, smid);
-#endif
-    mbar_init(smem_u32(&sm->q_full), 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&sm->list_full[i]), 1);
+      mbar_init(smem_u32(&sm->q_full[i]), 1);
+      mbar_init(smem_u32(&sm->q_free[i]), 1);
+      mbar_init(smem_u32(&sm->o_full[i]), 1);
+      mbar_init(smem_u32(&sm->stats_full[i]), kSoftmaxWarps);
+      mbar_init(smem_u32(&sm->o_free[i]), 4);  // one arrival per write-out warp
+    }
     for (int s = 0; s < kFwdStages; ++s) {
       mbar_init(smem_u32(&sm->kv_full[s]), 1);
       mbar_init(smem_u32(&sm->kv_empty[s]), 1);
     }
     for (int i = 0; i < kFwdSlots; ++i) {
       mbar_init(smem_u32(&sm->s_full[i]), 1);
-      mbar_init(smem_u32(&sm->p_full[i]), 8);  // one arrival per softmax warp
+      mbar_init(smem_u32(&sm->p_full[i]), kSoftmaxWarps);
     }
     sm->abort_flag = 0;
     mbar_fence_init();
-    fence_proxy_async_smem();
-    tma_prefetch_desc(&tm_q);
-    tma_prefetch_desc(&tm_k);
-    tma_prefetch_desc(&tm_v);
-    const uint32_t bar = smem_u32(&sm->q_full);
-    mbar_expect_tx(bar, 2 * kTileBytes);
-    tma_load_4d(smem_u32(sm->u.t.q[0]), &tm_q, bar, 0, mb * 64, h, b);
-    tma_load_4d(smem_u32(sm->u.t.q[1]), &tm_q, bar, 0, mb * 64, h, b);
   }
-  if (warp == 9) {
+  if (warp == kSWarp) {
     tmem_alloc(smem_u32(&sm->tmem_base), kFwdTmemCols);
     tmem_relinquish();
   }
-
-  // ---- this query block's key-block list, into shared memory ----
-  int n_tiles = 0;
-  if (p.block != nullptr) {
-    // mask mode: ordered compaction of the kept blocks of mask row (b, h, mb); list_*_stride are
-    // 0 for a broadcast axis and 1 otherwise here
-    const uint8_t* mrow = p.block + (b * p.list_b_stride) * p.ms0 + (h * p.list_h_stride) * p.ms1 +
-                          static_cast<int64_t>(mb) * p.ms2;
-    for (int c0 = 0; c0 < p.nb; c0 += kFwdThreads) {
-      const int c = c0 + static_cast<int>(threadIdx.x);
-      const bool keep = c < p.nb && mrow[c * p.ms3] != 0;
-      const unsigned bal = __ballot_sync(0xffffffffu, keep);
-      if (lane == 0) sm->wsum[warp] = __popc(bal);
-      __syncthreads();
-      int before = 0, total = 0;
-#pragma unroll
-      for (int w = 0; w < kFwdThreads / 32; ++w) {
-        const int cnt = sm->wsum[w];
-        before += w < warp ? cnt : 0;
-        total += cnt;
-      }
-      if (keep) sm->cols[n_tiles + before + __popc(bal & ((1u << lane) - 1u))] = c;
-      n_tiles += total;
-      __syncthreads();
-    }
-  } else {
-    const int64_t li = static_cast<int64_t>(b * p.list_b_stride + h * p.list_h_stride) * p.nb + mb;
-    const int beg = __ldg(p.row_ptr + li);
-    n_tiles = __ldg(p.row_ptr + li + 1) - beg;
-    for (int i = threadIdx.x; i < n_tiles; i += kFwdThreads) sm->cols[i] = __ldg(p.col_idx + beg + i);
+  if (warp == kProducerWarp && lane == 0) {
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
   }
-  const int n_super = (n_tiles + 1) >> 1;
-  const int32_t* cols = sm->cols;  // visible to every role after the set-up barrier
-  if (threadIdx.x == 0) BSA_TR(6, 0, 1);
-  if (threadIdx.x == 0) BSA_TR_CTA(3, n_tiles);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = sm->tmem_base;
   volatile int* abort_flag = &sm->abort_flag;
-  if (threadIdx.x == 0) BSA_TR(6, 0, 2);
 
-  if (warp == 8) {
-    // =========================== TMA producer ===========================
-    if (n_super == 0) {
-      // nobody consumes Q then, but its copy must have landed before shared memory is given back
-      if (!mbar_wait_warp(smem_u32(&sm->q_full), 0, abort_flag))
-        fwd_give_up(sm, p.status, kFailProducer);
-    } else {
-      const bool leader = elect_one();
-      for (int u = 0; u < n_super; ++u) {
-        const int ss = u % kFwdStages;
+  if (warp == kProducerWarp) {
+    // =========================== producer ===========================
+    const bool leader = elect_one();
+    bool ok = true;
+    int gs = 0;  // supersteps issued so far by this CTA (ring position)
+    int qi = 0;  // non-empty items so far (Q buffer position)
+    for (int i = 0, w = blockIdx.x; ok && w < p.items; ++i, w += stride) {
+      const FwdItem it = fwd_item(w, p);
+      const int par = i & 1;
+      // the list buffer (and the tile count) of item i-2 must have been read by everyone
+      if (i >= 2)
+        ok = mbar_wait_warp_idle(smem_u32(&sm->o_free[par]), ((i - 2) >> 1) & 1, abort_flag, 128);
+      if (!ok) break;
+      int32_t* cols = sm->cols[par];
+      int n_tiles = 0;
+      if (p.block != nullptr) {
+        // mask mode: ordered compaction of the kept blocks of mask row (b, h, mb);
+        // list_*_stride are 0 for a broadcast axis and 1 otherwise here
+        const uint8_t* mrow = p.block + (it.b * p.list_b_stride) * p.ms0 +
+                              (it.h * p.list_h_stride) * p.ms1 + static_cast<int64_t>(it.mb) * p.ms2;
+        for (int c0 = 0; c0 < p.nb; c0 += 128) {
+          // four independent loads per lane before the ballots
+          bool keep[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int c = c0 + 32 * j + lane;
+            keep[j] = c < p.nb && mrow[c * p.ms3] != 0;
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const unsigned bal = __ballot_sync(0xffffffffu, keep[j]);
+            if (keep[j]) cols[n_tiles + __popc(bal & ((1u << lane) - 1u))] = c0 + 32 * j + lane;
+            n_tiles += __popc(bal);
+          }
+        }
+      } else {
+        const int64_t li =
+            static_cast<int64_t>(it.b * p.list_b_stride + it.h * p.list_h_stride) * p.nb + it.mb;
+        const int beg = __ldg(p.row_ptr + li);
+        n_tiles = __ldg(p.row_ptr + li + 1) - beg;
+        for (int j = lane; j < n_tiles; j += 32) cols[j] = __ldg(p.col_idx + beg + j);
+      }
+      __syncwarp();
+      if (lane == 0) {
+        sm->ntiles[par] = n_tiles;
+        mbar_arrive(smem_u32(&sm->list_full[par]));  // release: count and list are visible
+      }
+      const int n_super = (n_tiles + 1) >> 1;
+      if (n_super == 0) continue;
+      const int qpar = qi & 1;
+      if (qi >= 2) ok = mbar_wait_warp(smem_u32(&sm->q_free[qpar]), ((qi - 2) >> 1) & 1, abort_flag);
+      if (!ok) break;
+      if (leader) {
+        const uint32_t bar = smem_u32(&sm->q_full[qpar]);
+        mbar_expect_tx(bar, 2 * kTileBytes);
+        tma_load_4d(smem_u32(sm->q[qpar][0]), &tm_q, bar, 0, it.mb * 64, it.h, it.b);
+        tma_load_4d(smem_u32(sm->q[qpar][1]), &tm_q, bar, 0, it.mb * 64, it.h, it.b);
+      }
+      ++qi;
+      for (int u = 0; u < n_super; ++u, ++gs) {
+        const int ss = gs % kFwdStages;
         const int nt = min(2, n_tiles - 2 * u);
         const int n0 = cols[2 * u];
         const int n1 = nt == 2 ? cols[2 * u + 1] : 0;
-        if (!mbar_wait_warp(smem_u32(&sm->kv_empty[ss]), ((u / kFwdStages) & 1) ^ 1, abort_flag)) {
-          fwd_give_up(sm, p.status, kFailProducer);
-          break;
-        }
+        ok = mbar_wait_warp(smem_u32(&sm->kv_empty[ss]), ((gs / kFwdStages) & 1) ^ 1, abort_flag);
+        if (!ok) break;
         if (leader) {
-          BSA_TR(0, u, 0);
           const uint32_t bar = smem_u32(&sm->kv_full[ss]);
           mbar_expect_tx(bar, 2 * kTileBytes * nt);
-          tma_load_4d(smem_u32(sm->u.t.k[ss][0]), &tm_k, bar, 0, n0 * 64, h, b);
-          tma_load_4d(smem_u32(sm->u.t.v[ss][0]), &tm_v, bar, 0, n0 * 64, h, b);
+          tma_load_4d(smem_u32(sm->k[ss][0]), &tm_k, bar, 0, n0 * 64, it.h, it.b);
+          tma_load_4d(smem_u32(sm->v[ss][0]), &tm_v, bar, 0, n0 * 64, it.h, it.b);
           if (nt == 2) {
-            tma_load_4d(smem_u32(sm->u.t.k[ss][1]), &tm_k, bar, 0, n1 * 64, h, b);
-            tma_load_4d(smem_u32(sm->u.t.v[ss][1]), &tm_v, bar, 0, n1 * 64, h, b);
+            tma_load_4d(smem_u32(sm->k[ss][1]), &tm_k, bar, 0, n1 * 64, it.h, it.b);
+            tma_load_4d(smem_u32(sm->v[ss][1]), &tm_v, bar, 0, n1 * 64, it.h, it.b);
           }
-          BSA_TR(0, u, 1);
         }
       }
     }
-  } else if (warp == 9) {
+    if (!ok) fwd_give_up(sm, p.status, kFailProducer);
+  } else if (warp == kSWarp) {
     // =========================== S issuer ===========================
-    if (n_super > 0) {
-      constexpr uint32_t idesc_s128 = umma_idesc(kBf16, 0, 0, 128, 128);  // [Q;Q] x [K_a;K_b]
-      constexpr uint32_t idesc_s64 = umma_idesc(kBf16, 0, 0, 128, 64);    // odd tail: one tile
-      const bool leader = elect_one();
-      const uint64_t desc_q = smem_desc_sw128(smem_u32(sm->u.t.q[0]), 16, 1024);
-      const uint64_t desc_k0 = smem_desc_sw128(smem_u32(sm->u.t.k[0][0]), 16, 1024);
-      bool ok = mbar_wait_warp(smem_u32(&sm->q_full), 0, abort_flag);
-      for (int u = 0; ok && u < n_super; ++u) {
-        const int ss = u % kFwdStages;
-        const int slot = u % kFwdSlots;
+    constexpr uint32_t idesc_s128 = umma_idesc(kBf16, 0, 0, 128, 128);  // [Q;Q] x [K_a;K_b]
+    constexpr uint32_t idesc_s64 = umma_idesc(kBf16, 0, 0, 128, 64);    // odd tail: one tile
+    const bool leader = elect_one();
+    const uint64_t desc_q0 = smem_desc_sw128(smem_u32(sm->q[0][0]), 16, 1024);
+    const uint64_t desc_k0 = smem_desc_sw128(smem_u32(sm->k[0][0]), 16, 1024);
+    bool ok = true;
+    int gs = 0, qi = 0;
+    for (int i = 0, w = blockIdx.x; ok && w < p.items; ++i, w += stride) {
+      const int par = i & 1;
+      ok = mbar_wait_warp(smem_u32(&sm->list_full[par]), (i >> 1) & 1, abort_flag);
+      if (!ok) break;
+      const int n_tiles = *const_cast<volatile int*>(&sm->ntiles[par]);
+      const int n_super = (n_tiles + 1) >> 1;
+      if (n_super == 0) continue;
+      const int qpar = qi & 1;
+      ok = mbar_wait_warp(smem_u32(&sm->q_full[qpar]), (qi >> 1) & 1, abort_flag);
+      if (!ok) break;
+      const uint64_t desc_q = desc_q0 + static_cast<uint64_t>(qpar * ((2 * kTileBytes) >> 4));
+      for (int u = 0; u < n_super; ++u, ++gs) {
+        const int ss = gs % kFwdStages;
+        const int slot = gs % kFwdSlots;
         const int nt = min(2, n_tiles - 2 * u);
-        ok = mbar_wait_warp(smem_u32(&sm->kv_full[ss]), (u / kFwdStages) & 1, abort_flag);
+        ok = mbar_wait_warp(smem_u32(&sm->kv_full[ss]), (gs / kFwdStages) & 1, abort_flag);
         if (!ok) break;
-        if (u >= kFwdSlots) {
-          // the slot still holds P of superstep u-3 until that superstep's P V is complete
-          const int up = u - kFwdSlots;
-          ok = mbar_wait_warp(smem_u32(&sm->kv_empty[up % kFwdStages]), (up / kFwdStages) & 1,
+        if (gs >= kFwdSlots) {
+          // the slot still holds P of superstep gs-2 until that superstep's P V is complete
+          const int gp = gs - kFwdSlots;
+          ok = mbar_wait_warp(smem_u32(&sm->kv_empty[gp % kFwdStages]), (gp / kFwdStages) & 1,
                               abort_flag);
           if (!ok) break;
           tc_fence_after();
         }
         if (leader) {
-          BSA_TR(1, u, 0);
           const uint64_t desc_k = desc_k0 + static_cast<uint64_t>(ss * ((2 * kTileBytes) >> 4));
           const uint32_t idesc = nt == 2 ? idesc_s128 : idesc_s64;
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
             umma_ss(tmem + 128 * slot, desc_q + 2 * kk, desc_k + 2 * kk, idesc, kk > 0);
           tc_commit(smem_u32(&sm->s_full[slot]));
-          BSA_TR(1, u, 1);
+          if (u == n_super - 1) tc_commit(smem_u32(&sm->q_free[qpar]));  // Q buffer reusable
         }
       }
-      if (!ok) fwd_give_up(sm, p.status, kFailMma);
+      ++qi;
     }
-  } else if (warp == 10) {
+    if (!ok) fwd_give_up(sm, p.status, kFailMma);
+  } else if (warp == kPvWarp) {
     // =========================== P V issuer ===========================
-    if (n_super > 0) {
-      constexpr uint32_t idesc_pv = umma_idesc(kBf16, 0, 1, 128, 64);  // P (TMEM) x V (MN-major)
-      const bool leader = elect_one();
-      const uint64_t desc_v0 = smem_desc_sw128(smem_u32(sm->u.t.v[0][0]), 8192, 1024);
-      bool ok = true;
-      for (int u = 0; ok && u < n_super; ++u) {
-        const int ss = u % kFwdStages;
-        const int slot = u % kFwdSlots;
+    constexpr uint32_t idesc_pv = umma_idesc(kBf16, 0, 1, 128, 64);  // P (TMEM) x V (MN-major)
+    const bool leader = elect_one();
+    const uint64_t desc_v0 = smem_desc_sw128(smem_u32(sm->v[0][0]), 8192, 1024);
+    bool ok = true;
+    int gs = 0;
+    for (int i = 0, w = blockIdx.x; ok && w < p.items; ++i, w += stride) {
+      const int par = i & 1;
+      ok = mbar_wait_warp(smem_u32(&sm->list_full[par]), (i >> 1) & 1, abort_flag);
+      if (!ok) break;
+      const int n_tiles = *const_cast<volatile int*>(&sm->ntiles[par]);
+      const int n_super = (n_tiles + 1) >> 1;
+      // the accumulators of this parity are free once item i-2 has been written out
+      if (i >= 2) ok = mbar_wait_warp(smem_u32(&sm->o_free[par]), ((i - 2) >> 1) & 1, abort_flag);
+      if (!ok) break;
+      if (n_super == 0) {
+        if (leader) mbar_arrive(smem_u32(&sm->o_full[par]));
+        continue;
+      }
+      for (int u = 0; u < n_super; ++u, ++gs) {
+        const int ss = gs % kFwdStages;
+        const int slot = gs % kFwdSlots;
         const int nt = min(2, n_tiles - 2 * u);
-        ok = mbar_wait_warp(smem_u32(&sm->p_full[slot]), (u / kFwdSlots) & 1, abort_flag);
+        ok = mbar_wait_warp(smem_u32(&sm->p_full[slot]), (gs / kFwdSlots) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
         if (leader) {
-          BSA_TR(7, u, 0);
           // P of tile t sits over that tile's own S columns: keys [32 g + 16 k2, +16) of tile t at
           // slot column 64 t + 32 g + 8 k2; the other half of the lanes holds zeros there
           for (int g = 0; g < 2; ++g) {
@@ -309,179 +360,200 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                   desc_v0 + static_cast<uint64_t>((ss * 2 + t) * (kTileBytes >> 4));
 #pragma unroll
               for (int k2 = 0; k2 < 2; ++k2)
-                umma_ts(tmem + kTmemO + 64 * g, tmem + 128 * slot + 64 * t + 32 * g + 8 * k2,
-                        desc_v + 128 * (2 * g + k2), idesc_pv, (u > 0) || (t > 0) || (k2 > 0));
+                umma_ts(tmem + kTmemO + 128 * par + 64 * g,
+                        tmem + 128 * slot + 64 * t + 32 * g + 8 * k2, desc_v + 128 * (2 * g + k2),
+                        idesc_pv, (u > 0) || (t > 0) || (k2 > 0));
             }
           }
           tc_commit(smem_u32(&sm->kv_empty[ss]));
-          BSA_TR(7, u, 1);
+          if (u == n_super - 1) tc_commit(smem_u32(&sm->o_full[par]));
         }
       }
-      if (!ok) fwd_give_up(sm, p.status, kFailMma);
     }
-  } else {
-    // =========================== softmax + epilogue ===========================
-    const int g = warp >> 2;          // key columns [32 g, +32) of the tile
+    if (!ok) fwd_give_up(sm, p.status, kFailMma);
+  } else if (warp < kSoftmaxWarps) {
+    // =========================== softmax ===========================
+    const int g = warp >> 2;          // key group: keys [32 g, +32) of the tile
     const int quarter = warp & 3;     // TMEM lane quarter this warp may touch
     const int t_mine = quarter >> 1;  // lanes 0..63 own tile a of a superstep, 64..127 tile b
-    const int lane_row = quarter * 32 + lane;          // TMEM lane
-    const int r_blk = (quarter & 1) * 32 + lane;       // row of the query block
-    const int row = mb * 64 + r_blk;
+    const int lane_row = quarter * 32 + lane;  // TMEM lane
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
-    const uint32_t o_addr = tmem + lane_base + kTmemO + 64 * g;
     const float c = p.scale_log2;
-    float m_ref = -INFINITY, m_true = -INFINITY, l = 0.f;
     bool ok = true;
-
-    for (int u = 0; u < n_super; ++u) {
-      const int slot = u % kFwdSlots;
-      const int nt = min(2, n_tiles - 2 * u);
-      ok = mbar_wait_warp(smem_u32(&sm->s_full[slot]), (u / kFwdSlots) & 1, abort_flag);
+    int gs = 0;
+    for (int i = 0, w = blockIdx.x; ok && w < p.items; ++i, w += stride) {
+      const int par = i & 1;
+      ok = mbar_wait_warp(smem_u32(&sm->list_full[par]), (i >> 1) & 1, abort_flag);
       if (!ok) break;
-      if (lane == 0 && !(warp & 1)) BSA_TR(2 + (warp >> 1), u, 0);
-      if (1 - t_mine < nt) {
-        // the other tile's P V also sweeps these lanes: give it zeros where that tile's P lives
-        uint32_t z[16];
+      const int n_tiles = *const_cast<volatile int*>(&sm->ntiles[par]);
+      const int n_super = (n_tiles + 1) >> 1;
+      const uint32_t o_addr = tmem + lane_base + kTmemO + 128 * par + 64 * g;
+      float m_ref = -INFINITY, m_true = -INFINITY, l = 0.f;
+
+      for (int u = 0; u < n_super; ++u, ++gs) {
+        const int slot = gs % kFwdSlots;
+        const int nt = min(2, n_tiles - 2 * u);
+        ok = mbar_wait_warp(smem_u32(&sm->s_full[slot]), (gs / kFwdSlots) & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        if (1 - t_mine < nt) {
+          // the other tile's P V also sweeps these lanes: give it zeros where that tile's P lives
+          uint32_t z[16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) z[i] = 0u;
-        tc_fence_after();
-        tmem_st_32x32b_x16(tmem + lane_base + 128 * slot + 64 * (1 - t_mine) + 32 * g, z);
-        if (t_mine >= nt) {
-          tc_wait_st();
-          tc_fence_before();
+          for (int j = 0; j < 16; ++j) z[j] = 0u;
+          tmem_st_32x32b_x16(tmem + lane_base + 128 * slot + 64 * (1 - t_mine) + 32 * g, z);
         }
+        if (t_mine < nt) {
+          // this warp's S: columns [64 t + 32 g, +32) of the slot; its P goes over the first 16
+          const uint32_t s_addr = tmem + lane_base + 128 * slot + 64 * t_mine + 32 * g;
+          uint32_t sr[32], pk[16];
+          tmem_ld_32x32b_x32(s_addr, sr);
+          tc_wait_ld();
+          const float zmax = max_chunk(sr) * c;
+          m_true = fmaxf(m_true, zmax);
+          float alpha = 1.f;
+          bool rescale = false;
+          if (m_ref == -INFINITY) {
+            m_ref = zmax;  // first tile of this lane in this item: O and l are still zero
+          } else if (zmax > m_ref + kRescaleThreshold) {
+            alpha = ex2_approx(m_ref - zmax);
+            l *= alpha;
+            m_ref = zmax;
+            rescale = true;
+          }
+          if (__any_sync(0xffffffffu, rescale)) {
+            // This warp's O rows must hold the previous superstep's product (u >= 1 here) first:
+            // P V of superstep gs-1 completing frees that superstep's stage.  S of superstep gs
+            // being complete implies P V of gs-2 and earlier are complete, and P V of gs+3 cannot
+            // complete before this warp delivers P of gs, so the awaited phase is unambiguous.
+            ok = mbar_wait_warp(smem_u32(&sm->kv_empty[(gs - 1) % kFwdStages]),
+                                ((gs - 1) / kFwdStages) & 1, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+#pragma unroll
+            for (int part = 0; part < 2; ++part) {
+              uint32_t orow[32];
+              tmem_ld_32x32b_x32(o_addr + 32 * part, orow);
+              tc_wait_ld();
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                orow[j] = __float_as_uint(__uint_as_float(orow[j]) * alpha);
+              tmem_st_32x32b_x32(o_addr + 32 * part, orow);
+            }
+          }
+          exp_chunk<kBf16>(sr, c, -m_ref, pk, l);
+          tmem_st_32x32b_x16(s_addr, pk);
+        }
+        tc_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&sm->p_full[slot]));
       }
-      if (t_mine < nt) {
-        tc_fence_after();
-        // this warp's S: columns [64 t + 32 g, +32) of the slot; its P goes over the first 16
-        const uint32_t s_addr = tmem + lane_base + 128 * slot + 64 * t_mine + 32 * g;
-        uint32_t sr[32], pk[16];
-        tmem_ld_32x32b_x32(s_addr, sr);
-        tc_wait_ld();
-        if (lane == 0 && !(warp & 1)) BSA_TR(2 + (warp >> 1), u, 1);
-        const float zmax = max_chunk(sr) * c;
-        m_true = fmaxf(m_true, zmax);
-        float alpha = 1.f;
-        bool rescale = false;
-        if (m_ref == -INFINITY) {
-          m_ref = zmax;  // first tile of this lane: O and l are still zero
-        } else if (zmax > m_ref + kRescaleThreshold) {
-          alpha = ex2_approx(m_ref - zmax);
-          l *= alpha;
-          m_ref = zmax;
-          rescale = true;
+      if (!ok) break;
+
+      // publish this item's (m, l) of the warp's lanes; the slots of item i-2 must have been read
+      if (i >= 2) ok = mbar_wait_warp(smem_u32(&sm->o_free[par]), ((i - 2) >> 1) & 1, abort_flag);
+      if (!ok) break;
+      sm->mref[par][g][lane_row] = m_ref;
+      sm->lsum[par][g][lane_row] = l;
+      sm->mtrue[par][g][lane_row] = m_true;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&sm->stats_full[par]));
+    }
+    if (!ok) fwd_give_up(sm, p.status, kFailSoftmax);
+  } else {
+    // =========================== write-out ===========================
+    // Merges the four partial results of every query row (key groups 0/1 x lanes r / r+64).  A warp
+    // reads both accumulators of its own lanes from TMEM; lanes 64..127 hand their weighted rows
+    // to lanes 0..63 through shared memory.  The named barriers below are always executed, also
+    // after a give-up, so that no warp of this role can be left waiting at one.
+    const int quarter = warp & 3;  // lane quarter a warp may touch = its index mod 4
+    const int t_mine = quarter >> 1;
+    const int lane_row = quarter * 32 + lane;
+    const int r_blk = (quarter & 1) * 32 + lane;  // row of the query block
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    bool ok = true;
+    for (int i = 0, w = blockIdx.x; w < p.items; ++i, w += stride) {
+      const FwdItem it = fwd_item(w, p);
+      const int par = i & 1;
+      if (ok) ok = mbar_wait_warp_idle(smem_u32(&sm->stats_full[par]), (i >> 1) & 1, abort_flag, 256);
+      if (ok) ok = mbar_wait_warp(smem_u32(&sm->list_full[par]), (i >> 1) & 1, abort_flag);
+      const int n_tiles = ok ? *const_cast<volatile int*>(&sm->ntiles[par]) : 0;
+      if (ok) ok = mbar_wait_warp(smem_u32(&sm->o_full[par]), (i >> 1) & 1, abort_flag);
+      float acc[64];
+      float m_all = -INFINITY, l_all = 0.f, mt = -INFINITY;
+      if (ok) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          m_all = fmaxf(m_all, sm->mref[par][j & 1][r_blk + 64 * (j >> 1)]);
+          mt = fmaxf(mt, sm->mtrue[par][j & 1][r_blk + 64 * (j >> 1)]);
         }
-        if (__any_sync(0xffffffffu, rescale)) {
-          // This warp's O must hold the previous superstep's product (u >= 1 here) first: P V of
-          // superstep u-1 completing frees that superstep's stage.  S_u being complete implies
-          // P V of u-3 and earlier are complete, and P V of u+3 cannot complete before this warp
-          // delivers P_u, so the awaited phase is unambiguous.
-          ok = mbar_wait_warp(smem_u32(&sm->kv_empty[(u - 1) % kFwdStages]),
-                              ((u - 1) / kFwdStages) & 1, abort_flag);
-          if (!ok) break;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float mi = sm->mref[par][j & 1][r_blk + 64 * (j >> 1)];
+          if (mi != -INFINITY)
+            l_all += ex2_approx(mi - m_all) * sm->lsum[par][j & 1][r_blk + 64 * (j >> 1)];
+        }
+        const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+        const float m0 = sm->mref[par][0][lane_row], m1 = sm->mref[par][1][lane_row];
+        const float w0 = m0 == -INFINITY ? 0.f : ex2_approx(m0 - m_all) * inv;
+        const float w1 = m1 == -INFINITY ? 0.f : ex2_approx(m1 - m_all) * inv;
+        if (n_tiles > 0) {  // warp-uniform; accumulators were written by every superstep
           tc_fence_after();
 #pragma unroll
           for (int part = 0; part < 2; ++part) {
-            uint32_t orow[32];
-            tmem_ld_32x32b_x32(o_addr + 32 * part, orow);
+            uint32_t a0[32], a1[32];
+            tmem_ld_32x32b_x32(tmem + lane_base + kTmemO + 128 * par + 32 * part, a0);
+            tmem_ld_32x32b_x32(tmem + lane_base + kTmemO + 128 * par + 64 + 32 * part, a1);
             tc_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              orow[i] = __float_as_uint(__uint_as_float(orow[i]) * alpha);
-            tmem_st_32x32b_x32(o_addr + 32 * part, orow);
+            for (int j = 0; j < 32; ++j)
+              acc[32 * part + j] = fmaf(__uint_as_float(a1[j]), w1, __uint_as_float(a0[j]) * w0);
           }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 64; ++j) acc[j] = 0.f;
         }
-        exp_chunk<kBf16>(sr, c, -m_ref, pk, l);
-        if (lane == 0 && !(warp & 1)) BSA_TR(2 + (warp >> 1), u, 2);
-        tmem_st_32x32b_x16(s_addr, pk);
-        tc_wait_st();
-        tc_fence_before();
+        if (t_mine == 1) {
+#pragma unroll
+          for (int j = 0; j < 64; ++j) sm->xfer[j][r_blk] = acc[j];
+        }
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&sm->p_full[slot]));
-      if (lane == 0 && !(warp & 1)) BSA_TR(2 + (warp >> 1), u, 3);
-    }
-
-    // ---- epilogue: merge the four partial results of every query row ----
-    // (key groups 0/1 x lanes r / r + 64).  A warp reads both accumulators of its own lanes
-    // straight from TMEM; only the hand-over from lanes 64..127 to lanes 0..63 goes through
-    // shared memory (the K/V ring, dead once the last P V is complete).
-    if (ok && n_super > 0)
-      ok = mbar_wait_warp(smem_u32(&sm->kv_empty[(n_super - 1) % kFwdStages]),
-                          ((n_super - 1) / kFwdStages) & 1, abort_flag);
-    if (!ok) fwd_give_up(sm, p.status, kFailSoftmax);
-    if (threadIdx.x == 0) BSA_TR(6, 1, 0);
-    sm->mref[g][lane_row] = m_ref;
-    sm->lsum[g][lane_row] = l;
-    sm->mtrue[g][lane_row] = m_true;
-    named_barrier_sync(1, 256);  // every softmax warp arrives at each of these, also after a give-up
-    const bool live = !*abort_flag;
-    if (threadIdx.x == 0) BSA_TR(6, 1, 1);
-    float m_all = -INFINITY;
+      named_barrier_sync(2, 128);
+      if (ok && t_mine == 0) {
+        const int row = it.mb * 64 + r_blk;
+        uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.o) + it.b * p.o_sb +
+                                              it.h * p.o_sh + static_cast<int64_t>(row) * p.o_sn);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) m_all = fmaxf(m_all, sm->mref[i & 1][r_blk + 64 * (i >> 1)]);
-    float l_all = 0.f;
+        for (int v4 = 0; v4 < 8; ++v4) {
+          uint32_t pkd[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float mi = sm->mref[i & 1][r_blk + 64 * (i >> 1)];
-      if (mi != -INFINITY) l_all += ex2_approx(mi - m_all) * sm->lsum[i & 1][r_blk + 64 * (i >> 1)];
-    }
-    const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
-    // weights of this lane's two accumulator rows; this warp merges columns [32 g, +32) of both
-    const float m0 = sm->mref[0][lane_row], m1 = sm->mref[1][lane_row];
-    const float w0 = m0 == -INFINITY ? 0.f : ex2_approx(m0 - m_all) * inv;
-    const float w1 = m1 == -INFINITY ? 0.f : ex2_approx(m1 - m_all) * inv;
-    float acc[32];
-    if (live && n_super > 0) {  // warp-uniform
-      uint32_t a0[32], a1[32];
-      tc_fence_after();
-      tmem_ld_32x32b_x32(tmem + lane_base + kTmemO + 32 * g, a0);
-      tmem_ld_32x32b_x32(tmem + lane_base + kTmemO + 64 + 32 * g, a1);
-      tc_wait_ld();
-#pragma unroll
-      for (int i = 0; i < 32; ++i)
-        acc[i] = fmaf(__uint_as_float(a1[i]), w1, __uint_as_float(a0[i]) * w0);
-    } else {
-#pragma unroll
-      for (int i = 0; i < 32; ++i) acc[i] = 0.f;
-    }
-    if (t_mine == 1) {
-#pragma unroll
-      for (int i = 0; i < 32; ++i) sm->u.xfer[32 * g + i][r_blk] = acc[i];
-    }
-    named_barrier_sync(1, 256);
-    if (threadIdx.x == 0) BSA_TR(6, 1, 2);
-    if (t_mine == 0 && live) {
-      uint32_t packed[16];
-#pragma unroll
-      for (int i = 0; i < 32; i += 2)
-        packed[i / 2] = pack_2x16<kBf16>(acc[i] + sm->u.xfer[32 * g + i][r_blk],
-                                         acc[i + 1] + sm->u.xfer[32 * g + i + 1][r_blk]);
-      uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.o) + b * p.o_sb + h * p.o_sh +
-                                            static_cast<int64_t>(row) * p.o_sn + 32 * g);
-#pragma unroll
-      for (int i = 0; i < 4; ++i)
-        dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
-      if (g == 0) {
-        const int64_t ri = (static_cast<int64_t>(b) * p.H + h) * p.N + row;
+          for (int j = 0; j < 4; ++j) {
+            const int col = 8 * v4 + 2 * j;
+            pkd[j] = pack_2x16<kBf16>(acc[col] + sm->xfer[col][r_blk],
+                                      acc[col + 1] + sm->xfer[col + 1][r_blk]);
+          }
+          dst[v4] = make_uint4(pkd[0], pkd[1], pkd[2], pkd[3]);
+        }
+        const int64_t ri = (static_cast<int64_t>(it.b) * p.H + it.h) * p.N + row;
         p.lse2[ri] = l_all > 0.f ? m_all + lg2_approx(l_all) : -INFINITY;
-        if (p.rowmax)
-          p.rowmax[ri] = fmaxf(fmaxf(sm->mtrue[0][r_blk], sm->mtrue[1][r_blk]),
-                               fmaxf(sm->mtrue[0][r_blk + 64], sm->mtrue[1][r_blk + 64]));
+        if (p.rowmax) p.rowmax[ri] = mt;
       }
+      named_barrier_sync(2, 128);  // xfer may be overwritten by the next item now
+      __syncwarp();
+      if (ok && lane == 0) mbar_arrive(smem_u32(&sm->o_free[par]));
     }
-    if (threadIdx.x == 0) BSA_TR(6, 1, 3);
+    if (!ok) fwd_give_up(sm, p.status, kFailOut);
   }
 
   // ---- tear-down: every role arrives here, also after a give-up ----
   tc_fence_before();
   __syncthreads();
-  if (warp == 9) {
+  if (warp == kSWarp) {
     __syncwarp();
     tc_fence_after();
     tmem_dealloc(tmem, kFwdTmemCols);
   }
-  if (threadIdx.x == 0) BSA_TR(6, 2, 0);
   if (threadIdx.x == 0) BSA_TR_CTA(1, global_timer_ns());
 }
 
@@ -489,10 +561,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
 #ifdef BSA_TRACE
 extern "C" int bsa_debug_copy_cta_times(unsigned long long* host) {
-  return cudaMemcpyFromSymbol(host, bsa::g_bsa_cta_times, sizeof(bsa::g_bsa_cta_times)) == cudaSuccess ? 0 : -5;
-}
-extern "C" int bsa_debug_copy_trace(long long* host) {
-  return cudaMemcpyFromSymbol(host, bsa::g_bsa_trace, sizeof(bsa::g_bsa_trace)) == cudaSuccess ? 0 : -5;
+  return cudaMemcpyFromSymbol(host, bsa::g_bsa_cta_times, sizeof(bsa::g_bsa_cta_times)) ==
+                 cudaSuccess
+             ? 0
+             : -5;
 }
 #endif
 
@@ -544,14 +616,17 @@ static int launch_fwd(const void* q, const int64_t q_strides[4], const void* k,
   prm.nb = nb;
   prm.list_b_stride = list_b_stride;
   prm.list_h_stride = list_h_stride;
+  prm.items = B * H * nb;
   prm.scale_log2 = sm_scale * 1.4426950408889634f;
   prm.status = status;
+  int sms = 0;
+  if ((rc = sm_count(&sms)) != BSA_OK) return rc;
 
   const size_t smem_bytes = sizeof(FwdSmem) + 1024;
   auto kern = dtype == BSA_BF16 ? attn_fwd_kernel<true> : attn_fwd_kernel<false>;
   if ((rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes)) != BSA_OK)
     return rc;
-  const dim3 grid(static_cast<unsigned>(B * H * nb));
+  const dim3 grid(static_cast<unsigned>(prm.items < sms ? prm.items : sms));  // one CTA per SM
   kern<<<grid, kFwdThreads, smem_bytes, static_cast<cudaStream_t>(stream)>>>(tm_q, tm_k, tm_v, prm);
   if (cudaGetLastError() != cudaSuccess) return BSA_ERR_CUDA;
   return BSA_OK;

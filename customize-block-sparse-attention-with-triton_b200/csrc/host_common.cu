@@ -29,6 +29,20 @@ int check_qkv_operand(const void* p, const int64_t s[4]) {
   return BSA_OK;
 }
 
+int sm_count(int* out) {
+  static std::atomic<int> cached[64];
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) return BSA_ERR_CUDA;
+  int n = (dev >= 0 && dev < 64) ? cached[dev].load(std::memory_order_relaxed) : 0;
+  if (n <= 0) {
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+      return BSA_ERR_CUDA;
+    if (dev >= 0 && dev < 64) cached[dev].store(n, std::memory_order_relaxed);
+  }
+  *out = n;
+  return BSA_OK;
+}
+
 int ensure_dynamic_smem(const void* kernel, size_t bytes) {
   // a handful of kernels x devices: a small fixed table guarded by a spin flag is enough
   struct Entry { const void* k; int dev; };

@@ -27,6 +27,9 @@ int check_qkv_operand(const void* p, const int64_t s[4]);
 int make_qkv_tmap(CUtensorMap* out, const void* base, const int64_t s[4], int B, int H, int N,
                   int dtype, int box_rows);
 
+// Number of SMs of the current device (cached per device).
+int sm_count(int* out);
+
 // Raises a kernel's dynamic shared-memory limit; done once per (kernel, device) and remembered.
 int ensure_dynamic_smem(const void* kernel, size_t bytes);
 

@@ -119,6 +119,28 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity,
   return __all_sync(0xffffffffu, ok);
 }
 
+// Same, for roles that wait for a long time (a whole work item): sleeps between polls so that the
+// waiting warp does not take issue slots from the working warps of its sub-partition.
+__device__ __forceinline__ bool mbar_wait_warp_idle(uint32_t bar, uint32_t parity,
+                                                    volatile int* abort_flag, unsigned sleep_ns) {
+  bool ok = true;
+  if (!mbar_try_wait(bar, parity)) {
+    uint64_t t0 = 0;
+    uint32_t spins = 0;
+    while (true) {
+      __nanosleep(sleep_ns);
+      if (mbar_try_wait(bar, parity)) break;
+      if ((++spins & 63u) == 0u) {
+        if (*abort_flag) { ok = false; break; }
+        const uint64_t now = global_timer_ns();
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > BSA_WAIT_LIMIT_NS) { ok = false; break; }
+      }
+    }
+  }
+  return __all_sync(0xffffffffu, ok);
+}
+
 // Bounded wait of a whole warp until a shared-memory counter (written by another warp after a
 // __threadfence_block) reaches `target`.  Same give-up rules as mbar_wait.
 __device__ __forceinline__ bool flag_wait_warp(const int* flag, int target,
