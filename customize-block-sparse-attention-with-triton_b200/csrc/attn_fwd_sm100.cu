@@ -14,13 +14,14 @@
 //                 TMA-loads Q (twice) and only the listed K/V tiles into a 4-deep ring of
 //                 superstages (2 K tiles + 2 V tiles each)
 //   warp 9      : S issuer and TMEM owner — S = [Q;Q] [K_a;K_b]^T as four M=128,N=128,K=16 MMAs
-//                 into one of 2 TMEM slots (lanes 0..63 use columns 0..63, lanes 64..127 columns
+//                 into one of 3 TMEM slots (lanes 0..63 use columns 0..63, lanes 64..127 columns
 //                 64..127; an N=128 instruction occupies the tensor pipe no longer than an N=64 one)
 //   warp 10     : P V issuer — O[g] += P_a[:, keys of group g] V_a[..] + P_b[:, keys of group g] V_b[..]
 //                 for key group g in {0,1}, P read from TMEM, V an MN-major smem operand.  Lanes
 //                 64..127 store zeros where tile a's P lives and lanes 0..63 where tile b's does,
 //                 so row r of an accumulator only sums tile-a products and row r+64 only tile-b
-//                 products.  Accumulators are double-buffered by item parity.
+//                 products.  The first P V of an item waits until the previous item is written out;
+//                 the softmax warps meanwhile work ahead through the S slots.
 //   warps 0..7  : online softmax.  Warp w works on TMEM lane quarter w % 4 and key group g = w / 4
 //                 (keys [32 g, +32) of its tile): tcgen05.ld of S, exp2, P written back over the
 //                 warp's own S columns as 16-bit, lazy rescale of its own accumulator rows.  No
@@ -43,12 +44,12 @@
 namespace bsa {
 
 constexpr int kFwdStages = 4;   // superstages (2 K + 2 V tiles) in flight in shared memory
-constexpr int kFwdSlots = 2;    // S/P supertiles (128 TMEM columns) in flight
+constexpr int kFwdSlots = 3;    // S/P supertiles (128 TMEM columns) in flight
 constexpr int kFwdThreads = 480;
 constexpr int kSoftmaxWarps = 8, kProducerWarp = 8, kSWarp = 9, kPvWarp = 10, kOutWarp0 = 11;
 constexpr uint32_t kTileBytes = 64 * 64 * 2;       // one Q, K or V tile
 constexpr uint32_t kFwdTmemCols = 512;
-constexpr uint32_t kTmemO = 256;   // accumulator of item parity a, key group g at 256 + 128 a + 64 g
+constexpr uint32_t kTmemO = 384;   // accumulator of key group g at 384 + 64 g; slot r at 128 r
 constexpr float kRescaleThreshold = 8.0f;
 constexpr int kFwdMaxTiles = 2048;  // key blocks per row that a CTA can list (N <= 131072)
 
@@ -304,7 +305,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         ok = mbar_wait_warp(smem_u32(&sm->kv_full[ss]), (gs / kFwdStages) & 1, abort_flag);
         if (!ok) break;
         if (gs >= kFwdSlots) {
-          // the slot still holds P of superstep gs-2 until that superstep's P V is complete
+          // the slot still holds P of superstep gs-3 until that superstep's P V is complete
           const int gp = gs - kFwdSlots;
           ok = mbar_wait_warp(smem_u32(&sm->kv_empty[gp % kFwdStages]), (gp / kFwdStages) & 1,
                               abort_flag);
@@ -337,8 +338,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (!ok) break;
       const int n_tiles = *const_cast<volatile int*>(&sm->ntiles[par]);
       const int n_super = (n_tiles + 1) >> 1;
-      // the accumulators of this parity are free once item i-2 has been written out
-      if (i >= 2) ok = mbar_wait_warp(smem_u32(&sm->o_free[par]), ((i - 2) >> 1) & 1, abort_flag);
+      // the accumulators are free once the previous item has been written out; the softmax warps
+      // meanwhile work ahead through the three S slots
+      if (i >= 1)
+        ok = mbar_wait_warp(smem_u32(&sm->o_free[par ^ 1]), ((i - 1) >> 1) & 1, abort_flag);
       if (!ok) break;
       if (n_super == 0) {
         if (leader) mbar_arrive(smem_u32(&sm->o_full[par]));
@@ -360,7 +363,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                   desc_v0 + static_cast<uint64_t>((ss * 2 + t) * (kTileBytes >> 4));
 #pragma unroll
               for (int k2 = 0; k2 < 2; ++k2)
-                umma_ts(tmem + kTmemO + 128 * par + 64 * g,
+                umma_ts(tmem + kTmemO + 64 * g,
                         tmem + 128 * slot + 64 * t + 32 * g + 8 * k2, desc_v + 128 * (2 * g + k2),
                         idesc_pv, (u > 0) || (t > 0) || (k2 > 0));
             }
@@ -387,7 +390,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (!ok) break;
       const int n_tiles = *const_cast<volatile int*>(&sm->ntiles[par]);
       const int n_super = (n_tiles + 1) >> 1;
-      const uint32_t o_addr = tmem + lane_base + kTmemO + 128 * par + 64 * g;
+      const uint32_t o_addr = tmem + lane_base + kTmemO + 64 * g;
       float m_ref = -INFINITY, m_true = -INFINITY, l = 0.f;
 
       for (int u = 0; u < n_super; ++u, ++gs) {
@@ -424,7 +427,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           if (__any_sync(0xffffffffu, rescale)) {
             // This warp's O rows must hold the previous superstep's product (u >= 1 here) first:
             // P V of superstep gs-1 completing frees that superstep's stage.  S of superstep gs
-            // being complete implies P V of gs-2 and earlier are complete, and P V of gs+3 cannot
+            // being complete implies P V of gs-3 and earlier are complete, and P V of gs+3 cannot
             // complete before this warp delivers P of gs, so the awaited phase is unambiguous.
             ok = mbar_wait_warp(smem_u32(&sm->kv_empty[(gs - 1) % kFwdStages]),
                                 ((gs - 1) / kFwdStages) & 1, abort_flag);
@@ -503,8 +506,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
           for (int part = 0; part < 2; ++part) {
             uint32_t a0[32], a1[32];
-            tmem_ld_32x32b_x32(tmem + lane_base + kTmemO + 128 * par + 32 * part, a0);
-            tmem_ld_32x32b_x32(tmem + lane_base + kTmemO + 128 * par + 64 + 32 * part, a1);
+            tmem_ld_32x32b_x32(tmem + lane_base + kTmemO + 32 * part, a0);
+            tmem_ld_32x32b_x32(tmem + lane_base + kTmemO + 64 + 32 * part, a1);
             tc_wait_ld();
 #pragma unroll
             for (int j = 0; j < 32; ++j)
