@@ -60,6 +60,7 @@ struct FwdSmem {
   float xfer[64][65];                         // write-out: lanes 64..127 hand over, [col][row]
   int32_t cols[2][kFwdMaxTiles];              // by item parity: the item's key-block list
   int ntiles[2];
+  int item[2];                                // by item parity: the work item, -1 = no more work
   float mref[2][2][128];                      // by item parity, key group, lane
   float lsum[2][2][128];
   float mtrue[2][2][128];
@@ -90,6 +91,7 @@ struct FwdParams {
   int items;                // B * H * nb
   float scale_log2;
   int32_t* status;
+  int32_t* ticket;          // optional work counter (0 at kernel start, left 0): dynamic item hand-out
 };
 
 enum FwdFail : int { kFailProducer = 1, kFailMma = 2, kFailSoftmax = 3, kFailOut = 4 };
@@ -205,13 +207,35 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     bool ok = true;
     int gs = 0;  // supersteps issued so far by this CTA (ring position)
     int qi = 0;  // non-empty items so far (Q buffer position)
-    for (int i = 0, w = blockIdx.x; ok && w < p.items; ++i, w += stride) {
-      const FwdItem it = fwd_item(w, p);
+    for (int i = 0, w = blockIdx.x; ok; ++i) {
       const int par = i & 1;
+      if (i > 0) {
+        // next item: the following ticket when items are handed out dynamically, else a fixed stride
+        if (p.ticket != nullptr) {
+          int t = 0;
+          if (lane == 0) {
+            t = atomicAdd(p.ticket, 1);
+            // every CTA draws until its first ticket past the end, so the launch draws exactly
+            // `items` tickets in all; whoever draws the last one leaves the counter at zero
+            if (t == p.items - 1) atomicExch(p.ticket, 0);
+          }
+          w = stride + __shfl_sync(0xffffffffu, t, 0);
+        } else {
+          w += stride;
+        }
+      }
       // the list buffer (and the tile count) of item i-2 must have been read by everyone
       if (i >= 2)
         ok = mbar_wait_warp_idle(smem_u32(&sm->o_free[par]), ((i - 2) >> 1) & 1, abort_flag, 128);
       if (!ok) break;
+      if (w >= p.items) {
+        if (lane == 0) {
+          sm->item[par] = -1;
+          mbar_arrive(smem_u32(&sm->list_full[par]));
+        }
+        break;
+      }
+      const FwdItem it = fwd_item(w, p);
       int32_t* cols = sm->cols[par];
       int n_tiles = 0;
       if (p.block != nullptr) {
@@ -244,6 +268,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       __syncwarp();
       if (lane == 0) {
         sm->ntiles[par] = n_tiles;
+        sm->item[par] = w;
         mbar_arrive(smem_u32(&sm->list_full[par]));  // release: count and list are visible
       }
       const int n_super = (n_tiles + 1) >> 1;
@@ -287,10 +312,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const uint64_t desc_k0 = smem_desc_sw128(smem_u32(sm->k[0][0]), 16, 1024);
     bool ok = true;
     int gs = 0, qi = 0;
-    for (int i = 0, w = blockIdx.x; ok && w < p.items; ++i, w += stride) {
+    for (int i = 0; ok; ++i) {
       const int par = i & 1;
       ok = mbar_wait_warp(smem_u32(&sm->list_full[par]), (i >> 1) & 1, abort_flag);
       if (!ok) break;
+      if (*const_cast<volatile int*>(&sm->item[par]) < 0) break;  // no more work
       const int n_tiles = *const_cast<volatile int*>(&sm->ntiles[par]);
       const int n_super = (n_tiles + 1) >> 1;
       if (n_super == 0) continue;
@@ -332,10 +358,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const uint64_t desc_v0 = smem_desc_sw128(smem_u32(sm->v[0][0]), 8192, 1024);
     bool ok = true;
     int gs = 0;
-    for (int i = 0, w = blockIdx.x; ok && w < p.items; ++i, w += stride) {
+    for (int i = 0; ok; ++i) {
       const int par = i & 1;
       ok = mbar_wait_warp(smem_u32(&sm->list_full[par]), (i >> 1) & 1, abort_flag);
       if (!ok) break;
+      if (*const_cast<volatile int*>(&sm->item[par]) < 0) break;  // no more work
       const int n_tiles = *const_cast<volatile int*>(&sm->ntiles[par]);
       const int n_super = (n_tiles + 1) >> 1;
       // the accumulators are free once the previous item has been written out; the softmax warps
@@ -384,10 +411,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const float c = p.scale_log2;
     bool ok = true;
     int gs = 0;
-    for (int i = 0, w = blockIdx.x; ok && w < p.items; ++i, w += stride) {
+    for (int i = 0; ok; ++i) {
       const int par = i & 1;
       ok = mbar_wait_warp(smem_u32(&sm->list_full[par]), (i >> 1) & 1, abort_flag);
       if (!ok) break;
+      if (*const_cast<volatile int*>(&sm->item[par]) < 0) break;  // no more work
       const int n_tiles = *const_cast<volatile int*>(&sm->ntiles[par]);
       const int n_super = (n_tiles + 1) >> 1;
       const uint32_t o_addr = tmem + lane_base + kTmemO + 64 * g;
@@ -468,20 +496,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     // =========================== write-out ===========================
     // Merges the four partial results of every query row (key groups 0/1 x lanes r / r+64).  A warp
     // reads both accumulators of its own lanes from TMEM; lanes 64..127 hand their weighted rows
-    // to lanes 0..63 through shared memory.  The named barriers below are always executed, also
-    // after a give-up, so that no warp of this role can be left waiting at one.
+    // to lanes 0..63 through shared memory.  Both named barriers of an iteration are always
+    // executed, also after a give-up, and the second one carries the give-up vote, so that no warp
+    // of this role can be left waiting at one.
     const int quarter = warp & 3;  // lane quarter a warp may touch = its index mod 4
     const int t_mine = quarter >> 1;
     const int lane_row = quarter * 32 + lane;
     const int r_blk = (quarter & 1) * 32 + lane;  // row of the query block
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
     bool ok = true;
-    for (int i = 0, w = blockIdx.x; w < p.items; ++i, w += stride) {
-      const FwdItem it = fwd_item(w, p);
+    for (int i = 0;; ++i) {
       const int par = i & 1;
-      if (ok) ok = mbar_wait_warp_idle(smem_u32(&sm->stats_full[par]), (i >> 1) & 1, abort_flag, 256);
-      if (ok) ok = mbar_wait_warp(smem_u32(&sm->list_full[par]), (i >> 1) & 1, abort_flag);
+      ok = mbar_wait_warp_idle(smem_u32(&sm->list_full[par]), (i >> 1) & 1, abort_flag, 256);
+      const int w = ok ? *const_cast<volatile int*>(&sm->item[par]) : 0;
+      if (w < 0) break;  // no more work: the same for all four warps
+      const FwdItem it = fwd_item(w, p);
       const int n_tiles = ok ? *const_cast<volatile int*>(&sm->ntiles[par]) : 0;
+      if (ok) ok = mbar_wait_warp_idle(smem_u32(&sm->stats_full[par]), (i >> 1) & 1, abort_flag, 256);
       if (ok) ok = mbar_wait_warp(smem_u32(&sm->o_full[par]), (i >> 1) & 1, abort_flag);
       float acc[64];
       float m_all = -INFINITY, l_all = 0.f, mt = -INFINITY;
@@ -542,9 +573,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         p.lse2[ri] = l_all > 0.f ? m_all + lg2_approx(l_all) : -INFINITY;
         if (p.rowmax) p.rowmax[ri] = mt;
       }
-      named_barrier_sync(2, 128);  // xfer may be overwritten by the next item now
+      // xfer may be overwritten by the next item now; all four warps leave together if any gave up
+      const bool any_failed = named_barrier_or(2, 128, !ok);
       __syncwarp();
       if (ok && lane == 0) mbar_arrive(smem_u32(&sm->o_free[par]));
+      if (any_failed) break;
     }
     if (!ok) fwd_give_up(sm, p.status, kFailOut);
   }
@@ -579,7 +612,7 @@ static int launch_fwd(const void* q, const int64_t q_strides[4], const void* k,
                       const int32_t* row_ptr, const int32_t* col_idx, const uint8_t* block,
                       const int64_t* block_strides, int list_b_stride, int list_h_stride,
                       float sm_scale, int dtype, int B, int H, int N, int D, int32_t* status,
-                      void* stream) {
+                      int32_t* ticket, void* stream) {
   if (B <= 0 || H <= 0 || N <= 0 || (N % kBlock) != 0 || D != kHeadDim) return BSA_ERR_BAD_SHAPE;
   if (dtype != BSA_F16 && dtype != BSA_BF16) return BSA_ERR_BAD_DTYPE;
   if (!lse2 || (block == nullptr && (!row_ptr || !col_idx))) return BSA_ERR_BAD_POINTER;
@@ -622,6 +655,7 @@ static int launch_fwd(const void* q, const int64_t q_strides[4], const void* k,
   prm.items = B * H * nb;
   prm.scale_log2 = sm_scale * 1.4426950408889634f;
   prm.status = status;
+  prm.ticket = ticket;
   int sms = 0;
   if ((rc = sm_count(&sms)) != BSA_OK) return rc;
 
@@ -642,11 +676,11 @@ extern "C" int bsa_attn_fwd(const void* q, const int64_t q_strides[4], const voi
                             void* o, const int64_t o_strides[4], float* lse2, float* rowmax,
                             const int32_t* row_ptr, const int32_t* col_idx, int list_b_stride,
                             int list_h_stride, float sm_scale, int dtype, int B, int H, int N,
-                            int D, int32_t* status, void* stream) {
+                            int D, int32_t* work_counter, int32_t* status, void* stream) {
   if (!row_ptr || !col_idx) return BSA_ERR_BAD_POINTER;
   return bsa::launch_fwd(q, q_strides, k, k_strides, v, v_strides, o, o_strides, lse2, rowmax,
                          row_ptr, col_idx, nullptr, nullptr, list_b_stride, list_h_stride, sm_scale,
-                         dtype, B, H, N, D, status, stream);
+                         dtype, B, H, N, D, status, work_counter, stream);
 }
 
 extern "C" int bsa_attn_fwd_block_mask(const void* q, const int64_t q_strides[4], const void* k,
@@ -655,12 +689,13 @@ extern "C" int bsa_attn_fwd_block_mask(const void* q, const int64_t q_strides[4]
                                        const int64_t o_strides[4], float* lse2, float* rowmax,
                                        const uint8_t* block, const int64_t block_strides[4],
                                        int Bm, int Hm, float sm_scale, int dtype, int B, int H,
-                                       int N, int D, int32_t* status, void* stream) {
+                                       int N, int D, int32_t* work_counter, int32_t* status,
+                                       void* stream) {
   if (!block || !block_strides) return BSA_ERR_BAD_POINTER;
   if ((Bm != 1 && Bm != B) || (Hm != 1 && Hm != H)) return BSA_ERR_BAD_SHAPE;
   for (int i = 0; i < 4; ++i)
     if (block_strides[i] < 0) return BSA_ERR_BAD_STRIDE;
   return bsa::launch_fwd(q, q_strides, k, k_strides, v, v_strides, o, o_strides, lse2, rowmax,
                          nullptr, nullptr, block, block_strides, Bm > 1 ? 1 : 0, Hm > 1 ? 1 : 0,
-                         sm_scale, dtype, B, H, N, D, status, stream);
+                         sm_scale, dtype, B, H, N, D, status, work_counter, stream);
 }

@@ -72,5 +72,5 @@ extern "C" int bsa_attn_fwd_block_mask_static(
   if (rc != BSA_OK) return rc;
   return bsa_attn_fwd(q, q_strides, k, k_strides, v, v_strides, o, o_strides, lse2, nullptr,
                       row_ptr, col_idx, Bm > 1 ? Hm : 0, Hm > 1 ? 1 : 0, sm_scale, dtype, B, H, N,
-                      D, nullptr, stream);
+                      D, nullptr, nullptr, stream);
 }

@@ -42,9 +42,9 @@ SIGNATURES = {
     "bsa_tile_list_sizes": [_i, _i, _i, ctypes.POINTER(ListSizes)],
     "bsa_tile_lists_build": [_vp, _s4, _i, _i, _i] + [_vp] * 10 + [_vp],
     "bsa_attn_fwd": [_vp, _s4, _vp, _s4, _vp, _s4, _vp, _s4, _vp, _vp, _vp, _vp, _i, _i, _f, _i,
-                     _i, _i, _i, _i, _vp, _vp],
+                     _i, _i, _i, _i, _vp, _vp, _vp],
     "bsa_attn_fwd_block_mask": [_vp, _s4, _vp, _s4, _vp, _s4, _vp, _s4, _vp, _vp, _vp, _s4, _i, _i,
-                                _f, _i, _i, _i, _i, _i, _vp, _vp],
+                                _f, _i, _i, _i, _i, _i, _vp, _vp, _vp],
     "bsa_attn_bwd_delta": [_vp, _vp, _s4, _vp, _i, _i, _i, _i, _i, _vp],
     "bsa_attn_bwd_dkdv": [_vp, _vp, _vp, _vp, _s4, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i,
                           _i, _i, _i, _i, _vp, _vp],

@@ -207,8 +207,32 @@ def check_status(status: torch.Tensor):
     """Synchronises the current stream and raises if a kernel's bounded wait gave up."""
     lib = _lib.load()
     with _on_device(status.device):
-        _lib.check("bsa_check_status", lib.bsa_check_status(
-            _lib.ptr(status), _lib.stream_ptr(status.device)))
+        try:
+            _lib.check("bsa_check_status", lib.bsa_check_status(
+                _lib.ptr(status), _lib.stream_ptr(status.device)))
+        except Exception:
+            # a kernel that gave up may have left its work counter part-way: start afresh
+            for key in [k for k in _work_counters if k[0] == status.device.index]:
+                del _work_counters[key]
+            raise
+
+
+# One zeroed int32 word per (device, stream) for the persistent forward kernel's dynamic hand-out
+# of query blocks.  The kernel leaves the word at zero, and calls on one stream cannot overlap, so
+# the word is allocated once and never touched from the host again.
+_work_counters = {}
+
+
+def _work_counter(device: torch.device, stream: int) -> Optional[torch.Tensor]:
+    key = (device.index, stream)
+    word = _work_counters.get(key)
+    if word is None:
+        if torch.cuda.is_current_stream_capturing():
+            return None  # no allocation inside a graph capture: fixed-stride hand-out instead
+        # zeroed on the stream that will use it, so no cross-stream ordering is needed
+        word = torch.zeros(1, dtype=torch.int32, device=device)
+        _work_counters[key] = word
+    return word
 
 
 def attention_forward(q, k, v, lists: TileLists, sm_scale: float, want_rowmax: bool = False,
@@ -223,11 +247,13 @@ def attention_forward(q, k, v, lists: TileLists, sm_scale: float, want_rowmax: b
     rowmax = torch.empty_like(lse2) if want_rowmax else None
     sb, sh = lists.list_strides(B, H)
     with _on_device(q.device):
+        stream = _lib.stream_ptr(q.device)
+        counter = _work_counter(q.device, stream.value or 0)
         _lib.check("bsa_attn_fwd", lib.bsa_attn_fwd(
             _lib.ptr(q), _lib.strides4(q), _lib.ptr(k), _lib.strides4(k), _lib.ptr(v),
             _lib.strides4(v), _lib.ptr(o), _lib.strides4(o), _lib.ptr(lse2), _lib.ptr(rowmax),
             _lib.ptr(lists.row_ptr), _lib.ptr(lists.col_idx), sb, sh, float(sm_scale),
-            _lib.dtype_code(q.dtype), B, H, N, D, _lib.ptr(status), _lib.stream_ptr(q.device)))
+            _lib.dtype_code(q.dtype), B, H, N, D, _lib.ptr(counter), _lib.ptr(status), stream))
     return o, lse2, rowmax
 
 
@@ -243,11 +269,13 @@ def attention_forward_masked(q, k, v, block_mask: torch.Tensor, sm_scale: float,
     lse2 = torch.empty((B, H, N), dtype=torch.float32, device=q.device)
     rowmax = torch.empty_like(lse2) if want_rowmax else None
     with _on_device(q.device):
+        stream = _lib.stream_ptr(q.device)
+        counter = _work_counter(q.device, stream.value or 0)
         _lib.check("bsa_attn_fwd_block_mask", lib.bsa_attn_fwd_block_mask(
             _lib.ptr(q), _lib.strides4(q), _lib.ptr(k), _lib.strides4(k), _lib.ptr(v),
             _lib.strides4(v), _lib.ptr(o), _lib.strides4(o), _lib.ptr(lse2), _lib.ptr(rowmax),
             _lib.ptr(m4), _lib.strides4(m4), m4.shape[0], m4.shape[1], float(sm_scale),
-            _lib.dtype_code(q.dtype), B, H, N, D, _lib.ptr(status), _lib.stream_ptr(q.device)))
+            _lib.dtype_code(q.dtype), B, H, N, D, _lib.ptr(counter), _lib.ptr(status), stream))
     return o, lse2, rowmax
 
 

@@ -114,6 +114,13 @@ int bsa_tile_lists_build(const uint8_t* block, const int64_t block_strides[4], i
  *             [Bm,Hm,nb,nb]; list_b_stride/list_h_stride give the list index of head (b,h) as
  *             b*list_b_stride + h*list_h_stride (0 for a broadcast axis).
  *   Rows of query blocks without any listed tile get o = 0 (the reference leaves them unwritten).
+ *   work_counter : optional int32 device word (may be NULL).  The kernel is persistent (one CTA
+ *             per SM); with a counter the CTAs draw query blocks from it as they become free, which
+ *             evens out rows of unequal length; without one every CTA walks a fixed stride of
+ *             query blocks.  The word must hold 0 when the kernel starts and holds 0 again when it
+ *             ends, so one zeroed word serves any number of calls that cannot overlap on the GPU
+ *             (calls on one stream); calls that may overlap need a word each.  After a kernel that
+ *             reported through `status`, zero the word again before reuse.
  *   status  : optional int32 device word (may be NULL); a non-zero value after the stream drains
  *             means a bounded wait inside the kernel gave up (see bsa_check_status).
  */
@@ -121,7 +128,8 @@ int bsa_attn_fwd(const void* q, const int64_t q_strides[4], const void* k,
                  const int64_t k_strides[4], const void* v, const int64_t v_strides[4], void* o,
                  const int64_t o_strides[4], float* lse2, float* rowmax, const int32_t* row_ptr,
                  const int32_t* col_idx, int list_b_stride, int list_h_stride, float sm_scale,
-                 int dtype, int B, int H, int N, int D, int32_t* status, void* stream);
+                 int dtype, int B, int H, int N, int D, int32_t* work_counter, int32_t* status,
+                 void* stream);
 
 /*
  * The same forward with the list building fused in: every CTA lists the kept key blocks of its own
@@ -136,8 +144,8 @@ int bsa_attn_fwd_block_mask(const void* q, const int64_t q_strides[4], const voi
                             const int64_t k_strides[4], const void* v, const int64_t v_strides[4],
                             void* o, const int64_t o_strides[4], float* lse2, float* rowmax,
                             const uint8_t* block, const int64_t block_strides[4], int Bm, int Hm,
-                            float sm_scale, int dtype, int B, int H, int N, int D, int32_t* status,
-                            void* stream);
+                            float sm_scale, int dtype, int B, int H, int N, int D,
+                            int32_t* work_counter, int32_t* status, void* stream);
 
 /*
  * delta[b,h,i] = sum_d o[b,h,i,d] * do[b,h,i,d] in fp32; replaces _attn_bwd_preprocess

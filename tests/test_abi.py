@@ -48,16 +48,16 @@ def test_shape_and_dtype_checks_come_before_any_cuda_call(lib):
     fake = ctypes.c_void_p(0x1000)
     # N not a multiple of 64 / D != 64
     args = [fake, s4, fake, s4, fake, s4, fake, s4, fake, None, fake, fake, 0, 0, 0.125]
-    assert lib.bsa_attn_fwd(*args, 0, 1, 1, 63, 64, None, None) == -1
-    assert lib.bsa_attn_fwd(*args, 0, 1, 1, 64, 128, None, None) == -1
-    assert lib.bsa_attn_fwd(*args, 7, 1, 1, 64, 64, None, None) == -2
+    assert lib.bsa_attn_fwd(*args, 0, 1, 1, 63, 64, None, None, None) == -1
+    assert lib.bsa_attn_fwd(*args, 0, 1, 1, 64, 128, None, None, None) == -1
+    assert lib.bsa_attn_fwd(*args, 7, 1, 1, 64, 64, None, None, None) == -2
     # innermost stride must be 1
     bad = (ctypes.c_int64 * 4)(64 * 64, 64 * 64, 64, 2)
     args2 = [fake, bad] + args[2:]
-    assert lib.bsa_attn_fwd(*args2, 0, 1, 1, 64, 64, None, None) == -3
+    assert lib.bsa_attn_fwd(*args2, 0, 1, 1, 64, 64, None, None, None) == -3
     # misaligned base pointer
     args3 = [ctypes.c_void_p(0x1004)] + args[1:]
-    assert lib.bsa_attn_fwd(*args3, 0, 1, 1, 64, 64, None, None) == -4
+    assert lib.bsa_attn_fwd(*args3, 0, 1, 1, 64, 64, None, None, None) == -4
     assert lib.bsa_mask_reduce(fake, s4, 1, 1, 100, fake, None, None) == -1
     assert lib.bsa_reorder(fake, fake, s4, fake, 1, 1, 10, 8, 2, 2, 2, 2, None) == -1  # F*H*W != T
     assert lib.bsa_reorder(fake, fake, s4, fake, 1, 1, 8, 8, 2, 2, 2, 3, None) == -2   # elem size

@@ -172,3 +172,30 @@ def test_baseline_sizes_against_gpu_fp32_reference(lib, N, p, dtype):
     # attention is linear in V: O(2V) == 2 O(V) up to output rounding
     o2, _, _ = attention_forward(q, k, (v.float() * 2).to(dtype), lists, 0.125)
     assert (o2.float() - 2 * o.float()).abs().max().item() <= 2e-2
+
+
+def test_work_counter_hand_out_equals_fixed_stride(lib):
+    """With a work counter the CTAs draw query blocks dynamically; the result must not depend on
+    who computes which block, and the counter must be back at zero for the next call."""
+    from fa2_custom_mask import _lib, fa2_custom_mask as host
+    B, H, N = 2, 8, 2048          # 512 query blocks: several per CTA
+    q, k, v = (t.cuda() for t in oracle.make_qkv(B, H, N, 64, seed=5, dtype=torch.float16))
+    mask = oracle.make_block_mask(B, H, N // 64, 0.3, seed=6, diagonal=False).cuda()
+    m4 = host._as_4d(host._as_bytes(mask))
+    counter = torch.zeros(1, dtype=torch.int32, device="cuda")
+    outs = []
+    for word in (None, counter, counter, counter):
+        o = torch.empty_like(q)
+        lse2 = torch.empty(B, H, N, dtype=torch.float32, device="cuda")
+        rc = lib.bsa_attn_fwd_block_mask(
+            _lib.ptr(q), _lib.strides4(q), _lib.ptr(k), _lib.strides4(k), _lib.ptr(v),
+            _lib.strides4(v), _lib.ptr(o), _lib.strides4(o), _lib.ptr(lse2), None, _lib.ptr(m4),
+            _lib.strides4(m4), B, H, 0.125, _lib.dtype_code(q.dtype), B, H, N, 64,
+            _lib.ptr(word), None, _lib.stream_ptr(q.device))
+        assert rc == 0
+        torch.cuda.synchronize()
+        assert int(counter.item()) == 0
+        outs.append((o, lse2))
+    for o, lse2 in outs[1:]:
+        assert torch.equal(o, outs[0][0]) and torch.equal(lse2, outs[0][1])
+    _compare(q.cpu(), k.cpu(), v.cpu(), mask.cpu(), 0.125, outs[1][0].float().cpu(), outs[1][1].cpu())
