@@ -43,33 +43,41 @@
 
 namespace bsa {
 
-constexpr int kFwdStages = 4;   // superstages (2 K + 2 V tiles) in flight in shared memory
-constexpr int kFwdSlots = 3;    // S/P supertiles (128 TMEM columns) in flight
+constexpr int kKStages = 3;     // K superstages (2 tiles) in flight: held from load to S complete
+constexpr int kVStages = 5;     // V superstages (2 tiles) in flight: held from load to P V complete
+constexpr int kSSlots = 2;      // S supertiles (128 TMEM columns): held from S issue to tcgen05.ld
 constexpr int kFwdThreads = 480;
 constexpr int kSoftmaxWarps = 8, kProducerWarp = 8, kSWarp = 9, kPvWarp = 10, kOutWarp0 = 11;
 constexpr uint32_t kTileBytes = 64 * 64 * 2;       // one Q, K or V tile
 constexpr uint32_t kFwdTmemCols = 512;
-constexpr uint32_t kTmemO = 384;   // accumulator of key group g at 384 + 64 g; slot r at 128 r
+// TMEM columns: S slot r at 128 r; accumulator of softmax team T at 256 + 64 T; P of team T at
+// 384 + 64 T (tile a's 64 keys as 32 columns of 16-bit pairs, then tile b's)
+constexpr uint32_t kTmemO = 256;
+constexpr uint32_t kTmemP = 384;
 constexpr float kRescaleThreshold = 8.0f;
 constexpr int kFwdMaxTiles = 2048;  // key blocks per row that a CTA can list (N <= 131072)
 
 struct FwdSmem {
   uint8_t q[2][2][kTileBytes];                // by item parity: the query block, twice
-  uint8_t k[kFwdStages][2][kTileBytes];
-  uint8_t v[kFwdStages][2][kTileBytes];
+  uint8_t k[kKStages][2][kTileBytes];
+  uint8_t v[kVStages][2][kTileBytes];
   float xfer[64][65];                         // write-out: lanes 64..127 hand over, [col][row]
   int32_t cols[2][kFwdMaxTiles];              // by item parity: the item's key-block list
   int ntiles[2];
   int item[2];                                // by item parity: the work item, -1 = no more work
-  float mref[2][2][128];                      // by item parity, key group, lane
+  float mref[2][2][128];                      // by item parity, softmax team, lane
   float lsum[2][2][128];
   float mtrue[2][2][128];
   uint64_t list_full[2];                      // producer -> everyone: list and tile count ready
   uint64_t q_full[2], q_free[2];
-  uint64_t kv_full[kFwdStages];
-  uint64_t kv_empty[kFwdStages];              // P V of the superstep done: stage and S slot free
-  uint64_t s_full[kFwdSlots];
-  uint64_t p_full[kFwdSlots];
+  uint64_t k_full[kKStages];
+  uint64_t k_empty[kKStages];                 // S of the superstep complete
+  uint64_t v_full[kVStages];
+  uint64_t v_empty[kVStages];                 // P V of the superstep complete
+  uint64_t s_full[kSSlots];
+  uint64_t s_free[kSSlots];                   // the four warps of the team have S in registers
+  uint64_t p_full[2];                         // by team: P of its current superstep stored
+  uint64_t p_free[2];                         // by team: P V of its latest superstep complete
   uint64_t o_full[2];                         // last P V of the item done
   uint64_t stats_full[2];                     // softmax warps published (m, l) of the item
   uint64_t o_free[2];                         // write-out done with accumulators/stats/list
@@ -175,13 +183,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_init(smem_u32(&sm->stats_full[i]), kSoftmaxWarps);
       mbar_init(smem_u32(&sm->o_free[i]), 4);  // one arrival per write-out warp
     }
-    for (int s = 0; s < kFwdStages; ++s) {
-      mbar_init(smem_u32(&sm->kv_full[s]), 1);
-      mbar_init(smem_u32(&sm->kv_empty[s]), 1);
+    for (int s = 0; s < kKStages; ++s) {
+      mbar_init(smem_u32(&sm->k_full[s]), 1);
+      mbar_init(smem_u32(&sm->k_empty[s]), 1);
     }
-    for (int i = 0; i < kFwdSlots; ++i) {
+    for (int s = 0; s < kVStages; ++s) {
+      mbar_init(smem_u32(&sm->v_full[s]), 1);
+      mbar_init(smem_u32(&sm->v_empty[s]), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&sm->s_full[i]), 1);
-      mbar_init(smem_u32(&sm->p_full[i]), kSoftmaxWarps);
+      mbar_init(smem_u32(&sm->s_free[i]), kSoftmaxWarps / 2);  // the four warps of one team
+      mbar_init(smem_u32(&sm->p_full[i]), kSoftmaxWarps / 2);
+      mbar_init(smem_u32(&sm->p_free[i]), 1);
     }
     sm->abort_flag = 0;
     mbar_fence_init();
@@ -284,21 +298,25 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
       ++qi;
       for (int u = 0; u < n_super; ++u, ++gs) {
-        const int ss = gs % kFwdStages;
+        const int ks = gs % kKStages, vs = gs % kVStages;
         const int nt = min(2, n_tiles - 2 * u);
         const int n0 = cols[2 * u];
         const int n1 = nt == 2 ? cols[2 * u + 1] : 0;
-        ok = mbar_wait_warp(smem_u32(&sm->kv_empty[ss]), ((gs / kFwdStages) & 1) ^ 1, abort_flag);
+        ok = mbar_wait_warp(smem_u32(&sm->k_empty[ks]), ((gs / kKStages) & 1) ^ 1, abort_flag);
         if (!ok) break;
         if (leader) {
-          const uint32_t bar = smem_u32(&sm->kv_full[ss]);
-          mbar_expect_tx(bar, 2 * kTileBytes * nt);
-          tma_load_4d(smem_u32(sm->k[ss][0]), &tm_k, bar, 0, n0 * 64, it.h, it.b);
-          tma_load_4d(smem_u32(sm->v[ss][0]), &tm_v, bar, 0, n0 * 64, it.h, it.b);
-          if (nt == 2) {
-            tma_load_4d(smem_u32(sm->k[ss][1]), &tm_k, bar, 0, n1 * 64, it.h, it.b);
-            tma_load_4d(smem_u32(sm->v[ss][1]), &tm_v, bar, 0, n1 * 64, it.h, it.b);
-          }
+          const uint32_t bar = smem_u32(&sm->k_full[ks]);
+          mbar_expect_tx(bar, kTileBytes * nt);
+          tma_load_4d(smem_u32(sm->k[ks][0]), &tm_k, bar, 0, n0 * 64, it.h, it.b);
+          if (nt == 2) tma_load_4d(smem_u32(sm->k[ks][1]), &tm_k, bar, 0, n1 * 64, it.h, it.b);
+        }
+        ok = mbar_wait_warp(smem_u32(&sm->v_empty[vs]), ((gs / kVStages) & 1) ^ 1, abort_flag);
+        if (!ok) break;
+        if (leader) {
+          const uint32_t bar = smem_u32(&sm->v_full[vs]);
+          mbar_expect_tx(bar, kTileBytes * nt);
+          tma_load_4d(smem_u32(sm->v[vs][0]), &tm_v, bar, 0, n0 * 64, it.h, it.b);
+          if (nt == 2) tma_load_4d(smem_u32(sm->v[vs][1]), &tm_v, bar, 0, n1 * 64, it.h, it.b);
         }
       }
     }
@@ -325,26 +343,24 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (!ok) break;
       const uint64_t desc_q = desc_q0 + static_cast<uint64_t>(qpar * ((2 * kTileBytes) >> 4));
       for (int u = 0; u < n_super; ++u, ++gs) {
-        const int ss = gs % kFwdStages;
-        const int slot = gs % kFwdSlots;
+        const int ks = gs % kKStages;
+        const int slot = gs & 1;
         const int nt = min(2, n_tiles - 2 * u);
-        ok = mbar_wait_warp(smem_u32(&sm->kv_full[ss]), (gs / kFwdStages) & 1, abort_flag);
+        ok = mbar_wait_warp(smem_u32(&sm->k_full[ks]), (gs / kKStages) & 1, abort_flag);
         if (!ok) break;
-        if (gs >= kFwdSlots) {
-          // the slot still holds P of superstep gs-3 until that superstep's P V is complete
-          const int gp = gs - kFwdSlots;
-          ok = mbar_wait_warp(smem_u32(&sm->kv_empty[gp % kFwdStages]), (gp / kFwdStages) & 1,
-                              abort_flag);
-          if (!ok) break;
-          tc_fence_after();
-        }
+        // the slot's previous S (superstep gs-2) must be in the softmax warps' registers; on the
+        // slot's first use this asks for the phase before the first one, which counts as complete
+        ok = mbar_wait_warp(smem_u32(&sm->s_free[slot]), ((gs >> 1) & 1) ^ 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
         if (leader) {
-          const uint64_t desc_k = desc_k0 + static_cast<uint64_t>(ss * ((2 * kTileBytes) >> 4));
+          const uint64_t desc_k = desc_k0 + static_cast<uint64_t>(ks * ((2 * kTileBytes) >> 4));
           const uint32_t idesc = nt == 2 ? idesc_s128 : idesc_s64;
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
             umma_ss(tmem + 128 * slot, desc_q + 2 * kk, desc_k + 2 * kk, idesc, kk > 0);
           tc_commit(smem_u32(&sm->s_full[slot]));
+          tc_commit(smem_u32(&sm->k_empty[ks]));
           if (u == n_super - 1) tc_commit(smem_u32(&sm->q_free[qpar]));  // Q buffer reusable
         }
       }
@@ -358,6 +374,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const uint64_t desc_v0 = smem_desc_sw128(smem_u32(sm->v[0][0]), 8192, 1024);
     bool ok = true;
     int gs = 0;
+    int kt[2] = {0, 0};  // supersteps taken by each softmax team so far
     for (int i = 0; ok; ++i) {
       const int par = i & 1;
       ok = mbar_wait_warp(smem_u32(&sm->list_full[par]), (i >> 1) & 1, abort_flag);
@@ -366,7 +383,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const int n_tiles = *const_cast<volatile int*>(&sm->ntiles[par]);
       const int n_super = (n_tiles + 1) >> 1;
       // the accumulators are free once the previous item has been written out; the softmax warps
-      // meanwhile work ahead through the three S slots
+      // meanwhile work ahead
       if (i >= 1)
         ok = mbar_wait_warp(smem_u32(&sm->o_free[par ^ 1]), ((i - 1) >> 1) & 1, abort_flag);
       if (!ok) break;
@@ -375,42 +392,59 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         continue;
       }
       for (int u = 0; u < n_super; ++u, ++gs) {
-        const int ss = gs % kFwdStages;
-        const int slot = gs % kFwdSlots;
+        const int vs = gs % kVStages;
+        const int team = u & 1;
         const int nt = min(2, n_tiles - 2 * u);
-        ok = mbar_wait_warp(smem_u32(&sm->p_full[slot]), (gs / kFwdSlots) & 1, abort_flag);
+        ok = mbar_wait_warp(smem_u32(&sm->v_full[vs]), (gs / kVStages) & 1, abort_flag);
+        if (!ok) break;
+        ok = mbar_wait_warp(smem_u32(&sm->p_full[team]), kt[team] & 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
         if (leader) {
-          // P of tile t sits over that tile's own S columns: keys [32 g + 16 k2, +16) of tile t at
-          // slot column 64 t + 32 g + 8 k2; the other half of the lanes holds zeros there
-          for (int g = 0; g < 2; ++g) {
-            for (int t = 0; t < nt; ++t) {
-              const uint64_t desc_v =
-                  desc_v0 + static_cast<uint64_t>((ss * 2 + t) * (kTileBytes >> 4));
+          // The supersteps of an item alternate between the two softmax teams (by u, so that the
+          // grouping of the sums does not depend on which CTA computes the item); each team has
+          // its own P buffer and accumulator, and its first superstep of an item (u = 0 or 1)
+          // starts the accumulator afresh.  Keys [16 kk, +16) of tile t sit at column 32 t + 8 kk
+          // of the P buffer; the other half of the lanes holds zeros there.
+          const uint32_t o_acc = tmem + kTmemO + 64 * team;
+          const uint32_t p_buf = tmem + kTmemP + 64 * team;
+          for (int t = 0; t < nt; ++t) {
+            const uint64_t desc_v = desc_v0 + static_cast<uint64_t>((vs * 2 + t) * (kTileBytes >> 4));
 #pragma unroll
-              for (int k2 = 0; k2 < 2; ++k2)
-                umma_ts(tmem + kTmemO + 64 * g,
-                        tmem + 128 * slot + 64 * t + 32 * g + 8 * k2, desc_v + 128 * (2 * g + k2),
-                        idesc_pv, (u > 0) || (t > 0) || (k2 > 0));
-            }
+            for (int kk = 0; kk < 4; ++kk)
+              umma_ts(o_acc, p_buf + 32 * t + 8 * kk, desc_v + 128 * kk, idesc_pv,
+                      (u > 1) || (t > 0) || (kk > 0));
           }
-          tc_commit(smem_u32(&sm->kv_empty[ss]));
+          tc_commit(smem_u32(&sm->v_empty[vs]));
+          tc_commit(smem_u32(&sm->p_free[team]));
           if (u == n_super - 1) tc_commit(smem_u32(&sm->o_full[par]));
         }
+        ++kt[team];
       }
     }
     if (!ok) fwd_give_up(sm, p.status, kFailMma);
   } else if (warp < kSoftmaxWarps) {
     // =========================== softmax ===========================
-    const int g = warp >> 2;          // key group: keys [32 g, +32) of the tile
+    const int team = warp >> 2;       // supersteps alternate between the two teams of four warps
     const int quarter = warp & 3;     // TMEM lane quarter this warp may touch
     const int t_mine = quarter >> 1;  // lanes 0..63 own tile a of a superstep, 64..127 tile b
     const int lane_row = quarter * 32 + lane;  // TMEM lane
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t o_addr = tmem + lane_base + kTmemO + 64 * team;
+    const uint32_t p_addr = tmem + lane_base + kTmemP + 64 * team + 32 * t_mine;
     const float c = p.scale_log2;
+    {
+      // P V of a tile sweeps all 128 lanes: the half of the lanes that does not own the tile holds
+      // zeros where that tile's P lives.  Nothing else ever writes there, so once is enough.
+      uint32_t z[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) z[j] = 0u;
+      tmem_st_32x32b_x32(tmem + lane_base + kTmemP + 64 * team + 32 * (1 - t_mine), z);
+      tc_wait_st();
+    }
     bool ok = true;
-    int gs = 0;
+    int gs = 0;  // supersteps of all items so far (S slot position)
+    int kt = 0;  // supersteps this team has taken so far (P buffer phase)
     for (int i = 0; ok; ++i) {
       const int par = i & 1;
       ok = mbar_wait_warp(smem_u32(&sm->list_full[par]), (i >> 1) & 1, abort_flag);
@@ -418,29 +452,35 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (*const_cast<volatile int*>(&sm->item[par]) < 0) break;  // no more work
       const int n_tiles = *const_cast<volatile int*>(&sm->ntiles[par]);
       const int n_super = (n_tiles + 1) >> 1;
-      const uint32_t o_addr = tmem + lane_base + kTmemO + 64 * g;
       float m_ref = -INFINITY, m_true = -INFINITY, l = 0.f;
 
       for (int u = 0; u < n_super; ++u, ++gs) {
-        const int slot = gs % kFwdSlots;
+        if ((u & 1) != team) continue;  // the other team's superstep
+        const int slot = gs & 1;
         const int nt = min(2, n_tiles - 2 * u);
-        ok = mbar_wait_warp(smem_u32(&sm->s_full[slot]), (gs / kFwdSlots) & 1, abort_flag);
+        ok = mbar_wait_warp(smem_u32(&sm->s_full[slot]), (gs >> 1) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
-        if (1 - t_mine < nt) {
-          // the other tile's P V also sweeps these lanes: give it zeros where that tile's P lives
-          uint32_t z[16];
-#pragma unroll
-          for (int j = 0; j < 16; ++j) z[j] = 0u;
-          tmem_st_32x32b_x16(tmem + lane_base + 128 * slot + 64 * (1 - t_mine) + 32 * g, z);
-        }
+        // this warp's S: columns [64 t, +64) of the slot
+        uint32_t sr[64], pk[32];
         if (t_mine < nt) {
-          // this warp's S: columns [64 t + 32 g, +32) of the slot; its P goes over the first 16
-          const uint32_t s_addr = tmem + lane_base + 128 * slot + 64 * t_mine + 32 * g;
-          uint32_t sr[32], pk[16];
+          const uint32_t s_addr = tmem + lane_base + 128 * slot + 64 * t_mine;
           tmem_ld_32x32b_x32(s_addr, sr);
+          tmem_ld_32x32b_x32(s_addr + 32, sr + 32);
           tc_wait_ld();
-          const float zmax = max_chunk(sr) * c;
+        }
+        // S is in registers: the slot may take the S of superstep gs+2
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&sm->s_free[slot]));
+        // The team's previous P V must be complete before its P buffer is overwritten (and before
+        // a rescale touches the accumulator).  It normally completed long ago: test now, so that
+        // the round trip to the barrier overlaps the arithmetic, and wait only if need be.
+        const uint32_t pfree_bar = smem_u32(&sm->p_free[team]);
+        const uint32_t pfree_par = (kt & 1) ^ 1;  // phase kt-1; passes at once for kt = 0
+        bool pfree = mbar_try_wait(pfree_bar, pfree_par);
+        if (t_mine < nt) {
+          const float zmax = fmaxf(max_chunk(sr), max_chunk(sr + 32)) * c;
           m_true = fmaxf(m_true, zmax);
           float alpha = 1.f;
           bool rescale = false;
@@ -453,13 +493,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             rescale = true;
           }
           if (__any_sync(0xffffffffu, rescale)) {
-            // This warp's O rows must hold the previous superstep's product (u >= 1 here) first:
-            // P V of superstep gs-1 completing frees that superstep's stage.  S of superstep gs
-            // being complete implies P V of gs-3 and earlier are complete, and P V of gs+3 cannot
-            // complete before this warp delivers P of gs, so the awaited phase is unambiguous.
-            ok = mbar_wait_warp(smem_u32(&sm->kv_empty[(gs - 1) % kFwdStages]),
-                                ((gs - 1) / kFwdStages) & 1, abort_flag);
-            if (!ok) break;
+            // this warp's O rows must hold the team's previous product first
+            if (!__all_sync(0xffffffffu, pfree)) {
+              ok = mbar_wait_warp(pfree_bar, pfree_par, abort_flag);
+              if (!ok) break;
+              pfree = true;
+            }
             tc_fence_after();
 #pragma unroll
             for (int part = 0; part < 2; ++part) {
@@ -473,21 +512,30 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             }
           }
           exp_chunk<kBf16>(sr, c, -m_ref, pk, l);
-          tmem_st_32x32b_x16(s_addr, pk);
+          exp_chunk<kBf16>(sr + 32, c, -m_ref, pk + 16, l);
+        }
+        if (!__all_sync(0xffffffffu, pfree)) {
+          ok = mbar_wait_warp(pfree_bar, pfree_par, abort_flag);
+          if (!ok) break;
+        }
+        if (t_mine < nt) {
+          tc_fence_after();
+          tmem_st_32x32b_x32(p_addr, pk);
         }
         tc_wait_st();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&sm->p_full[slot]));
+        if (lane == 0) mbar_arrive(smem_u32(&sm->p_full[team]));
+        ++kt;
       }
       if (!ok) break;
 
       // publish this item's (m, l) of the warp's lanes; the slots of item i-2 must have been read
       if (i >= 2) ok = mbar_wait_warp(smem_u32(&sm->o_free[par]), ((i - 2) >> 1) & 1, abort_flag);
       if (!ok) break;
-      sm->mref[par][g][lane_row] = m_ref;
-      sm->lsum[par][g][lane_row] = l;
-      sm->mtrue[par][g][lane_row] = m_true;
+      sm->mref[par][team][lane_row] = m_ref;
+      sm->lsum[par][team][lane_row] = l;
+      sm->mtrue[par][team][lane_row] = m_true;
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&sm->stats_full[par]));
     }
@@ -532,7 +580,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const float m0 = sm->mref[par][0][lane_row], m1 = sm->mref[par][1][lane_row];
         const float w0 = m0 == -INFINITY ? 0.f : ex2_approx(m0 - m_all) * inv;
         const float w1 = m1 == -INFINITY ? 0.f : ex2_approx(m1 - m_all) * inv;
-        if (n_tiles > 0) {  // warp-uniform; accumulators were written by every superstep
+        if (n_tiles > 0) {  // warp-uniform
+          // a team's accumulator holds this item's sums only if the team had a superstep in it
+          const bool live1 = n_tiles > 2;  // team 1 takes the odd supersteps
           tc_fence_after();
 #pragma unroll
           for (int part = 0; part < 2; ++part) {
@@ -541,8 +591,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             tmem_ld_32x32b_x32(tmem + lane_base + kTmemO + 64 + 32 * part, a1);
             tc_wait_ld();
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              acc[32 * part + j] = fmaf(__uint_as_float(a1[j]), w1, __uint_as_float(a0[j]) * w0);
+            for (int j = 0; j < 32; ++j) {
+              const float x0 = __uint_as_float(a0[j]) * w0;
+              acc[32 * part + j] = live1 ? fmaf(__uint_as_float(a1[j]), w1, x0) : x0;
+            }
           }
         } else {
 #pragma unroll
