@@ -45,9 +45,13 @@ namespace bsa {
 
 constexpr int kKStages = 3;     // K superstages (2 tiles) in flight: held from load to S complete
 constexpr int kVStages = 5;     // V superstages (2 tiles) in flight: held from load to P V complete
-constexpr int kSSlots = 2;      // S supertiles (128 TMEM columns): held from S issue to tcgen05.ld
-constexpr int kFwdThreads = 480;
-constexpr int kSoftmaxWarps = 8, kProducerWarp = 8, kSWarp = 9, kPvWarp = 10, kOutWarp0 = 11;
+constexpr int kSSlots = 2;      // S supertiles (128 TMEM columns), one per softmax team: held from
+                                // S issue to tcgen05.ld
+constexpr int kFwdThreads = 512;  // 16 warps x 128 registers = the whole register file
+constexpr int kSoftmaxWarps = 8, kProducerWarp = 8, kSWarp = 9, kPvWarp = 10, kOutWarp0 = 12;
+// registers per thread after re-allocation: softmax warps 0..7, warps 8..11, write-out warps 12..15
+constexpr int kRegsSoftmax = 152, kRegsIssue = 80, kRegsOut = 128;
+static_assert(256 * kRegsSoftmax + 128 * kRegsIssue + 128 * kRegsOut == 512 * 128, "register file");
 constexpr uint32_t kTileBytes = 64 * 64 * 2;       // one Q, K or V tile
 constexpr uint32_t kFwdTmemCols = 512;
 // TMEM columns: S slot r at 128 r; accumulator of softmax team T at 256 + 64 T; P of team T at
@@ -215,6 +219,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const uint32_t tmem = sm->tmem_base;
   volatile int* abort_flag = &sm->abort_flag;
 
+  // The softmax warps keep 64 logits and 32 packed probabilities per thread in registers and have
+  // nothing else on their sub-partition to hide a spill behind; the issuing warps need few.
+  // (Each role's code sits inside the branch that holds its warpgroup's re-allocation, so that
+  // the compiler allots the role that many registers.)
+  if (warp >= kSoftmaxWarps && warp < kOutWarp0) {
+  warpgroup_reg_release<kRegsIssue>();
   if (warp == kProducerWarp) {
     // =========================== producer ===========================
     const bool leader = elect_one();
@@ -330,6 +340,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const uint64_t desc_k0 = smem_desc_sw128(smem_u32(sm->k[0][0]), 16, 1024);
     bool ok = true;
     int gs = 0, qi = 0;
+    int kt0 = 0, kt1 = 0;  // supersteps issued for each softmax team so far
     for (int i = 0; ok; ++i) {
       const int par = i & 1;
       ok = mbar_wait_warp(smem_u32(&sm->list_full[par]), (i >> 1) & 1, abort_flag);
@@ -344,14 +355,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const uint64_t desc_q = desc_q0 + static_cast<uint64_t>(qpar * ((2 * kTileBytes) >> 4));
       for (int u = 0; u < n_super; ++u, ++gs) {
         const int ks = gs % kKStages;
-        const int slot = gs & 1;
+        const int slot = u & 1;  // the S slot of the softmax team whose superstep this is
         const int nt = min(2, n_tiles - 2 * u);
         ok = mbar_wait_warp(smem_u32(&sm->k_full[ks]), (gs / kKStages) & 1, abort_flag);
         if (!ok) break;
-        // the slot's previous S (superstep gs-2) must be in the softmax warps' registers; on the
-        // slot's first use this asks for the phase before the first one, which counts as complete
-        ok = mbar_wait_warp(smem_u32(&sm->s_free[slot]), ((gs >> 1) & 1) ^ 1, abort_flag);
+        // the team's previous S must be in its registers; on the slot's first use this asks for
+        // the phase before the first one, which counts as complete
+        const int kts = slot ? kt1 : kt0;
+        ok = mbar_wait_warp(smem_u32(&sm->s_free[slot]), (kts & 1) ^ 1, abort_flag);
         if (!ok) break;
+        if (slot) ++kt1; else ++kt0;
         tc_fence_after();
         if (leader) {
           const uint64_t desc_k = desc_k0 + static_cast<uint64_t>(ks * ((2 * kTileBytes) >> 4));
@@ -423,8 +436,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
     }
     if (!ok) fwd_give_up(sm, p.status, kFailMma);
+  }  // warp 11 only fills the warpgroup of the issuing warps
   } else if (warp < kSoftmaxWarps) {
     // =========================== softmax ===========================
+    warpgroup_reg_acquire<kRegsSoftmax>();
     const int team = warp >> 2;       // supersteps alternate between the two teams of four warps
     const int quarter = warp & 3;     // TMEM lane quarter this warp may touch
     const int t_mine = quarter >> 1;  // lanes 0..63 own tile a of a superstep, 64..127 tile b
@@ -456,9 +471,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
       for (int u = 0; u < n_super; ++u, ++gs) {
         if ((u & 1) != team) continue;  // the other team's superstep
-        const int slot = gs & 1;
+        // Every barrier a warp waits on is one whose every phase it sees (a parity wait cannot
+        // tell a phase from the one two before it): the S slot is the team's own.
+        const int slot = team;
         const int nt = min(2, n_tiles - 2 * u);
-        ok = mbar_wait_warp(smem_u32(&sm->s_full[slot]), (gs >> 1) & 1, abort_flag);
+        ok = mbar_wait_warp(smem_u32(&sm->s_full[slot]), kt & 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
         // this warp's S: columns [64 t, +64) of the slot
@@ -469,7 +486,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           tmem_ld_32x32b_x32(s_addr + 32, sr + 32);
           tc_wait_ld();
         }
-        // S is in registers: the slot may take the S of superstep gs+2
+        // S is in registers: the slot may take the team's next S
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&sm->s_free[slot]));
@@ -541,6 +558,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
     if (!ok) fwd_give_up(sm, p.status, kFailSoftmax);
   } else {
+    warpgroup_reg_release<kRegsOut>();
     // =========================== write-out ===========================
     // Merges the four partial results of every query row (key groups 0/1 x lanes r / r+64).  A warp
     // reads both accumulators of its own lanes from TMEM; lanes 64..127 hand their weighted rows

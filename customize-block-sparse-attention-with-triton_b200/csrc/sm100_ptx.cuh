@@ -26,6 +26,17 @@ __device__ __forceinline__ bool elect_one() {
 __device__ __forceinline__ int uniform_warp_index() {
   return __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
 }
+// Register re-allocation between warpgroups (four consecutive warps, all of which must execute
+// the same instruction): a warpgroup that needs few registers hands some back, one that needs
+// many takes them.  The counts must add up to what the CTA was launched with.
+template <int kRegs>
+__device__ __forceinline__ void warpgroup_reg_release() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+template <int kRegs>
+__device__ __forceinline__ void warpgroup_reg_acquire() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
 __device__ __forceinline__ void named_barrier_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
@@ -103,6 +114,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// The same test, but the hardware may park the thread for up to about `hint_ns` until the phase
+// completes instead of returning at once: a waiting warp then issues next to nothing.
+__device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+
 // Bounded wait.  Returns false when the wait gave up: either another role of this CTA raised
 // *abort_flag, or about BSA_WAIT_LIMIT_NS passed.  On give-up the caller records the code, raises
 // the flag and leaves through the normal tear-down path so TMEM is always released.
@@ -115,7 +140,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
   uint64_t t0 = 0;
   uint32_t spins = 0;
   while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait_parked(bar, parity, 2000u)) return true;
     if ((++spins & 255u) == 0u) {
       if (*abort_flag) return false;
       uint64_t now = global_timer_ns();
