@@ -458,7 +458,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tc_wait_st();
     }
     bool ok = true;
-    int gs = 0;  // supersteps of all items so far (S slot position)
     int kt = 0;  // supersteps this team has taken so far (P buffer phase)
     for (int i = 0; ok; ++i) {
       const int par = i & 1;
@@ -468,34 +467,36 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const int n_tiles = *const_cast<volatile int*>(&sm->ntiles[par]);
       const int n_super = (n_tiles + 1) >> 1;
       float m_ref = -INFINITY, m_true = -INFINITY, l = 0.f;
+      // Every barrier a warp waits on is one whose every phase it sees (a parity wait cannot tell a
+      // phase from the one two before it): the S slot is the team's own, phase = the team's count.
+      const uint32_t sfull_bar = smem_u32(&sm->s_full[team]);
+      const uint32_t s_addr = tmem + lane_base + 128 * team + 64 * t_mine;  // columns [64 t, +64)
+      uint32_t sr[64];
+      bool have_s = false;  // S of the coming superstep is already on its way into sr
 
-      for (int u = 0; u < n_super; ++u, ++gs) {
-        if ((u & 1) != team) continue;  // the other team's superstep
-        // Every barrier a warp waits on is one whose every phase it sees (a parity wait cannot
-        // tell a phase from the one two before it): the S slot is the team's own.
-        const int slot = team;
+      for (int u = team; u < n_super; u += 2) {
         const int nt = min(2, n_tiles - 2 * u);
-        ok = mbar_wait_warp(smem_u32(&sm->s_full[slot]), kt & 1, abort_flag);
-        if (!ok) break;
-        tc_fence_after();
-        // this warp's S: columns [64 t, +64) of the slot
-        uint32_t sr[64], pk[32];
-        if (t_mine < nt) {
-          const uint32_t s_addr = tmem + lane_base + 128 * slot + 64 * t_mine;
-          tmem_ld_32x32b_x32(s_addr, sr);
-          tmem_ld_32x32b_x32(s_addr + 32, sr + 32);
-          tc_wait_ld();
+        if (!have_s) {
+          ok = mbar_wait_warp(sfull_bar, kt & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          if (t_mine < nt) {
+            tmem_ld_32x32b_x32(s_addr, sr);
+            tmem_ld_32x32b_x32(s_addr + 32, sr + 32);
+          }
         }
+        tc_wait_ld();
         // S is in registers: the slot may take the team's next S
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&sm->s_free[slot]));
+        if (lane == 0) mbar_arrive(smem_u32(&sm->s_free[team]));
         // The team's previous P V must be complete before its P buffer is overwritten (and before
         // a rescale touches the accumulator).  It normally completed long ago: test now, so that
         // the round trip to the barrier overlaps the arithmetic, and wait only if need be.
         const uint32_t pfree_bar = smem_u32(&sm->p_free[team]);
         const uint32_t pfree_par = (kt & 1) ^ 1;  // phase kt-1; passes at once for kt = 0
         bool pfree = mbar_try_wait(pfree_bar, pfree_par);
+        uint32_t pk[32];
         if (t_mine < nt) {
           const float zmax = fmaxf(max_chunk(sr), max_chunk(sr + 32)) * c;
           m_true = fmaxf(m_true, zmax);
@@ -538,6 +539,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if (t_mine < nt) {
           tc_fence_after();
           tmem_st_32x32b_x32(p_addr, pk);
+        }
+        // While the P store drains: if the team's next S of this item is complete (it normally
+        // is), start loading it, so that its latency hides behind the store and the arrive.
+        have_s = false;
+        if (u + 2 < n_super) {
+          have_s = __all_sync(0xffffffffu, mbar_try_wait(sfull_bar, (kt + 1) & 1));
+          if (have_s) {
+            tc_fence_after();
+            if (t_mine < min(2, n_tiles - 2 * (u + 2))) {
+              tmem_ld_32x32b_x32(s_addr, sr);
+              tmem_ld_32x32b_x32(s_addr + 32, sr + 32);
+            }
+          }
         }
         tc_wait_st();
         tc_fence_before();
