@@ -1,41 +1,53 @@
 // Forward block-sparse attention for sm_100a.
 //
-// Persistent kernel: one CTA per SM walks a strided sequence of work items, each item being ONE
-// query block (64 rows) of one (batch, head) with its list of key blocks, taken two at a time
+// Persistent kernel: one CTA per SM.  A work item is ONE query block (64 rows) of one (batch, head)
+// with its list of key blocks; CTA c starts with item c and then draws further items from an
+// optional work counter (or walks a fixed stride).  The list is taken two key tiles at a time
 // ("supersteps").  The 64 query rows are loaded twice, as rows 0..63 and 64..127 of the tcgen05 A
 // operand, so that the 128 TMEM lanes split the two key tiles of a superstep between them: lanes
 // 0..63 own tile a, lanes 64..127 own tile b.  Every SM sub-partition (32 lanes) therefore always
 // has the same amount of exp2 work, whatever the sparsity pattern — the exponentials, not the
 // tensor pipe, bound this kernel at head dimension 64.
 //
-// Roles (15 warps); every role walks the same item sequence, so set-up of item i+1 and write-out
+// Roles (16 warps); every role walks the same item sequence, so set-up of item i+1 and write-out
 // of item i-1 overlap the arithmetic of item i:
-//   warp 8      : producer — lists the item's key blocks (from the mask row, or copies the CSR row),
-//                 TMA-loads Q (twice) and only the listed K/V tiles into a 4-deep ring of
-//                 superstages (2 K tiles + 2 V tiles each)
+//   warp 8      : producer — draws the item, lists its key blocks (from the mask row, or copies the
+//                 CSR row), TMA-loads Q (twice) and only the listed K/V tiles: K into a 3-deep ring
+//                 of superstages (held until S is complete), V into a 5-deep one (held until P V is)
 //   warp 9      : S issuer and TMEM owner — S = [Q;Q] [K_a;K_b]^T as four M=128,N=128,K=16 MMAs
-//                 into one of 3 TMEM slots (lanes 0..63 use columns 0..63, lanes 64..127 columns
-//                 64..127; an N=128 instruction occupies the tensor pipe no longer than an N=64 one)
-//   warp 10     : P V issuer — O[g] += P_a[:, keys of group g] V_a[..] + P_b[:, keys of group g] V_b[..]
-//                 for key group g in {0,1}, P read from TMEM, V an MN-major smem operand.  Lanes
-//                 64..127 store zeros where tile a's P lives and lanes 0..63 where tile b's does,
-//                 so row r of an accumulator only sums tile-a products and row r+64 only tile-b
-//                 products.  The first P V of an item waits until the previous item is written out;
-//                 the softmax warps meanwhile work ahead through the S slots.
-//   warps 0..7  : online softmax.  Warp w works on TMEM lane quarter w % 4 and key group g = w / 4
-//                 (keys [32 g, +32) of its tile): tcgen05.ld of S, exp2, P written back over the
-//                 warp's own S columns as 16-bit, lazy rescale of its own accumulator rows.  No
-//                 communication between these warps inside an item.
-//   warps 11..14: write-out — merge the four partial results (m, l, O) of every query row (key
-//                 groups 0/1 x lanes r / r+64), normalise, store O, LSE and the row maximum.
+//                 into the S slot of the softmax team whose superstep it is (lanes 0..63 use columns
+//                 0..63, lanes 64..127 columns 64..127; an N=128 instruction occupies the tensor
+//                 pipe no longer than an N=64 one)
+//   warp 10     : P V issuer — O[T] += P_a V_a + P_b V_b for the team T of the superstep, P read from
+//                 the team's P buffer in TMEM, V an MN-major shared-memory operand.  Lanes 64..127
+//                 hold zeros where tile a's P lives and lanes 0..63 where tile b's does, so row r of
+//                 an accumulator only sums tile-a products and row r+64 only tile-b products.  The
+//                 first P V of an item waits until the previous item is written out; the softmax
+//                 warps meanwhile work ahead.
+//   warps 0..7  : online softmax in two teams of four warps (team = warp / 4, TMEM lane quarter =
+//                 warp % 4).  The supersteps of an item alternate between the teams; each team has
+//                 its own S slot, P buffer, accumulator, and (m, l) per lane, so while one team does
+//                 its exponentials the other waits, loads or stores.  A warp loads its 64 S columns
+//                 (which frees the slot for the team's next S at once), takes the row maximum, exp2,
+//                 stores P as 16-bit, and rescales its own accumulator rows when the maximum moved.
+//   warps 12..15: write-out — merge the four partial results (m, l, O) of every query row (teams
+//                 0/1 x lanes r / r+64), normalise, store O, LSE and the row maximum.
+// Warpgroup register re-allocation gives the softmax warps 152 registers (they hold 64 logits and
+// 32 packed probabilities per thread and have nothing to hide a spill behind), the issuing warps 80.
+//
+// TMEM (512 columns): S slots 2 x 128, accumulators 2 x 64, P buffers 2 x 64.
 //
 // Numerics follow the reference's loop (fa2_custom_mask/fa2_fwd.py:150-196): logits scaled by
 // sm_scale*log2(e), exp2 domain, fp32 row sums of the fp32 probabilities, P rounded to the input
 // dtype before P V.  The running maximum is only advanced when it grew by more than 8 (a factor
-// 256), which leaves O = acc / l unchanged because both use the same reference maximum.
+// 256), which leaves O = acc / l unchanged because both use the same reference maximum.  Which
+// team takes which superstep depends on the item alone, so results do not depend on which CTA
+// computes an item.
 //
 // Every wait is bounded; a wait that gives up raises a CTA-wide flag, every role then falls
-// through its loops without touching barriers' data again, and TMEM is always released.
+// through its loops without touching barriers' data again, and TMEM is always released.  Every
+// barrier is waited on only by warps that see each of its phases (a parity wait cannot tell a
+// phase from the one two before it).
 #include <math.h>
 
 #include "host_common.h"
