@@ -211,6 +211,16 @@ def extra_measurements(dev, peak_tf, peak_gbs):
         gbs = N * N / (ms * 1e-3) / 1e9
         out[f"mask_reduce_N{N}"] = {"ms": ms, "GBps": gbs, "frac_of_measured_hbm": gbs / peak_gbs}
         del dense
+    # head-wise token reorder on the reference's own grid (13 x 30 x 45 image tokens), sized past L2
+    from fa2_custom_mask import apply_head_wise_reorder
+    Bv, Hv, Fv, Yv, Xv = 2, 48, 13, 30, 45
+    x = torch.randn(Bv, Hv, Fv * Yv * Xv, HEAD_DIM, device=dev, dtype=torch.float16)
+    orders = torch.tensor([[0, 1, 2], [0, 2, 1], [1, 0, 2], [1, 2, 0], [2, 0, 1], [2, 1, 0]],
+                          device=dev, dtype=torch.int32)[torch.arange(Hv, device=dev) % 6]
+    ms = timed(lambda: apply_head_wise_reorder(x, orders, Fv, Yv, Xv), 10)
+    gbs = 2 * x.numel() * x.element_size() / (ms * 1e-3) / 1e9
+    out["reorder_B2_H48_T17550_f16"] = {"ms": ms, "GBps": gbs, "frac_of_measured_hbm": gbs / peak_gbs}
+    del x
     return out
 
 

@@ -95,36 +95,54 @@ __device__ __forceinline__ int permuted_token(int t, int e0, int e1, int e2, int
 }
 
 constexpr int kReorderThreads = 256;
+constexpr int kReorderPieces = 4;  // independent loads in flight per thread
 
-// One thread moves one Vec-sized piece of one token row.  kInverse: the source grid has the
-// extents permuted by `orders`, and `inv_orders` lays the coordinates back out.
+// A CTA moves kReorderThreads * kReorderPieces Vec-sized pieces of the token rows of one
+// (batch, head) (blockIdx.y, strided if the grid's y extent is smaller than batch * heads): all
+// index arithmetic is 32-bit and the head's axis order is read once per CTA.  Every thread issues
+// its loads before its stores.  kInverse: the source grid has the extents permuted by `orders`,
+// and `inv_orders` lays the coordinates back out.
 template <typename Vec, bool kInverse>
 __global__ void __launch_bounds__(kReorderThreads)
 reorder_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, int64_t sb, int64_t sh,
                int64_t st, const int32_t* __restrict__ orders,
-               const int32_t* __restrict__ inv_orders, int heads, int T, int F, int Hh, int W,
-               int vec_per_row, int64_t total) {
-  const int64_t idx = static_cast<int64_t>(blockIdx.x) * kReorderThreads + threadIdx.x;
-  if (idx >= total) return;
-  const int piece = static_cast<int>(idx % vec_per_row);
-  const int64_t tok = idx / vec_per_row;
-  const int t = static_cast<int>(tok % T);
-  const int64_t bh = tok / T;
-  const int h = static_cast<int>(bh % heads);
-  const int64_t b = bh / heads;
-  int new_t;
-  const int o0 = __ldg(orders + 3 * h), o1 = __ldg(orders + 3 * h + 1),
-            o2 = __ldg(orders + 3 * h + 2);
-  if constexpr (!kInverse) {
-    new_t = permuted_token(t, F, Hh, W, o0, o1, o2);
-  } else {
-    const int e0 = pick3(o0, F, Hh, W), e1 = pick3(o1, F, Hh, W), e2 = pick3(o2, F, Hh, W);
-    new_t = permuted_token(t, e0, e1, e2, __ldg(inv_orders + 3 * h), __ldg(inv_orders + 3 * h + 1),
-                           __ldg(inv_orders + 3 * h + 2));
+               const int32_t* __restrict__ inv_orders, int heads, int n_bh, int T, int F, int Hh,
+               int W, int vec_per_row) {
+  const uint32_t per_head = static_cast<uint32_t>(T) * static_cast<uint32_t>(vec_per_row);
+  const uint32_t first = blockIdx.x * (kReorderThreads * kReorderPieces) + threadIdx.x;
+  for (int bh = blockIdx.y; bh < n_bh; bh += gridDim.y) {
+    const int h = bh % heads;
+    const int b = bh / heads;
+    const int o0 = __ldg(orders + 3 * h), o1 = __ldg(orders + 3 * h + 1),
+              o2 = __ldg(orders + 3 * h + 2);
+    int e0 = F, e1 = Hh, e2 = W, p0 = o0, p1 = o1, p2 = o2;
+    if constexpr (kInverse) {
+      e0 = pick3(o0, F, Hh, W);
+      e1 = pick3(o1, F, Hh, W);
+      e2 = pick3(o2, F, Hh, W);
+      p0 = __ldg(inv_orders + 3 * h);
+      p1 = __ldg(inv_orders + 3 * h + 1);
+      p2 = __ldg(inv_orders + 3 * h + 2);
+    }
+    const uint8_t* src = in + b * sb + h * sh;  // byte offsets
+    uint8_t* dst = out + b * sb + h * sh;
+    Vec val[kReorderPieces];
+    int64_t to[kReorderPieces];
+#pragma unroll
+    for (int i = 0; i < kReorderPieces; ++i) {
+      const uint32_t idx = first + i * kReorderThreads;
+      to[i] = -1;
+      if (idx < per_head) {
+        const int t = static_cast<int>(idx / static_cast<uint32_t>(vec_per_row));
+        const int piece = static_cast<int>(idx - static_cast<uint32_t>(t) * vec_per_row);
+        val[i] = *reinterpret_cast<const Vec*>(src + t * st + piece * sizeof(Vec));
+        to[i] = permuted_token(t, e0, e1, e2, p0, p1, p2) * st + piece * sizeof(Vec);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < kReorderPieces; ++i)
+      if (to[i] >= 0) *reinterpret_cast<Vec*>(dst + to[i]) = val[i];
   }
-  const int64_t base = b * sb + h * sh;  // byte offsets
-  const Vec val = *reinterpret_cast<const Vec*>(in + base + t * st + piece * sizeof(Vec));
-  *reinterpret_cast<Vec*>(out + base + new_t * st + piece * sizeof(Vec)) = val;
 }
 
 template <bool kInverse>
@@ -149,17 +167,20 @@ static int launch_reorder(const void* in, void* out, const int64_t s[4], const i
   while (vec > elem_bytes && !fits(vec)) vec >>= 1;
   if (!fits(vec)) return BSA_ERR_BAD_POINTER;
   const int vec_per_row = static_cast<int>(row_bytes / vec);
-  const int64_t total = static_cast<int64_t>(B) * heads * T * vec_per_row;
-  const int64_t blocks = (total + kReorderThreads - 1) / kReorderThreads;
-  if (blocks > 0x7fffffffLL) return BSA_ERR_TOO_LARGE;
+  const int64_t per_head = static_cast<int64_t>(T) * vec_per_row;
+  const int64_t n_bh = static_cast<int64_t>(B) * heads;
+  if (per_head > 0x7fffffffLL || n_bh > 0x7fffffffLL) return BSA_ERR_TOO_LARGE;
+  constexpr int kPerCta = kReorderThreads * kReorderPieces;
+  const dim3 g(static_cast<unsigned>((per_head + kPerCta - 1) / kPerCta),
+               static_cast<unsigned>(n_bh < 65535 ? n_bh : 65535));
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
   const uint8_t* pi = static_cast<const uint8_t*>(in);
   uint8_t* po = static_cast<uint8_t*>(out);
-  const unsigned g = static_cast<unsigned>(blocks);
 #define BSA_LAUNCH_REORDER(V)                                                                      \
   reorder_kernel<V, kInverse><<<g, kReorderThreads, 0, cs>>>(pi, po, sb, sh, st, orders,           \
-                                                             inv_orders, heads, T, F, Hh, W,       \
-                                                             vec_per_row, total)
+                                                             inv_orders, heads,                    \
+                                                             static_cast<int>(n_bh), T, F, Hh, W,  \
+                                                             vec_per_row)
   switch (vec) {
     case 16: BSA_LAUNCH_REORDER(uint4); break;
     case 8: BSA_LAUNCH_REORDER(uint2); break;
