@@ -191,7 +191,7 @@ def extra_measurements(dev, peak_tf, peak_gbs):
              ("fwd_bwd_cfg5_B2_H16_N16384_causal_p0.25_bf16", 2, 16, 16384, 0.25, torch.bfloat16, True, True)]
     for name, B, H, N, p, dtype, causal, with_bwd in specs:
         (q, k, v, do), m = problem(B, H, N, p, dtype, seed=len(name), causal=causal)
-        lists = build_tile_lists(m, want_q=with_bwd, want_k=with_bwd)
+        lists = build_tile_lists(m, want_csc=with_bwd)
         tiles = int(m.sum())
         iters = 20 if tiles < 100000 else 5
         ms = timed(lambda: attention_forward(q, k, v, lists, SM_SCALE), iters)

@@ -1,13 +1,20 @@
 // Backward block-sparse attention for sm_100a: one kernel template, two instantiations.
 //
-//   dK/dV (kDKDV = true):  a CTA owns a PAIR of key blocks (128 keys = 128 TMEM lanes), keeps K and
-//       V of the pair in shared memory and walks the pair's list of query blocks (key-pair lists):
-//         S^T = K Q_m^T, dP^T = V dO_m^T            (SS MMAs, M=128, N=64)
-//         P^T = exp2(S^T c - LSE2[q]), dS^T = P^T (dP^T - delta[q])   (one thread per key row)
-//         dV += P^T dO_m, dK += dS^T Q_m            (TS MMAs: A from TMEM, B MN-major from smem)
-//   dQ    (kDKDV = false): a CTA owns a PAIR of query blocks, keeps Q and dO of the pair resident
-//       and walks the query-pair lists:
-//         S = Q K_n^T, dP = dO V_n^T;  dS = exp2(S c - LSE2[row]) (dP - delta[row]);  dQ += dS K_n
+//   dK/dV (kDKDV = true):  a CTA owns ONE key block (64 keys), keeps its K and V in shared memory,
+//       each loaded twice (rows 0..63 and 64..127 of the tcgen05 A operands), and walks the
+//       block's list of query blocks (the column lists of the mask) two at a time ("supersteps"):
+//         S^T = [K;K] [Q_a;Q_b]^T, dP^T = [V;V] [dO_a;dO_b]^T   (SS MMAs, M=128, N=128)
+//       so that TMEM lanes 0..63 hold query tile a (columns 0..63) and lanes 64..127 query tile b
+//       (columns 64..127): every SM sub-partition has exponentials to do whatever the mask is.
+//         P^T = exp2(S^T c - LSE2[q]), dS^T = P^T (dP^T - delta[q])     (one thread per key row)
+//         dV += P^T_a dO_a + P^T_b dO_b,  dK += dS^T_a Q_a + dS^T_b Q_b (TS MMAs: A from TMEM, B
+//       MN-major from shared memory).  The half of the lanes that does not own a tile holds zeros
+//       where that tile's P^T / dS^T live, so lane r sums the tile-a products of key r and lane
+//       r+64 its tile-b products; the two are added when the block is written out.
+//   dQ    (kDKDV = false): a CTA owns one query block, keeps Q and dO resident (twice) and walks the
+//       row list of key blocks two at a time:
+//         S = [Q;Q] [K_a;K_b]^T, dP = [dO;dO] [V_a;V_b]^T;  dS = exp2(S c - LSE2[row]) (dP - delta[row]);
+//         dQ += dS_a K_a + dS_b K_b
 //
 // Formulas are those of the reference's backward (fa2_custom_mask/fa2_bwd.py:56-74, 116-130) with
 // M replaced by a true base-2 log-sum-exp; the iteration space is the tile lists, not the
@@ -16,8 +23,9 @@
 // Roles: warps 0..7 compute (lane quarter = warp % 4, column half = warp / 4), warp 8 TMA
 // producer, warp 9 issues the S/dP MMAs and owns TMEM, warp 10 issues the accumulating MMAs (two
 // issuers, so neither waits behind the other's barrier round trips; both run warp-wide with one
-// elected lane issuing).  A block of the pair that does not list the current step's tile stores
-// zeros for P/dS and skips the exponentials.
+// elected lane issuing).  S/dP are released as soon as the compute warps hold them in registers;
+// P^T/dS^T live in their own TMEM buffers until the accumulating MMAs that read them are complete.
+// Every wait is bounded and every barrier is waited on by warps that see each of its phases.
 #include <math.h>
 
 #include "host_common.h"
@@ -28,37 +36,38 @@ namespace bsa {
 constexpr int kBwdStages = 4;
 constexpr int kBwdThreads = 352;
 constexpr uint32_t kBwdTile = 64 * 64 * 2;
-constexpr uint32_t kBwdPairTile = 128 * 64 * 2;
 constexpr uint32_t kBwdTmemCols = 512;
-// TMEM columns: X0 = S (or S^T) x2, X1 = dP (or dP^T) x2, P x2 (16-bit), dS x2 (16-bit), two fp32
-// accumulators.
+// TMEM columns: X0 = S (or S^T), X1 = dP (or dP^T), 128 each (tile a in columns 0..63 of lanes
+// 0..63, tile b in columns 64..127 of lanes 64..127); P and dS as 16-bit pairs, 32 columns per
+// tile; two fp32 accumulators.
 constexpr uint32_t kTmX0 = 0, kTmX1 = 128, kTmP = 256, kTmDS = 320, kTmAcc0 = 384, kTmAcc1 = 448;
 
 struct BwdSmem {
-  uint8_t stat0[kBwdPairTile];
-  uint8_t stat1[kBwdPairTile];
-  uint8_t str0[kBwdStages][kBwdTile];
-  uint8_t str1[kBwdStages][kBwdTile];
-  float lse[kBwdStages][64];
-  float delta[kBwdStages][64];
+  uint8_t stat0[2][kBwdTile];               // the CTA's own block, twice: K (dK/dV) or Q (dQ)
+  uint8_t stat1[2][kBwdTile];               // V or dO, twice
+  uint8_t str0[kBwdStages][2][kBwdTile];    // streamed tiles a, b: Q (dK/dV) or K (dQ)
+  uint8_t str1[kBwdStages][2][kBwdTile];    // dO or V
+  float lse[kBwdStages][2][64];             // dK/dV: LSE2 and delta of the streamed query tiles
+  float delta[kBwdStages][2][64];
+  float xfer[2][64][65];                    // write-out: lanes 64..127 hand over, [acc][col][row]
   uint64_t stat_full;
   uint64_t in_full[kBwdStages];
-  uint64_t in_empty[kBwdStages];
-  uint64_t x_full[2];
-  uint64_t d_full[2];
+  uint64_t in_empty[kBwdStages];            // accumulating MMAs of the superstep complete
+  uint64_t x_full, x_free;                  // S/dP complete; S/dP in the compute warps' registers
+  uint64_t d_full, d_free;                  // P/dS stored; accumulating MMAs that read them complete
   uint32_t tmem_base;
   int abort_flag;
 };
 
 struct BwdParams {
-  const int32_t* pair_ptr;
-  const int32_t* pair_ent;
+  const int32_t* list_ptr;  // dK/dV: column lists (col_ptr/row_idx); dQ: row lists (row_ptr/col_idx)
+  const int32_t* list_idx;
   const float* lse2;
   const float* delta;
   void* out0;  // dV (dK/dV kernel only)
   void* out1;  // dK or dQ
   int64_t sb, sh, sn;
-  int B, H, N, npair;
+  int B, H, N, nb;
   int list_b_stride, list_h_stride;
   float scale_log2;
   float sm_scale;
@@ -70,17 +79,20 @@ __device__ __forceinline__ void bwd_give_up(BwdSmem* sm, int32_t* status, int co
   if (status) atomicCAS(status, 0, code);
 }
 
+// Stores 32 columns of one output row: (own[i] + other[i]) * scale as 16-bit.
 template <bool kBf16>
-__device__ __forceinline__ void store_half_row(void* base, int64_t elem_off, const uint32_t* acc,
-                                               float scale) {
+__device__ __forceinline__ void store_half_row(void* base, int64_t elem_off, const uint32_t* own,
+                                               const float* other, int other_stride, float scale) {
   uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(base) + elem_off);
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     uint32_t w[4];
 #pragma unroll
-    for (int t = 0; t < 4; ++t)
-      w[t] = pack_2x16<kBf16>(__uint_as_float(acc[8 * i + 2 * t]) * scale,
-                              __uint_as_float(acc[8 * i + 2 * t + 1]) * scale);
+    for (int t = 0; t < 4; ++t) {
+      const int c = 8 * i + 2 * t;
+      w[t] = pack_2x16<kBf16>((__uint_as_float(own[c]) + other[c * other_stride]) * scale,
+                              (__uint_as_float(own[c + 1]) + other[(c + 1) * other_stride]) * scale);
+    }
     dst[i] = make_uint4(w[0], w[1], w[2], w[3]);
   }
 }
@@ -98,15 +110,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
   const int warp = uniform_warp_index();
   const int lane = threadIdx.x & 31;
 
-  const int bh = blockIdx.x / p.npair;
+  const int bh = blockIdx.x / p.nb;
   // dQ: long (late) rows first; dK/dV: long (early) key columns first when the mask is causal
-  const int pr = kDKDV ? (blockIdx.x % p.npair) : (p.npair - 1 - (blockIdx.x % p.npair));
+  const int blk = kDKDV ? (blockIdx.x % p.nb) : (p.nb - 1 - (blockIdx.x % p.nb));
   const int b = bh / p.H;
   const int h = bh % p.H;
-  const int64_t li = static_cast<int64_t>(b * p.list_b_stride + h * p.list_h_stride) * p.npair + pr;
-  const int beg = __ldg(p.pair_ptr + li);
-  const int n_steps = __ldg(p.pair_ptr + li + 1) - beg;
-  const int32_t* ents = p.pair_ent + beg;
+  const int64_t li = static_cast<int64_t>(b * p.list_b_stride + h * p.list_h_stride) * p.nb + blk;
+  const int beg = __ldg(p.list_ptr + li);
+  const int n_tiles = __ldg(p.list_ptr + li + 1) - beg;
+  const int n_super = (n_tiles + 1) >> 1;
+  const int32_t* ents = p.list_idx + beg;
   const int64_t vec_base = (static_cast<int64_t>(b) * p.H + h) * p.N;  // into lse2 / delta
 
   if (threadIdx.x == 0) {
@@ -115,10 +128,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
       mbar_init(smem_u32(&sm->in_full[s]), 1);
       mbar_init(smem_u32(&sm->in_empty[s]), 1);
     }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(smem_u32(&sm->x_full[i]), 1);
-      mbar_init(smem_u32(&sm->d_full[i]), 8);  // one arrival per compute warp
-    }
+    mbar_init(smem_u32(&sm->x_full), 1);
+    mbar_init(smem_u32(&sm->x_free), 8);  // one arrival per compute warp
+    mbar_init(smem_u32(&sm->d_full), 8);
+    mbar_init(smem_u32(&sm->d_free), 1);
     sm->abort_flag = 0;
     mbar_fence_init();
   }
@@ -140,99 +153,114 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
 
   if (warp == 8) {
     // =========================== TMA producer ===========================
-    if (n_steps > 0) {
+    if (n_super > 0) {
       const bool leader = elect_one();
       if (leader) {
-        mbar_expect_tx(smem_u32(&sm->stat_full), 2 * kBwdPairTile);
-        tma_load_4d(smem_u32(sm->stat0), &tm_stat0, smem_u32(&sm->stat_full), 0, pr * 128, h, b);
-        tma_load_4d(smem_u32(sm->stat1), &tm_stat1, smem_u32(&sm->stat_full), 0, pr * 128, h, b);
+        const uint32_t bar = smem_u32(&sm->stat_full);
+        mbar_expect_tx(bar, 4 * kBwdTile);
+        tma_load_4d(smem_u32(sm->stat0[0]), &tm_stat0, bar, 0, blk * 64, h, b);
+        tma_load_4d(smem_u32(sm->stat0[1]), &tm_stat0, bar, 0, blk * 64, h, b);
+        tma_load_4d(smem_u32(sm->stat1[0]), &tm_stat1, bar, 0, blk * 64, h, b);
+        tma_load_4d(smem_u32(sm->stat1[1]), &tm_stat1, bar, 0, blk * 64, h, b);
       }
-      for (int j = 0; j < n_steps; ++j) {
+      for (int j = 0; j < n_super; ++j) {
         const int s = j % kBwdStages;
-        const uint32_t ph = (j / kBwdStages) & 1;
-        const int blk = __ldg(ents + j) >> 2;
-        if (!mbar_wait_warp(smem_u32(&sm->in_empty[s]), ph ^ 1, abort_flag)) {
+        const int nt = min(2, n_tiles - 2 * j);
+        const int n0 = __ldg(ents + 2 * j);
+        const int n1 = nt == 2 ? __ldg(ents + 2 * j + 1) : 0;
+        if (!mbar_wait_warp(smem_u32(&sm->in_empty[s]), ((j / kBwdStages) & 1) ^ 1, abort_flag)) {
           bwd_give_up(sm, p.status, 1);
           break;
         }
         if (leader) {
           const uint32_t bar = smem_u32(&sm->in_full[s]);
-          mbar_expect_tx(bar, 2 * kBwdTile + (kDKDV ? 512u : 0u));
-          tma_load_4d(smem_u32(sm->str0[s]), &tm_str0, bar, 0, blk * 64, h, b);
-          tma_load_4d(smem_u32(sm->str1[s]), &tm_str1, bar, 0, blk * 64, h, b);
+          mbar_expect_tx(bar, nt * (2 * kBwdTile + (kDKDV ? 512u : 0u)));
+          tma_load_4d(smem_u32(sm->str0[s][0]), &tm_str0, bar, 0, n0 * 64, h, b);
+          tma_load_4d(smem_u32(sm->str1[s][0]), &tm_str1, bar, 0, n0 * 64, h, b);
           if constexpr (kDKDV) {
-            bulk_load_1d(smem_u32(sm->lse[s]), p.lse2 + vec_base + blk * 64, 256, bar);
-            bulk_load_1d(smem_u32(sm->delta[s]), p.delta + vec_base + blk * 64, 256, bar);
+            bulk_load_1d(smem_u32(sm->lse[s][0]), p.lse2 + vec_base + n0 * 64, 256, bar);
+            bulk_load_1d(smem_u32(sm->delta[s][0]), p.delta + vec_base + n0 * 64, 256, bar);
+          }
+          if (nt == 2) {
+            tma_load_4d(smem_u32(sm->str0[s][1]), &tm_str0, bar, 0, n1 * 64, h, b);
+            tma_load_4d(smem_u32(sm->str1[s][1]), &tm_str1, bar, 0, n1 * 64, h, b);
+            if constexpr (kDKDV) {
+              bulk_load_1d(smem_u32(sm->lse[s][1]), p.lse2 + vec_base + n1 * 64, 256, bar);
+              bulk_load_1d(smem_u32(sm->delta[s][1]), p.delta + vec_base + n1 * 64, 256, bar);
+            }
           }
         }
       }
     }
   } else if (warp == 9) {
     // =========================== S / dP issuer ===========================
-    if (n_steps > 0) {
-      constexpr uint32_t idesc_x = umma_idesc(kBf16, 0, 0, 128, 64);
+    if (n_super > 0) {
+      constexpr uint32_t idesc_x128 = umma_idesc(kBf16, 0, 0, 128, 128);
+      constexpr uint32_t idesc_x64 = umma_idesc(kBf16, 0, 0, 128, 64);  // odd tail: one tile
       const bool leader = elect_one();
-      const uint64_t desc_a0 = smem_desc_sw128(smem_u32(sm->stat0), 16, 1024);
-      const uint64_t desc_a1 = smem_desc_sw128(smem_u32(sm->stat1), 16, 1024);
-      const uint64_t desc_b0 = smem_desc_sw128(smem_u32(sm->str0[0]), 16, 1024);
-      const uint64_t desc_b1 = smem_desc_sw128(smem_u32(sm->str1[0]), 16, 1024);
+      const uint64_t desc_a0 = smem_desc_sw128(smem_u32(sm->stat0[0]), 16, 1024);
+      const uint64_t desc_a1 = smem_desc_sw128(smem_u32(sm->stat1[0]), 16, 1024);
+      const uint64_t desc_b0 = smem_desc_sw128(smem_u32(sm->str0[0][0]), 16, 1024);
+      const uint64_t desc_b1 = smem_desc_sw128(smem_u32(sm->str1[0][0]), 16, 1024);
       bool ok = mbar_wait_warp(smem_u32(&sm->stat_full), 0, abort_flag);
-      for (int j = 0; ok && j < n_steps; ++j) {
+      for (int j = 0; ok && j < n_super; ++j) {
         const int s = j % kBwdStages;
-        const int buf = j & 1;
+        const int nt = min(2, n_tiles - 2 * j);
         ok = mbar_wait_warp(smem_u32(&sm->in_full[s]), (j / kBwdStages) & 1, abort_flag);
         if (!ok) break;
-        if (j >= 2) {
-          // buffer `buf` still feeds the accumulating MMAs of step j-2 (P, dS live there too)
-          const int jp = j - 2;
-          ok = mbar_wait_warp(smem_u32(&sm->in_empty[jp % kBwdStages]), (jp / kBwdStages) & 1,
-                              abort_flag);
-          if (!ok) break;
-          tc_fence_after();
-        }
+        // S/dP of the previous superstep must be in the compute warps' registers (for j = 0 this
+        // asks for the phase before the first one, which counts as complete)
+        ok = mbar_wait_warp(smem_u32(&sm->x_free), (j & 1) ^ 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
         if (leader) {
-          const uint64_t b0 = desc_b0 + static_cast<uint64_t>(s * (kBwdTile >> 4));
-          const uint64_t b1 = desc_b1 + static_cast<uint64_t>(s * (kBwdTile >> 4));
+          const uint64_t b0 = desc_b0 + static_cast<uint64_t>(s * ((2 * kBwdTile) >> 4));
+          const uint64_t b1 = desc_b1 + static_cast<uint64_t>(s * ((2 * kBwdTile) >> 4));
+          const uint32_t idesc = nt == 2 ? idesc_x128 : idesc_x64;
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            umma_ss(tmem + kTmX0 + 64 * buf, desc_a0 + 2 * kk, b0 + 2 * kk, idesc_x, kk > 0);
+            umma_ss(tmem + kTmX0, desc_a0 + 2 * kk, b0 + 2 * kk, idesc, kk > 0);
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            umma_ss(tmem + kTmX1 + 64 * buf, desc_a1 + 2 * kk, b1 + 2 * kk, idesc_x, kk > 0);
-          tc_commit(smem_u32(&sm->x_full[buf]));
+            umma_ss(tmem + kTmX1, desc_a1 + 2 * kk, b1 + 2 * kk, idesc, kk > 0);
+          tc_commit(smem_u32(&sm->x_full));
         }
       }
       if (!ok) bwd_give_up(sm, p.status, 2);
     }
   } else if (warp == 10) {
     // =========================== accumulating-MMA issuer ===========================
-    if (n_steps > 0) {
+    if (n_super > 0) {
       constexpr uint32_t idesc_acc = umma_idesc(kBf16, 0, 1, 128, 64);
       const bool leader = elect_one();
-      const uint64_t desc_m0 = smem_desc_sw128(smem_u32(sm->str0[0]), 8192, 1024);
-      const uint64_t desc_m1 = smem_desc_sw128(smem_u32(sm->str1[0]), 8192, 1024);
+      const uint64_t desc_m0 = smem_desc_sw128(smem_u32(sm->str0[0][0]), 8192, 1024);
+      const uint64_t desc_m1 = smem_desc_sw128(smem_u32(sm->str1[0][0]), 8192, 1024);
       bool ok = true;
-      for (int j = 0; ok && j < n_steps; ++j) {
+      for (int j = 0; ok && j < n_super; ++j) {
         const int s = j % kBwdStages;
-        const int buf = j & 1;
-        ok = mbar_wait_warp(smem_u32(&sm->d_full[buf]), (j >> 1) & 1, abort_flag);
+        const int nt = min(2, n_tiles - 2 * j);
+        ok = mbar_wait_warp(smem_u32(&sm->d_full), j & 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
         if (leader) {
-          const uint32_t acc_on = (j > 0) ? 1u : 0u;
-          if constexpr (kDKDV) {
-            const uint64_t bmn = desc_m1 + static_cast<uint64_t>(s * (kBwdTile >> 4));
+          // keys/queries [16 kk, +16) of tile t sit at column 32 t + 8 kk of the P / dS buffers
+          for (int t = 0; t < nt; ++t) {
+            const uint32_t first = (j > 0 || t > 0) ? 1u : 0u;
+            if constexpr (kDKDV) {
+              const uint64_t bmn = desc_m1 + static_cast<uint64_t>((2 * s + t) * (kBwdTile >> 4));
+#pragma unroll
+              for (int kk = 0; kk < 4; ++kk)
+                umma_ts(tmem + kTmAcc0, tmem + kTmP + 32 * t + 8 * kk, bmn + 128 * kk, idesc_acc,
+                        first | (kk > 0));
+            }
+            const uint64_t bmn = desc_m0 + static_cast<uint64_t>((2 * s + t) * (kBwdTile >> 4));
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk)
-              umma_ts(tmem + kTmAcc0, tmem + kTmP + 32 * buf + 8 * kk, bmn + 128 * kk, idesc_acc,
-                      acc_on | (kk > 0));
+              umma_ts(tmem + kTmAcc1, tmem + kTmDS + 32 * t + 8 * kk, bmn + 128 * kk, idesc_acc,
+                      first | (kk > 0));
           }
-          const uint64_t bmn = desc_m0 + static_cast<uint64_t>(s * (kBwdTile >> 4));
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk)
-            umma_ts(tmem + kTmAcc1, tmem + kTmDS + 32 * buf + 8 * kk, bmn + 128 * kk, idesc_acc,
-                    acc_on | (kk > 0));
-          tc_commit(smem_u32(&sm->in_empty[s]));  // stage free; X/P/dS buffer free; acc updated
+          tc_commit(smem_u32(&sm->in_empty[s]));  // stage free
+          tc_commit(smem_u32(&sm->d_free));       // P/dS buffers free; accumulators updated
         }
       }
       if (!ok) bwd_give_up(sm, p.status, 2);
@@ -240,42 +268,54 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
   } else {
     // =========================== compute warps ===========================
     const int quarter = warp & 3;
-    const int ch = warp >> 2;           // which 32 of the 64 tile columns
-    const int half = quarter >> 1;      // which block of the pair this row belongs to
-    const int row = pr * 128 + quarter * 32 + lane;
+    const int ch = warp >> 2;           // which 32 of the tile's 64 columns
+    const int t_mine = quarter >> 1;    // lanes 0..63 own tile a of a superstep, 64..127 tile b
+    const int r_blk = (quarter & 1) * 32 + lane;  // row of the CTA's block
+    const int row = blk * 64 + r_blk;
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
     const float c = p.scale_log2;
     float my_lse = 0.f, my_delta = 0.f;
     if constexpr (!kDKDV) {
-      if (row < p.N) {
-        my_lse = __ldg(p.lse2 + vec_base + row);
-        my_delta = __ldg(p.delta + vec_base + row);
-      }
+      my_lse = __ldg(p.lse2 + vec_base + row);
+      my_delta = __ldg(p.delta + vec_base + row);
     }
     bool ok = true;
-    int ent_next = n_steps > 0 ? __ldg(ents) : 0;
-    for (int j = 0; j < n_steps; ++j) {
-      const int ent = ent_next;
-      if (j + 1 < n_steps) ent_next = __ldg(ents + j + 1);
+    if (n_super > 0) {
+      // The accumulating MMAs of a tile sweep all 128 lanes: the half of the lanes that does not
+      // own the tile holds zeros where that tile's P / dS live.  Nothing else ever writes there.
+      uint32_t z[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) z[i] = 0u;
+      if constexpr (kDKDV) tmem_st_32x32b_x16(tmem + lane_base + kTmP + 32 * (1 - t_mine) + 16 * ch, z);
+      tmem_st_32x32b_x16(tmem + lane_base + kTmDS + 32 * (1 - t_mine) + 16 * ch, z);
+      tc_wait_st();
+    }
+    for (int j = 0; j < n_super; ++j) {
       const int s = j % kBwdStages;
-      const int buf = j & 1;
-      const bool listed = (ent >> half) & 1;
+      const int nt = min(2, n_tiles - 2 * j);
+      const bool active = t_mine < nt;  // warp-uniform
       if constexpr (kDKDV) {
         // the LSE2/delta vectors of this stage arrive through the async proxy
         ok = mbar_wait_warp(smem_u32(&sm->in_full[s]), (j / kBwdStages) & 1, abort_flag);
         if (!ok) break;
       }
-      ok = mbar_wait_warp(smem_u32(&sm->x_full[buf]), (j >> 1) & 1, abort_flag);
+      ok = mbar_wait_warp(smem_u32(&sm->x_full), j & 1, abort_flag);
       if (!ok) break;
       tc_fence_after();
+      uint32_t xs[32], xd[32];
+      if (active) {
+        tmem_ld_32x32b_x32(tmem + lane_base + kTmX0 + 64 * t_mine + 32 * ch, xs);
+        tmem_ld_32x32b_x32(tmem + lane_base + kTmX1 + 64 * t_mine + 32 * ch, xd);
+      }
+      tc_wait_ld();
+      // S/dP are in registers: the next superstep's may be issued
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&sm->x_free));
       uint32_t pk_p[16], pk_ds[16];
-      if (listed) {
-        uint32_t xs[32], xd[32];
-        tmem_ld_32x32b_x32(tmem + lane_base + kTmX0 + 64 * buf + 32 * ch, xs);
-        tmem_ld_32x32b_x32(tmem + lane_base + kTmX1 + 64 * buf + 32 * ch, xd);
-        tc_wait_ld();
-        const float4* lse4 = reinterpret_cast<const float4*>(&sm->lse[s][32 * ch]);
-        const float4* del4 = reinterpret_cast<const float4*>(&sm->delta[s][32 * ch]);
+      if (active) {
+        const float4* lse4 = reinterpret_cast<const float4*>(&sm->lse[s][t_mine][32 * ch]);
+        const float4* del4 = reinterpret_cast<const float4*>(&sm->delta[s][t_mine][32 * ch]);
 #pragma unroll
         for (int i = 0; i < 32; i += 4) {
           float l[4], d[4];
@@ -298,52 +338,59 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
           pk_ds[i / 2] = pack_2x16<kBf16>(dsv[0], dsv[1]);
           pk_ds[i / 2 + 1] = pack_2x16<kBf16>(dsv[2], dsv[3]);
         }
-      } else {
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          pk_p[i] = 0u;
-          pk_ds[i] = 0u;
-        }
       }
-      if constexpr (kDKDV) tmem_st_32x32b_x16(tmem + lane_base + kTmP + 32 * buf + 16 * ch, pk_p);
-      tmem_st_32x32b_x16(tmem + lane_base + kTmDS + 32 * buf + 16 * ch, pk_ds);
+      // the accumulating MMAs of the previous superstep still read the P/dS buffers
+      ok = mbar_wait_warp(smem_u32(&sm->d_free), (j & 1) ^ 1, abort_flag);
+      if (!ok) break;
+      if (active) {
+        tc_fence_after();
+        if constexpr (kDKDV) tmem_st_32x32b_x16(tmem + lane_base + kTmP + 32 * t_mine + 16 * ch, pk_p);
+        tmem_st_32x32b_x16(tmem + lane_base + kTmDS + 32 * t_mine + 16 * ch, pk_ds);
+      }
       tc_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&sm->d_full[buf]));
+      if (lane == 0) mbar_arrive(smem_u32(&sm->d_full));
     }
+    if (ok && n_super > 0)
+      ok = mbar_wait_warp(smem_u32(&sm->d_free), (n_super - 1) & 1, abort_flag);
+    if (!ok) bwd_give_up(sm, p.status, 3);
 
-    if (!ok) {
-      bwd_give_up(sm, p.status, 3);
-    } else {
-      if (n_steps > 0) {
-        ok = mbar_wait_warp(smem_u32(&sm->in_empty[(n_steps - 1) % kBwdStages]),
-                            ((n_steps - 1) / kBwdStages) & 1, abort_flag);
-        if (!ok) bwd_give_up(sm, p.status, 3);
-      }
-      if (ok) {
+    // ---- write-out: lane r holds the tile-a sums of row r, lane r+64 its tile-b sums ----
+    // The named barrier is executed by all eight compute warps, also after a give-up (every
+    // bounded wait of a warp still in the loop ends once the flag is up).
+    constexpr int kAccs = kDKDV ? 2 : 1;
+    if (ok && n_super > 0 && t_mine == 1) {
+      tc_fence_after();
+#pragma unroll
+      for (int a = 0; a < kAccs; ++a) {
         uint32_t acc[32];
-        const int64_t off = b * p.sb + h * p.sh + static_cast<int64_t>(row) * p.sn + 32 * ch;
-        if constexpr (kDKDV) {
-          if (n_steps > 0) {
-            tc_fence_after();
-            tmem_ld_32x32b_x32(tmem + lane_base + kTmAcc0 + 32 * ch, acc);
-            tc_wait_ld();
-          } else {
+        tmem_ld_32x32b_x32(tmem + lane_base + (kDKDV && a == 0 ? kTmAcc0 : kTmAcc1) + 32 * ch, acc);
+        tc_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) acc[i] = 0u;
-          }
-          if (row < p.N) store_half_row<kBf16>(p.out0, off, acc, 1.0f);
-        }
-        if (n_steps > 0) {
+        for (int i = 0; i < 32; ++i) sm->xfer[a][32 * ch + i][r_blk] = __uint_as_float(acc[i]);
+      }
+    }
+    named_barrier_sync(1, 256);
+    if (ok && !*abort_flag && t_mine == 0) {
+      const int64_t off = b * p.sb + h * p.sh + static_cast<int64_t>(row) * p.sn + 32 * ch;
+#pragma unroll
+      for (int a = 0; a < kAccs; ++a) {
+        uint32_t acc[32];
+        void* out = (kDKDV && a == 0) ? p.out0 : p.out1;
+        const float scale = (kDKDV && a == 0) ? 1.0f : p.sm_scale;
+        if (n_super > 0) {
           tc_fence_after();
-          tmem_ld_32x32b_x32(tmem + lane_base + kTmAcc1 + 32 * ch, acc);
+          tmem_ld_32x32b_x32(tmem + lane_base + (kDKDV && a == 0 ? kTmAcc0 : kTmAcc1) + 32 * ch, acc);
           tc_wait_ld();
+          // lanes 64..127 are never unwritten, even for a single-tile list: the first
+          // accumulate-off MMA sweeps all lanes, and theirs hold zeros for tile a
+          store_half_row<kBf16>(out, off, acc, &sm->xfer[a][32 * ch][r_blk], 65, scale);
         } else {
+          uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(out) + off);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) acc[i] = 0u;
+          for (int i = 0; i < 4; ++i) dst[i] = make_uint4(0u, 0u, 0u, 0u);
         }
-        if (row < p.N) store_half_row<kBf16>(p.out1, off, acc, p.sm_scale);
       }
     }
   }
@@ -360,12 +407,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
 template <bool kDKDV>
 static int launch_bwd(const void* q, const void* k, const void* v, const void* dout,
                       const int64_t strides[4], const float* lse2, const float* delta, void* out0,
-                      void* out1, const int32_t* pair_ptr, const int32_t* pair_ent,
+                      void* out1, const int32_t* list_ptr, const int32_t* list_idx,
                       int list_b_stride, int list_h_stride, float sm_scale, int dtype, int B, int H,
                       int N, int D, int32_t* status, void* stream) {
   if (B <= 0 || H <= 0 || N <= 0 || (N % kBlock) != 0 || D != kHeadDim) return BSA_ERR_BAD_SHAPE;
   if (dtype != BSA_F16 && dtype != BSA_BF16) return BSA_ERR_BAD_DTYPE;
-  if (!lse2 || !delta || !pair_ptr || !pair_ent || !is_aligned(lse2, 16) || !is_aligned(delta, 16))
+  if (!lse2 || !delta || !list_ptr || !list_idx || !is_aligned(lse2, 16) || !is_aligned(delta, 16))
     return BSA_ERR_BAD_POINTER;
   int rc;
   const void* ops[6] = {q, k, v, dout, out1, kDKDV ? out0 : out1};
@@ -373,8 +420,7 @@ static int launch_bwd(const void* q, const void* k, const void* v, const void* d
     if ((rc = check_qkv_operand(op, strides)) != BSA_OK) return rc;
   if ((rc = check_device_sm100()) != BSA_OK) return rc;
   const int nb = N / kBlock;
-  const int npair = (nb + 1) / 2;
-  if (static_cast<int64_t>(B) * H * npair > 0x7fffffffLL) return BSA_ERR_TOO_LARGE;
+  if (static_cast<int64_t>(B) * H * nb > 0x7fffffffLL) return BSA_ERR_TOO_LARGE;
 
   // dK/dV: K, V resident; Q, dO streamed.   dQ: Q, dO resident; K, V streamed.
   const void* stat0 = kDKDV ? k : q;
@@ -382,14 +428,14 @@ static int launch_bwd(const void* q, const void* k, const void* v, const void* d
   const void* str0 = kDKDV ? q : k;
   const void* str1 = kDKDV ? dout : v;
   CUtensorMap tm_a0, tm_a1, tm_b0, tm_b1;
-  if ((rc = make_qkv_tmap(&tm_a0, stat0, strides, B, H, N, dtype, 128)) != BSA_OK) return rc;
-  if ((rc = make_qkv_tmap(&tm_a1, stat1, strides, B, H, N, dtype, 128)) != BSA_OK) return rc;
+  if ((rc = make_qkv_tmap(&tm_a0, stat0, strides, B, H, N, dtype, 64)) != BSA_OK) return rc;
+  if ((rc = make_qkv_tmap(&tm_a1, stat1, strides, B, H, N, dtype, 64)) != BSA_OK) return rc;
   if ((rc = make_qkv_tmap(&tm_b0, str0, strides, B, H, N, dtype, 64)) != BSA_OK) return rc;
   if ((rc = make_qkv_tmap(&tm_b1, str1, strides, B, H, N, dtype, 64)) != BSA_OK) return rc;
 
   BwdParams prm;
-  prm.pair_ptr = pair_ptr;
-  prm.pair_ent = pair_ent;
+  prm.list_ptr = list_ptr;
+  prm.list_idx = list_idx;
   prm.lse2 = lse2;
   prm.delta = delta;
   prm.out0 = out0;
@@ -400,7 +446,7 @@ static int launch_bwd(const void* q, const void* k, const void* v, const void* d
   prm.B = B;
   prm.H = H;
   prm.N = N;
-  prm.npair = npair;
+  prm.nb = nb;
   prm.list_b_stride = list_b_stride;
   prm.list_h_stride = list_h_stride;
   prm.scale_log2 = sm_scale * 1.4426950408889634f;
@@ -411,7 +457,7 @@ static int launch_bwd(const void* q, const void* k, const void* v, const void* d
   auto kern = dtype == BSA_BF16 ? attn_bwd_kernel<true, kDKDV> : attn_bwd_kernel<false, kDKDV>;
   if ((rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes)) != BSA_OK)
     return rc;
-  const dim3 grid(static_cast<unsigned>(B * H * npair));
+  const dim3 grid(static_cast<unsigned>(B * H * nb));
   kern<<<grid, kBwdThreads, smem_bytes, static_cast<cudaStream_t>(stream)>>>(tm_a0, tm_a1, tm_b0,
                                                                              tm_b1, prm);
   return cudaGetLastError() == cudaSuccess ? BSA_OK : BSA_ERR_CUDA;
@@ -421,21 +467,21 @@ static int launch_bwd(const void* q, const void* k, const void* v, const void* d
 
 extern "C" int bsa_attn_bwd_dkdv(const void* q, const void* k, const void* v, const void* dout,
                                  const int64_t strides[4], const float* lse2, const float* delta,
-                                 void* dk, void* dv, const int32_t* kpair_ptr,
-                                 const int32_t* kpair_ent, int list_b_stride, int list_h_stride,
+                                 void* dk, void* dv, const int32_t* col_ptr,
+                                 const int32_t* row_idx, int list_b_stride, int list_h_stride,
                                  float sm_scale, int dtype, int B, int H, int N, int D,
                                  int32_t* status, void* stream) {
-  return bsa::launch_bwd<true>(q, k, v, dout, strides, lse2, delta, dv, dk, kpair_ptr, kpair_ent,
+  return bsa::launch_bwd<true>(q, k, v, dout, strides, lse2, delta, dv, dk, col_ptr, row_idx,
                                list_b_stride, list_h_stride, sm_scale, dtype, B, H, N, D, status,
                                stream);
 }
 
 extern "C" int bsa_attn_bwd_dq(const void* q, const void* k, const void* v, const void* dout,
                                const int64_t strides[4], const float* lse2, const float* delta,
-                               void* dq, const int32_t* qpair_ptr, const int32_t* qpair_ent,
+                               void* dq, const int32_t* row_ptr, const int32_t* col_idx,
                                int list_b_stride, int list_h_stride, float sm_scale, int dtype,
                                int B, int H, int N, int D, int32_t* status, void* stream) {
-  return bsa::launch_bwd<false>(q, k, v, dout, strides, lse2, delta, nullptr, dq, qpair_ptr,
-                                qpair_ent, list_b_stride, list_h_stride, sm_scale, dtype, B, H, N,
+  return bsa::launch_bwd<false>(q, k, v, dout, strides, lse2, delta, nullptr, dq, row_ptr,
+                                col_idx, list_b_stride, list_h_stride, sm_scale, dtype, B, H, N,
                                 D, status, stream);
 }

@@ -112,12 +112,13 @@ def reduce_dense_mask(dense: torch.Tensor, return_partial: bool = False):
     return (out, partial) if return_partial else out
 
 
-def build_tile_lists(block_mask: torch.Tensor, want_q: bool = True, want_k: bool = True,
+def build_tile_lists(block_mask: torch.Tensor, want_q: bool = False, want_k: bool = False,
                      want_csr: bool = True, want_groups: bool = False,
-                     want_csc: bool = False) -> TileLists:
+                     want_csc: bool = True) -> TileLists:
     """Block mask [..,nb,nb] -> device tile lists (worst-case sized, no host synchronisation).
-    want_csr: row lists (forward kernel); want_q / want_k: query- and key-pair lists (backward
-    kernels); want_csc: transposed CSR; want_groups: the reference's groups layout."""
+    want_csr: row lists (forward and dQ kernels); want_csc: column lists (dK/dV kernel);
+    want_q / want_k: lists over pairs of adjacent query / key blocks (a data product, not used by
+    the kernels); want_groups: the reference's groups layout."""
     lib = _lib.load()
     m4 = _as_4d(_as_bytes(block_mask))
     if not m4.is_cuda:
@@ -281,7 +282,7 @@ def attention_forward_masked(q, k, v, block_mask: torch.Tensor, sm_scale: float,
 
 def attention_backward(q, k, v, o, lse2, dout, lists: TileLists, sm_scale: float,
                        status: Optional[torch.Tensor] = None):
-    """delta, then dK/dV over the key-pair lists and dQ over the query-pair lists."""
+    """delta, then dK/dV over the column lists and dQ over the row lists."""
     lib = _lib.load()
     B, H, N, D = q.shape
     # the three kernels take one stride set for q, k, v, o, dO and the gradients
@@ -299,12 +300,12 @@ def attention_backward(q, k, v, o, lse2, dout, lists: TileLists, sm_scale: float
             _lib.ptr(o), _lib.ptr(dout), st, _lib.ptr(delta), code, B, H, N, D, stream))
         _lib.check("bsa_attn_bwd_dkdv", lib.bsa_attn_bwd_dkdv(
             _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(dout), st, _lib.ptr(lse2),
-            _lib.ptr(delta), _lib.ptr(dk), _lib.ptr(dv), _lib.ptr(lists.kpair_ptr),
-            _lib.ptr(lists.kpair_ent), sb, sh, float(sm_scale), code, B, H, N, D,
+            _lib.ptr(delta), _lib.ptr(dk), _lib.ptr(dv), _lib.ptr(lists.col_ptr),
+            _lib.ptr(lists.row_idx), sb, sh, float(sm_scale), code, B, H, N, D,
             _lib.ptr(status), stream))
         _lib.check("bsa_attn_bwd_dq", lib.bsa_attn_bwd_dq(
             _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(dout), st, _lib.ptr(lse2),
-            _lib.ptr(delta), _lib.ptr(dq), _lib.ptr(lists.qpair_ptr), _lib.ptr(lists.qpair_ent),
+            _lib.ptr(delta), _lib.ptr(dq), _lib.ptr(lists.row_ptr), _lib.ptr(lists.col_idx),
             sb, sh, float(sm_scale), code, B, H, N, D, _lib.ptr(status), stream))
     return dq, dk, dv
 
@@ -328,12 +329,12 @@ class _attention(torch.autograd.Function):
         if not (q.dtype == k.dtype == v.dtype) or q.dtype not in (torch.float16, torch.bfloat16):
             raise TypeError("q, k, v must all be float16 or all bfloat16")
         block = _block_mask_for(mask, B, H, N, q.device)
-        # the forward lists each mask row inside the kernel; only the backward needs pair lists
+        # the forward lists each mask row inside the kernel; only the backward needs lists as data
         o, lse2, _ = attention_forward_masked(q, k, v, block, sm_scale)
         if any(ctx.needs_input_grad[:3]):
-            lists = build_tile_lists(block, want_csr=False, want_q=True, want_k=True)
-            ctx.save_for_backward(q, k, v, o, lse2, lists.qpair_ptr, lists.qpair_ent,
-                                  lists.kpair_ptr, lists.kpair_ent)
+            lists = build_tile_lists(block, want_csr=True, want_csc=True)
+            ctx.save_for_backward(q, k, v, o, lse2, lists.row_ptr, lists.col_idx,
+                                  lists.col_ptr, lists.row_idx)
             ctx.lists_shape = (lists.Bm, lists.Hm, lists.nb)
         ctx.sm_scale = sm_scale
         ctx.HEAD_DIM = D
@@ -342,10 +343,9 @@ class _attention(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, do):
-        q, k, v, o, lse2, qp, qe, kp, ke = ctx.saved_tensors
+        q, k, v, o, lse2, rp, ci, cp, ri = ctx.saved_tensors
         Bm, Hm, nb = ctx.lists_shape
-        lists = TileLists(Bm=Bm, Hm=Hm, nb=nb, qpair_ptr=qp, qpair_ent=qe, kpair_ptr=kp,
-                          kpair_ent=ke)
+        lists = TileLists(Bm=Bm, Hm=Hm, nb=nb, row_ptr=rp, col_idx=ci, col_ptr=cp, row_idx=ri)
         dq, dk, dv = attention_backward(q, k, v, o, lse2, do, lists, ctx.sm_scale)
         return dq, dk, dv, None, None
 

@@ -156,24 +156,26 @@ int bsa_attn_bwd_delta(const void* o, const void* dout, const int64_t o_strides[
                        int dtype, int B, int H, int N, int D, void* stream);
 
 /*
- * dK and dV over the key-pair lists; replaces _attn_bwd_dkdv
+ * dK and dV; replaces _attn_bwd_dkdv
  * (fa2_custom_mask/fa2_bwd.py:23-81, driven from fa2_custom_mask/fa2_bwd.py:199-234).
  * All of q,k,v,dout,dk,dv share `strides`.  lse2 and delta are the outputs of bsa_attn_fwd and
- * bsa_attn_bwd_delta.  Key blocks that no query block lists get dk = dv = 0.
+ * bsa_attn_bwd_delta.  col_ptr/row_idx are the column lists of bsa_tile_lists_build (for every key
+ * block the query blocks that list it), addressed like the row lists of bsa_attn_fwd.  Key blocks
+ * that no query block lists get dk = dv = 0.
  */
 int bsa_attn_bwd_dkdv(const void* q, const void* k, const void* v, const void* dout,
                       const int64_t strides[4], const float* lse2, const float* delta, void* dk,
-                      void* dv, const int32_t* kpair_ptr, const int32_t* kpair_ent,
+                      void* dv, const int32_t* col_ptr, const int32_t* row_idx,
                       int list_b_stride, int list_h_stride, float sm_scale, int dtype, int B, int H,
                       int N, int D, int32_t* status, void* stream);
 
 /*
- * dQ over the query-pair lists; replaces _attn_bwd_dq
+ * dQ over the row lists (row_ptr/col_idx, as in bsa_attn_fwd); replaces _attn_bwd_dq
  * (fa2_custom_mask/fa2_bwd.py:85-137, driven from fa2_custom_mask/fa2_bwd.py:237-285).
  */
 int bsa_attn_bwd_dq(const void* q, const void* k, const void* v, const void* dout,
                     const int64_t strides[4], const float* lse2, const float* delta, void* dq,
-                    const int32_t* qpair_ptr, const int32_t* qpair_ent, int list_b_stride,
+                    const int32_t* row_ptr, const int32_t* col_idx, int list_b_stride,
                     int list_h_stride, float sm_scale, int dtype, int B, int H, int N, int D,
                     int32_t* status, void* stream);
 

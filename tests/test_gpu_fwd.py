@@ -23,7 +23,7 @@ def _run(q, k, v, mask, sm_scale, want_rowmax=True, mode="lists"):
                                                    sm_scale, want_rowmax)
         torch.cuda.synchronize()
         return o.float().cpu(), lse2.cpu(), (rowmax.cpu() if rowmax is not None else None)
-    lists = build_tile_lists(mask.cuda(), want_q=False, want_k=False)
+    lists = build_tile_lists(mask.cuda(), want_csc=False)
     o, lse2, rowmax = attention_forward(q.cuda(), k.cuda(), v.cuda(), lists, sm_scale, want_rowmax)
     torch.cuda.synchronize()
     return o.float().cpu(), lse2.cpu(), (rowmax.cpu() if rowmax is not None else None)
@@ -156,7 +156,7 @@ def test_baseline_sizes_against_gpu_fp32_reference(lib, N, p, dtype):
     from fa2_custom_mask import attention_forward, build_tile_lists
     q, k, v = (t.cuda() for t in oracle.make_qkv(1, 1, N, 64, seed=N, dtype=dtype))
     mask = oracle.make_block_mask(1, 1, N // 64, p, seed=N).cuda()
-    lists = build_tile_lists(mask, want_q=False, want_k=False)
+    lists = build_tile_lists(mask, want_csc=False)
     o, lse2, _ = attention_forward(q, k, v, lists, 0.125)
     worst = 0.0
     for r0 in range(0, N, 2048):

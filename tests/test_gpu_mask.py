@@ -68,12 +68,12 @@ def test_lists_on_broadcast_and_strided_masks(lib):
     from fa2_custom_mask import build_tile_lists
     base = oracle.make_block_mask(1, 1, 12, 0.4, seed=1)
     expanded = base.cuda().expand(2, 3, 12, 12)          # stride 0 over batch and heads
-    tl = build_tile_lists(expanded, want_csr=True)
+    tl = build_tile_lists(expanded, want_csr=True, want_csc=False)
     ref = oracle.tile_lists(base.expand(2, 3, 12, 12).numpy())
     np.testing.assert_array_equal(tl.row_ptr.cpu().numpy(), ref["row_ptr"])
     np.testing.assert_array_equal(tl.col_idx.cpu().numpy()[:ref["col_idx"].size], ref["col_idx"])
     sliced = oracle.make_block_mask(1, 2, 20, 0.4, seed=2).cuda()[:, :, 3:15, 5:17]  # non-contiguous
-    tl = build_tile_lists(sliced, want_csr=True, want_csc=True)
+    tl = build_tile_lists(sliced, want_csr=True, want_csc=True, want_k=True)
     ref = oracle.tile_lists(sliced.cpu().numpy())
     np.testing.assert_array_equal(tl.col_ptr.cpu().numpy(), ref["col_ptr"])
     np.testing.assert_array_equal(tl.row_idx.cpu().numpy()[:ref["row_idx"].size], ref["row_idx"])

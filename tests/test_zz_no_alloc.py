@@ -44,7 +44,7 @@ def test_static_entry_matches_two_call_path_twice_in_a_row(lib):
         q, k, v = (t.cuda() for t in oracle.make_qkv(B, H, N, 64, seed=seed, dtype=dtype))
         mask = oracle.make_block_mask(B, H, N // 64, p, seed=seed, diagonal=diag).cuda()
         o_s, lse_s = _static_forward(lib, q, k, v, mask, 0.125)
-        lists = build_tile_lists(mask, want_q=False, want_k=False)
+        lists = build_tile_lists(mask, want_csc=False)
         o_r, lse_r, _ = attention_forward(q, k, v, lists, 0.125)
         torch.cuda.synchronize()
         assert (o_s.float() - o_r.float()).abs().max().item() <= O_TOL
