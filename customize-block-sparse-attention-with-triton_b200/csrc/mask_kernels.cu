@@ -1,7 +1,8 @@
 // Mask preprocessing on the device (HBM-bound byte/integer work):
 //   bsa_mask_reduce      dense [.., N, N] boolean mask  ->  [.., nb, nb] block mask (any over 64x64)
 //   bsa_tile_lists_build block mask -> CSR, transposed CSR, pair lists, and the reference's
-//                        (groups, n_list) layout, with three launches and no host synchronisation.
+//                        (groups, n_list) layout, with three launches (one, for the row lists of
+//                        a small mask alone) and no host synchronisation.
 #include "host_common.h"
 
 namespace bsa {

@@ -13,9 +13,11 @@
  * whose work it takes over.
  *
  * Vocabulary: a "block" is 64 consecutive tokens; nb = N/64 blocks per sequence; a "tile" is one
- * (query block m, key block n) pair that the block mask keeps.  Kernels work on PAIRS of adjacent
- * blocks (128 rows of a tcgen05 accumulator): a "pair list" for pair p holds, ascending, every
- * block index j of the other axis that is kept for block 2p or 2p+1, encoded as
+ * (query block m, key block n) pair that the block mask keeps.  The kernels walk row lists (per
+ * query block its kept key blocks: forward, dQ) and column lists (per key block the query blocks
+ * that keep it: dK/dV).  bsa_tile_lists_build can also emit lists over PAIRS of adjacent blocks:
+ * the "pair list" of pair p holds, ascending, every block index j of the other axis that is kept
+ * for block 2p or 2p+1, encoded as
  *     entry = (j << 2) | flags,   flags bit0: block 2p keeps j,  bit1: block 2p+1 keeps j.
  */
 #ifndef BSATTN_H_
@@ -87,10 +89,11 @@ int bsa_tile_list_sizes(int B, int H, int nb, bsa_list_sizes* out);
  * outputs are reproduced bit-exactly:  n_list == col_idx[0:nnz]  and  groups == groups[0:G].
  *   block      : bytes, logical [B,H,nb,nb], element strides block_strides[4] (0 = broadcast).
  *   row_ptr/col_idx : CSR over rows r=(b*H+h)*nb+m, empty rows kept, columns ascending
- *                     (forward kernel).
- *   col_ptr/row_idx : CSR of the transposed mask (per key block, query blocks ascending).
- *   qpair_ptr/qpair_ent : pair lists over query-block pairs (dQ kernel).
- *   kpair_ptr/kpair_ent : pair lists over key-block pairs (dK/dV kernel).
+ *                     (forward and dQ kernels).
+ *   col_ptr/row_idx : CSR of the transposed mask (per key block, query blocks ascending;
+ *                     dK/dV kernel).
+ *   qpair_ptr/qpair_ent : pair lists over query-block pairs (not read by any kernel here).
+ *   kpair_ptr/kpair_ent : pair lists over key-block pairs (likewise).
  *   groups     : rows (b,h,m,start,len) of the non-empty rows only, in row order.
  *   meta       : int32[8] = {nnz, G, qpair entries, kpair entries, 0,0,0,0}.
  * Any (ptr,idx) pair, and groups, may be NULL to skip that product; meta is required.
