@@ -199,3 +199,39 @@ def test_work_counter_hand_out_equals_fixed_stride(lib):
     for o, lse2 in outs[1:]:
         assert torch.equal(o, outs[0][0]) and torch.equal(lse2, outs[0][1])
     _compare(q.cpu(), k.cpu(), v.cpu(), mask.cpu(), 0.125, outs[1][0].float().cpu(), outs[1][1].cpu())
+
+
+def test_two_streams_and_graph_replay(lib):
+    """Calls on different streams get a work counter each and may overlap on the GPU; a call captured
+    into a CUDA graph replays with the same result."""
+    from fa2_custom_mask import attention_forward_masked
+    cases = []
+    for seed in (11, 12):
+        q, k, v = (t.cuda() for t in oracle.make_qkv(1, 4, 2048, 64, seed=seed, dtype=torch.float16))
+        mask = oracle.make_block_mask(1, 4, 32, 0.3, seed=seed).cuda()
+        ref = attention_forward_masked(q, k, v, mask, 0.125)[0]
+        cases.append((q, k, v, mask, ref))
+    torch.cuda.synchronize()
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    outs = [[], []]
+    for _ in range(8):                      # interleaved launches on the two streams
+        for s, (q, k, v, mask, _) , o in zip(streams, cases, outs):
+            with torch.cuda.stream(s):
+                o.append(attention_forward_masked(q, k, v, mask, 0.125)[0])
+    torch.cuda.synchronize()
+    for (_, _, _, _, ref), o in zip(cases, outs):
+        assert all(torch.equal(x, ref) for x in o)
+
+    q, k, v, mask, ref = cases[0]
+    s = streams[0]
+    with torch.cuda.stream(s):
+        attention_forward_masked(q, k, v, mask, 0.125)      # the stream's counter exists before capture
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=s):
+            out = attention_forward_masked(q, k, v, mask, 0.125)[0]
+        for _ in range(3):
+            out.zero_()
+            graph.replay()
+            torch.cuda.synchronize()
+            assert torch.equal(out, ref)
