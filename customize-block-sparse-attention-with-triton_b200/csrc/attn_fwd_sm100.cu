@@ -96,7 +96,7 @@ struct FwdSmem {
   uint64_t p_free[2];                         // by team: P V of its latest superstep complete
   uint64_t o_full[2];                         // last P V of the item done
   uint64_t stats_full[2];                     // softmax warps published (m, l) of the item
-  uint64_t o_free[2];                         // write-out done with accumulators/stats/list
+  uint64_t o_free[2];                         // write-out holds accumulators/stats/header in registers
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -644,6 +644,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
           for (int j = 0; j < 64; ++j) acc[j] = 0.f;
         }
+        // Accumulators, statistics and the item's header are in registers now: the next item may
+        // use them, while this one is still being merged and stored.
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&sm->o_free[par]));
         if (t_mine == 1) {
 #pragma unroll
           for (int j = 0; j < 64; ++j) sm->xfer[j][r_blk] = acc[j];
@@ -671,8 +676,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
       // xfer may be overwritten by the next item now; all four warps leave together if any gave up
       const bool any_failed = named_barrier_or(2, 128, !ok);
-      __syncwarp();
-      if (ok && lane == 0) mbar_arrive(smem_u32(&sm->o_free[par]));
       if (any_failed) break;
     }
     if (!ok) fwd_give_up(sm, p.status, kFailOut);
