@@ -20,6 +20,8 @@
 // M replaced by a true base-2 log-sum-exp; the iteration space is the tile lists, not the
 // reference's causal loops.  dK and dQ carry the factor sm_scale.
 //
+// Persistent: one CTA per SM walks the blocks w = blockIdx.x, blockIdx.x + gridDim.x, ... (long
+// lists first when the mask is causal).
 // Roles: warps 0..7 compute (lane quarter = warp % 4, column half = warp / 4), warp 8 TMA
 // producer, warp 9 issues the S/dP MMAs and owns TMEM, warp 10 issues the accumulating MMAs (two
 // issuers, so neither waits behind the other's barrier round trips; both run warp-wide with one
@@ -50,7 +52,8 @@ struct BwdSmem {
   float lse[kBwdStages][2][64];             // dK/dV: LSE2 and delta of the streamed query tiles
   float delta[kBwdStages][2][64];
   float xfer[2][64][65];                    // write-out: lanes 64..127 hand over, [acc][col][row]
-  uint64_t stat_full;
+  uint64_t stat_full, stat_free;            // own operands loaded; their S/dP instructions complete
+  uint64_t acc_free;                        // the compute warps hold the accumulators in registers
   uint64_t in_full[kBwdStages];
   uint64_t in_empty[kBwdStages];            // accumulating MMAs of the superstep complete
   uint64_t x_full, x_free;                  // S/dP complete; S/dP in the compute warps' registers
@@ -68,6 +71,7 @@ struct BwdParams {
   void* out1;  // dK or dQ
   int64_t sb, sh, sn;
   int B, H, N, nb;
+  int items;  // B * H * nb
   int list_b_stride, list_h_stride;
   float scale_log2;
   float sm_scale;
@@ -97,6 +101,32 @@ __device__ __forceinline__ void store_half_row(void* base, int64_t elem_off, con
   }
 }
 
+// Work item w -> (batch, head, block) and the block's list.
+// dQ: long (late) rows first; dK/dV: long (early) key columns first when the mask is causal.
+struct BwdItem {
+  int b, h, blk, n_tiles;
+  const int32_t* ents;
+  int64_t vec_base;  // into lse2 / delta
+};
+template <bool kDKDV>
+__device__ __forceinline__ BwdItem bwd_item(int w, const BwdParams& p) {
+  BwdItem it;
+  const int bh = w / p.nb;
+  it.blk = kDKDV ? (w - bh * p.nb) : (p.nb - 1 - (w - bh * p.nb));
+  it.b = bh / p.H;
+  it.h = bh - it.b * p.H;
+  const int64_t li =
+      static_cast<int64_t>(it.b * p.list_b_stride + it.h * p.list_h_stride) * p.nb + it.blk;
+  const int beg = __ldg(p.list_ptr + li);
+  it.n_tiles = __ldg(p.list_ptr + li + 1) - beg;
+  it.ents = p.list_idx + beg;
+  it.vec_base = (static_cast<int64_t>(it.b) * p.H + it.h) * p.N;
+  return it;
+}
+
+// Persistent: one CTA per SM walks the items w = blockIdx.x, blockIdx.x + gridDim.x, ...; every
+// role walks the same sequence and counts supersteps (gs) and non-empty items (ni) the same way,
+// so barrier phases follow from those counts.
 template <bool kBf16, bool kDKDV>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
@@ -109,21 +139,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
 
   const int warp = uniform_warp_index();
   const int lane = threadIdx.x & 31;
-
-  const int bh = blockIdx.x / p.nb;
-  // dQ: long (late) rows first; dK/dV: long (early) key columns first when the mask is causal
-  const int blk = kDKDV ? (blockIdx.x % p.nb) : (p.nb - 1 - (blockIdx.x % p.nb));
-  const int b = bh / p.H;
-  const int h = bh % p.H;
-  const int64_t li = static_cast<int64_t>(b * p.list_b_stride + h * p.list_h_stride) * p.nb + blk;
-  const int beg = __ldg(p.list_ptr + li);
-  const int n_tiles = __ldg(p.list_ptr + li + 1) - beg;
-  const int n_super = (n_tiles + 1) >> 1;
-  const int32_t* ents = p.list_idx + beg;
-  const int64_t vec_base = (static_cast<int64_t>(b) * p.H + h) * p.N;  // into lse2 / delta
+  const int stride = gridDim.x;
 
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(&sm->stat_full), 1);
+    mbar_init(smem_u32(&sm->stat_free), 1);
     for (int s = 0; s < kBwdStages; ++s) {
       mbar_init(smem_u32(&sm->in_full[s]), 1);
       mbar_init(smem_u32(&sm->in_empty[s]), 1);
@@ -132,6 +152,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
     mbar_init(smem_u32(&sm->x_free), 8);  // one arrival per compute warp
     mbar_init(smem_u32(&sm->d_full), 8);
     mbar_init(smem_u32(&sm->d_free), 1);
+    mbar_init(smem_u32(&sm->acc_free), 8);
     sm->abort_flag = 0;
     mbar_fence_init();
   }
@@ -153,64 +174,77 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
 
   if (warp == 8) {
     // =========================== TMA producer ===========================
-    if (n_super > 0) {
-      const bool leader = elect_one();
+    const bool leader = elect_one();
+    bool ok = true;
+    int gs = 0, ni = 0;
+    for (int w = blockIdx.x; ok && w < p.items; w += stride) {
+      const BwdItem it = bwd_item<kDKDV>(w, p);
+      const int n_super = (it.n_tiles + 1) >> 1;
+      if (n_super == 0) continue;
+      // the block's own operands: the previous item's S/dP instructions must be complete
+      if (ni >= 1) ok = mbar_wait_warp(smem_u32(&sm->stat_free), (ni - 1) & 1, abort_flag);
+      if (!ok) break;
       if (leader) {
         const uint32_t bar = smem_u32(&sm->stat_full);
         mbar_expect_tx(bar, 4 * kBwdTile);
-        tma_load_4d(smem_u32(sm->stat0[0]), &tm_stat0, bar, 0, blk * 64, h, b);
-        tma_load_4d(smem_u32(sm->stat0[1]), &tm_stat0, bar, 0, blk * 64, h, b);
-        tma_load_4d(smem_u32(sm->stat1[0]), &tm_stat1, bar, 0, blk * 64, h, b);
-        tma_load_4d(smem_u32(sm->stat1[1]), &tm_stat1, bar, 0, blk * 64, h, b);
+        tma_load_4d(smem_u32(sm->stat0[0]), &tm_stat0, bar, 0, it.blk * 64, it.h, it.b);
+        tma_load_4d(smem_u32(sm->stat0[1]), &tm_stat0, bar, 0, it.blk * 64, it.h, it.b);
+        tma_load_4d(smem_u32(sm->stat1[0]), &tm_stat1, bar, 0, it.blk * 64, it.h, it.b);
+        tma_load_4d(smem_u32(sm->stat1[1]), &tm_stat1, bar, 0, it.blk * 64, it.h, it.b);
       }
-      for (int j = 0; j < n_super; ++j) {
-        const int s = j % kBwdStages;
-        const int nt = min(2, n_tiles - 2 * j);
-        const int n0 = __ldg(ents + 2 * j);
-        const int n1 = nt == 2 ? __ldg(ents + 2 * j + 1) : 0;
-        if (!mbar_wait_warp(smem_u32(&sm->in_empty[s]), ((j / kBwdStages) & 1) ^ 1, abort_flag)) {
-          bwd_give_up(sm, p.status, 1);
-          break;
-        }
+      for (int j = 0; j < n_super; ++j, ++gs) {
+        const int s = gs % kBwdStages;
+        const int nt = min(2, it.n_tiles - 2 * j);
+        const int n0 = __ldg(it.ents + 2 * j);
+        const int n1 = nt == 2 ? __ldg(it.ents + 2 * j + 1) : 0;
+        ok = mbar_wait_warp(smem_u32(&sm->in_empty[s]), ((gs / kBwdStages) & 1) ^ 1, abort_flag);
+        if (!ok) break;
         if (leader) {
           const uint32_t bar = smem_u32(&sm->in_full[s]);
           mbar_expect_tx(bar, nt * (2 * kBwdTile + (kDKDV ? 512u : 0u)));
-          tma_load_4d(smem_u32(sm->str0[s][0]), &tm_str0, bar, 0, n0 * 64, h, b);
-          tma_load_4d(smem_u32(sm->str1[s][0]), &tm_str1, bar, 0, n0 * 64, h, b);
+          tma_load_4d(smem_u32(sm->str0[s][0]), &tm_str0, bar, 0, n0 * 64, it.h, it.b);
+          tma_load_4d(smem_u32(sm->str1[s][0]), &tm_str1, bar, 0, n0 * 64, it.h, it.b);
           if constexpr (kDKDV) {
-            bulk_load_1d(smem_u32(sm->lse[s][0]), p.lse2 + vec_base + n0 * 64, 256, bar);
-            bulk_load_1d(smem_u32(sm->delta[s][0]), p.delta + vec_base + n0 * 64, 256, bar);
+            bulk_load_1d(smem_u32(sm->lse[s][0]), p.lse2 + it.vec_base + n0 * 64, 256, bar);
+            bulk_load_1d(smem_u32(sm->delta[s][0]), p.delta + it.vec_base + n0 * 64, 256, bar);
           }
           if (nt == 2) {
-            tma_load_4d(smem_u32(sm->str0[s][1]), &tm_str0, bar, 0, n1 * 64, h, b);
-            tma_load_4d(smem_u32(sm->str1[s][1]), &tm_str1, bar, 0, n1 * 64, h, b);
+            tma_load_4d(smem_u32(sm->str0[s][1]), &tm_str0, bar, 0, n1 * 64, it.h, it.b);
+            tma_load_4d(smem_u32(sm->str1[s][1]), &tm_str1, bar, 0, n1 * 64, it.h, it.b);
             if constexpr (kDKDV) {
-              bulk_load_1d(smem_u32(sm->lse[s][1]), p.lse2 + vec_base + n1 * 64, 256, bar);
-              bulk_load_1d(smem_u32(sm->delta[s][1]), p.delta + vec_base + n1 * 64, 256, bar);
+              bulk_load_1d(smem_u32(sm->lse[s][1]), p.lse2 + it.vec_base + n1 * 64, 256, bar);
+              bulk_load_1d(smem_u32(sm->delta[s][1]), p.delta + it.vec_base + n1 * 64, 256, bar);
             }
           }
         }
       }
+      ++ni;
     }
+    if (!ok) bwd_give_up(sm, p.status, 1);
   } else if (warp == 9) {
     // =========================== S / dP issuer ===========================
-    if (n_super > 0) {
-      constexpr uint32_t idesc_x128 = umma_idesc(kBf16, 0, 0, 128, 128);
-      constexpr uint32_t idesc_x64 = umma_idesc(kBf16, 0, 0, 128, 64);  // odd tail: one tile
-      const bool leader = elect_one();
-      const uint64_t desc_a0 = smem_desc_sw128(smem_u32(sm->stat0[0]), 16, 1024);
-      const uint64_t desc_a1 = smem_desc_sw128(smem_u32(sm->stat1[0]), 16, 1024);
-      const uint64_t desc_b0 = smem_desc_sw128(smem_u32(sm->str0[0][0]), 16, 1024);
-      const uint64_t desc_b1 = smem_desc_sw128(smem_u32(sm->str1[0][0]), 16, 1024);
-      bool ok = mbar_wait_warp(smem_u32(&sm->stat_full), 0, abort_flag);
-      for (int j = 0; ok && j < n_super; ++j) {
-        const int s = j % kBwdStages;
-        const int nt = min(2, n_tiles - 2 * j);
-        ok = mbar_wait_warp(smem_u32(&sm->in_full[s]), (j / kBwdStages) & 1, abort_flag);
+    constexpr uint32_t idesc_x128 = umma_idesc(kBf16, 0, 0, 128, 128);
+    constexpr uint32_t idesc_x64 = umma_idesc(kBf16, 0, 0, 128, 64);  // odd tail: one tile
+    const bool leader = elect_one();
+    const uint64_t desc_a0 = smem_desc_sw128(smem_u32(sm->stat0[0]), 16, 1024);
+    const uint64_t desc_a1 = smem_desc_sw128(smem_u32(sm->stat1[0]), 16, 1024);
+    const uint64_t desc_b0 = smem_desc_sw128(smem_u32(sm->str0[0][0]), 16, 1024);
+    const uint64_t desc_b1 = smem_desc_sw128(smem_u32(sm->str1[0][0]), 16, 1024);
+    bool ok = true;
+    int gs = 0, ni = 0;
+    for (int w = blockIdx.x; ok && w < p.items; w += stride) {
+      const BwdItem it = bwd_item<kDKDV>(w, p);
+      const int n_super = (it.n_tiles + 1) >> 1;
+      if (n_super == 0) continue;
+      ok = mbar_wait_warp(smem_u32(&sm->stat_full), ni & 1, abort_flag);
+      for (int j = 0; ok && j < n_super; ++j, ++gs) {
+        const int s = gs % kBwdStages;
+        const int nt = min(2, it.n_tiles - 2 * j);
+        ok = mbar_wait_warp(smem_u32(&sm->in_full[s]), (gs / kBwdStages) & 1, abort_flag);
         if (!ok) break;
-        // S/dP of the previous superstep must be in the compute warps' registers (for j = 0 this
-        // asks for the phase before the first one, which counts as complete)
-        ok = mbar_wait_warp(smem_u32(&sm->x_free), (j & 1) ^ 1, abort_flag);
+        // S/dP of the previous superstep must be in the compute warps' registers (for the first
+        // one this asks for the phase before the first one, which counts as complete)
+        ok = mbar_wait_warp(smem_u32(&sm->x_free), (gs & 1) ^ 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
         if (leader) {
@@ -224,22 +258,30 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
           for (int kk = 0; kk < 4; ++kk)
             umma_ss(tmem + kTmX1, desc_a1 + 2 * kk, b1 + 2 * kk, idesc, kk > 0);
           tc_commit(smem_u32(&sm->x_full));
+          if (j == n_super - 1) tc_commit(smem_u32(&sm->stat_free));  // own operands reusable
         }
       }
-      if (!ok) bwd_give_up(sm, p.status, 2);
+      ++ni;
     }
+    if (!ok) bwd_give_up(sm, p.status, 2);
   } else if (warp == 10) {
     // =========================== accumulating-MMA issuer ===========================
-    if (n_super > 0) {
-      constexpr uint32_t idesc_acc = umma_idesc(kBf16, 0, 1, 128, 64);
-      const bool leader = elect_one();
-      const uint64_t desc_m0 = smem_desc_sw128(smem_u32(sm->str0[0][0]), 8192, 1024);
-      const uint64_t desc_m1 = smem_desc_sw128(smem_u32(sm->str1[0][0]), 8192, 1024);
-      bool ok = true;
-      for (int j = 0; ok && j < n_super; ++j) {
-        const int s = j % kBwdStages;
-        const int nt = min(2, n_tiles - 2 * j);
-        ok = mbar_wait_warp(smem_u32(&sm->d_full), j & 1, abort_flag);
+    constexpr uint32_t idesc_acc = umma_idesc(kBf16, 0, 1, 128, 64);
+    const bool leader = elect_one();
+    const uint64_t desc_m0 = smem_desc_sw128(smem_u32(sm->str0[0][0]), 8192, 1024);
+    const uint64_t desc_m1 = smem_desc_sw128(smem_u32(sm->str1[0][0]), 8192, 1024);
+    bool ok = true;
+    int gs = 0, ni = 0;
+    for (int w = blockIdx.x; ok && w < p.items; w += stride) {
+      const BwdItem it = bwd_item<kDKDV>(w, p);
+      const int n_super = (it.n_tiles + 1) >> 1;
+      if (n_super == 0) continue;
+      // the compute warps must hold the previous item's accumulators in registers
+      if (ni >= 1) ok = mbar_wait_warp(smem_u32(&sm->acc_free), (ni - 1) & 1, abort_flag);
+      for (int j = 0; ok && j < n_super; ++j, ++gs) {
+        const int s = gs % kBwdStages;
+        const int nt = min(2, it.n_tiles - 2 * j);
+        ok = mbar_wait_warp(smem_u32(&sm->d_full), gs & 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
         if (leader) {
@@ -263,24 +305,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
           tc_commit(smem_u32(&sm->d_free));       // P/dS buffers free; accumulators updated
         }
       }
-      if (!ok) bwd_give_up(sm, p.status, 2);
+      ++ni;
     }
+    if (!ok) bwd_give_up(sm, p.status, 2);
   } else {
     // =========================== compute warps ===========================
     const int quarter = warp & 3;
     const int ch = warp >> 2;           // which 32 of the tile's 64 columns
     const int t_mine = quarter >> 1;    // lanes 0..63 own tile a of a superstep, 64..127 tile b
     const int r_blk = (quarter & 1) * 32 + lane;  // row of the CTA's block
-    const int row = blk * 64 + r_blk;
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
     const float c = p.scale_log2;
-    float my_lse = 0.f, my_delta = 0.f;
-    if constexpr (!kDKDV) {
-      my_lse = __ldg(p.lse2 + vec_base + row);
-      my_delta = __ldg(p.delta + vec_base + row);
-    }
-    bool ok = true;
-    if (n_super > 0) {
+    constexpr int kAccs = kDKDV ? 2 : 1;
+    {
       // The accumulating MMAs of a tile sweep all 128 lanes: the half of the lanes that does not
       // own the tile holds zeros where that tile's P / dS live.  Nothing else ever writes there.
       uint32_t z[16];
@@ -290,109 +327,140 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
       tmem_st_32x32b_x16(tmem + lane_base + kTmDS + 32 * (1 - t_mine) + 16 * ch, z);
       tc_wait_st();
     }
-    for (int j = 0; j < n_super; ++j) {
-      const int s = j % kBwdStages;
-      const int nt = min(2, n_tiles - 2 * j);
-      const bool active = t_mine < nt;  // warp-uniform
-      if constexpr (kDKDV) {
-        // the LSE2/delta vectors of this stage arrive through the async proxy
-        ok = mbar_wait_warp(smem_u32(&sm->in_full[s]), (j / kBwdStages) & 1, abort_flag);
-        if (!ok) break;
-      }
-      ok = mbar_wait_warp(smem_u32(&sm->x_full), j & 1, abort_flag);
-      if (!ok) break;
-      tc_fence_after();
-      uint32_t xs[32], xd[32];
-      if (active) {
-        tmem_ld_32x32b_x32(tmem + lane_base + kTmX0 + 64 * t_mine + 32 * ch, xs);
-        tmem_ld_32x32b_x32(tmem + lane_base + kTmX1 + 64 * t_mine + 32 * ch, xd);
-      }
-      tc_wait_ld();
-      // S/dP are in registers: the next superstep's may be issued
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&sm->x_free));
-      uint32_t pk_p[16], pk_ds[16];
-      if (active) {
-        const float4* lse4 = reinterpret_cast<const float4*>(&sm->lse[s][t_mine][32 * ch]);
-        const float4* del4 = reinterpret_cast<const float4*>(&sm->delta[s][t_mine][32 * ch]);
+    bool ok = true;
+    int gs = 0;
+    for (int w = blockIdx.x; w < p.items; w += stride) {
+      const BwdItem it = bwd_item<kDKDV>(w, p);
+      const int n_super = (it.n_tiles + 1) >> 1;
+      const int row = it.blk * 64 + r_blk;
+      const int64_t off =
+          it.b * p.sb + it.h * p.sh + static_cast<int64_t>(row) * p.sn + 32 * ch;
+      if (n_super == 0) {
+        // a block with an empty list: zero gradients (the same decision in all eight warps)
+        if (t_mine == 0) {
 #pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-          float l[4], d[4];
-          if constexpr (kDKDV) {
-            const float4 lv = lse4[i / 4], dv = del4[i / 4];
-            l[0] = lv.x; l[1] = lv.y; l[2] = lv.z; l[3] = lv.w;
-            d[0] = dv.x; d[1] = dv.y; d[2] = dv.z; d[3] = dv.w;
-          } else {
-            l[0] = l[1] = l[2] = l[3] = my_lse;
-            d[0] = d[1] = d[2] = d[3] = my_delta;
-          }
-          float pv[4], dsv[4];
+          for (int a = 0; a < kAccs; ++a) {
+            uint4* dst = reinterpret_cast<uint4*>(
+                static_cast<uint16_t*>((kDKDV && a == 0) ? p.out0 : p.out1) + off);
 #pragma unroll
-          for (int t = 0; t < 4; ++t) {
-            pv[t] = ex2_approx(fmaf(__uint_as_float(xs[i + t]), c, -l[t]));
-            dsv[t] = pv[t] * (__uint_as_float(xd[i + t]) - d[t]);
+            for (int i = 0; i < 4; ++i) dst[i] = make_uint4(0u, 0u, 0u, 0u);
           }
-          pk_p[i / 2] = pack_2x16<kBf16>(pv[0], pv[1]);
-          pk_p[i / 2 + 1] = pack_2x16<kBf16>(pv[2], pv[3]);
-          pk_ds[i / 2] = pack_2x16<kBf16>(dsv[0], dsv[1]);
-          pk_ds[i / 2 + 1] = pack_2x16<kBf16>(dsv[2], dsv[3]);
         }
+        continue;
       }
-      // the accumulating MMAs of the previous superstep still read the P/dS buffers
-      ok = mbar_wait_warp(smem_u32(&sm->d_free), (j & 1) ^ 1, abort_flag);
-      if (!ok) break;
-      if (active) {
+      float my_lse = 0.f, my_delta = 0.f;
+      if constexpr (!kDKDV) {
+        my_lse = __ldg(p.lse2 + it.vec_base + row);
+        my_delta = __ldg(p.delta + it.vec_base + row);
+      }
+      for (int j = 0; ok && j < n_super; ++j, ++gs) {
+        const int s = gs % kBwdStages;
+        const int nt = min(2, it.n_tiles - 2 * j);
+        const bool active = t_mine < nt;  // warp-uniform
+        if constexpr (kDKDV) {
+          // the LSE2/delta vectors of this stage arrive through the async proxy
+          ok = mbar_wait_warp(smem_u32(&sm->in_full[s]), (gs / kBwdStages) & 1, abort_flag);
+          if (!ok) break;
+        }
+        ok = mbar_wait_warp(smem_u32(&sm->x_full), gs & 1, abort_flag);
+        if (!ok) break;
         tc_fence_after();
-        if constexpr (kDKDV) tmem_st_32x32b_x16(tmem + lane_base + kTmP + 32 * t_mine + 16 * ch, pk_p);
-        tmem_st_32x32b_x16(tmem + lane_base + kTmDS + 32 * t_mine + 16 * ch, pk_ds);
-      }
-      tc_wait_st();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&sm->d_full));
-    }
-    if (ok && n_super > 0)
-      ok = mbar_wait_warp(smem_u32(&sm->d_free), (n_super - 1) & 1, abort_flag);
-    if (!ok) bwd_give_up(sm, p.status, 3);
-
-    // ---- write-out: lane r holds the tile-a sums of row r, lane r+64 its tile-b sums ----
-    // The named barrier is executed by all eight compute warps, also after a give-up (every
-    // bounded wait of a warp still in the loop ends once the flag is up).
-    constexpr int kAccs = kDKDV ? 2 : 1;
-    if (ok && n_super > 0 && t_mine == 1) {
-      tc_fence_after();
-#pragma unroll
-      for (int a = 0; a < kAccs; ++a) {
-        uint32_t acc[32];
-        tmem_ld_32x32b_x32(tmem + lane_base + (kDKDV && a == 0 ? kTmAcc0 : kTmAcc1) + 32 * ch, acc);
+        uint32_t xs[32], xd[32];
+        if (active) {
+          tmem_ld_32x32b_x32(tmem + lane_base + kTmX0 + 64 * t_mine + 32 * ch, xs);
+          tmem_ld_32x32b_x32(tmem + lane_base + kTmX1 + 64 * t_mine + 32 * ch, xd);
+        }
         tc_wait_ld();
+        // S/dP are in registers: the next superstep's may be issued
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&sm->x_free));
+        uint32_t pk_p[16], pk_ds[16];
+        if (active) {
+          const float4* lse4 = reinterpret_cast<const float4*>(&sm->lse[s][t_mine][32 * ch]);
+          const float4* del4 = reinterpret_cast<const float4*>(&sm->delta[s][t_mine][32 * ch]);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) sm->xfer[a][32 * ch + i][r_blk] = __uint_as_float(acc[i]);
-      }
-    }
-    named_barrier_sync(1, 256);
-    if (ok && !*abort_flag && t_mine == 0) {
-      const int64_t off = b * p.sb + h * p.sh + static_cast<int64_t>(row) * p.sn + 32 * ch;
+          for (int i = 0; i < 32; i += 4) {
+            float l[4], d[4];
+            if constexpr (kDKDV) {
+              const float4 lv = lse4[i / 4], dv = del4[i / 4];
+              l[0] = lv.x; l[1] = lv.y; l[2] = lv.z; l[3] = lv.w;
+              d[0] = dv.x; d[1] = dv.y; d[2] = dv.z; d[3] = dv.w;
+            } else {
+              l[0] = l[1] = l[2] = l[3] = my_lse;
+              d[0] = d[1] = d[2] = d[3] = my_delta;
+            }
+            float pv[4], dsv[4];
 #pragma unroll
-      for (int a = 0; a < kAccs; ++a) {
-        uint32_t acc[32];
-        void* out = (kDKDV && a == 0) ? p.out0 : p.out1;
-        const float scale = (kDKDV && a == 0) ? 1.0f : p.sm_scale;
-        if (n_super > 0) {
+            for (int t = 0; t < 4; ++t) {
+              pv[t] = ex2_approx(fmaf(__uint_as_float(xs[i + t]), c, -l[t]));
+              dsv[t] = pv[t] * (__uint_as_float(xd[i + t]) - d[t]);
+            }
+            pk_p[i / 2] = pack_2x16<kBf16>(pv[0], pv[1]);
+            pk_p[i / 2 + 1] = pack_2x16<kBf16>(pv[2], pv[3]);
+            pk_ds[i / 2] = pack_2x16<kBf16>(dsv[0], dsv[1]);
+            pk_ds[i / 2 + 1] = pack_2x16<kBf16>(dsv[2], dsv[3]);
+          }
+        }
+        // the accumulating MMAs of the previous superstep still read the P/dS buffers
+        ok = mbar_wait_warp(smem_u32(&sm->d_free), (gs & 1) ^ 1, abort_flag);
+        if (!ok) break;
+        if (active) {
           tc_fence_after();
+          if constexpr (kDKDV) tmem_st_32x32b_x16(tmem + lane_base + kTmP + 32 * t_mine + 16 * ch, pk_p);
+          tmem_st_32x32b_x16(tmem + lane_base + kTmDS + 32 * t_mine + 16 * ch, pk_ds);
+        }
+        tc_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&sm->d_full));
+      }
+      // all accumulating MMAs of the item complete (gs was advanced past the last superstep)
+      if (ok) ok = mbar_wait_warp(smem_u32(&sm->d_free), (gs - 1) & 1, abort_flag);
+
+      // ---- write-out: lane r holds the tile-a sums of row r, lane r+64 its tile-b sums ----
+      // Both named barriers are executed by all eight compute warps, also after a give-up (every
+      // bounded wait of a warp still in the loop ends once the flag is up); the second one carries
+      // the give-up vote.  Lanes 64..127 are never unwritten, even for a single-tile list: the
+      // first accumulate-off MMA sweeps all lanes, and theirs hold zeros for tile a.
+      if (ok && t_mine == 1) {
+        // lanes 64..127 pass their sums on through shared memory, one accumulator at a time
+        tc_fence_after();
+#pragma unroll
+        for (int a = 0; a < kAccs; ++a) {
+          uint32_t up[32];
+          tmem_ld_32x32b_x32(tmem + lane_base + (kDKDV && a == 0 ? kTmAcc0 : kTmAcc1) + 32 * ch, up);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) sm->xfer[a][32 * ch + i][r_blk] = __uint_as_float(up[i]);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&sm->acc_free));
+      }
+      named_barrier_sync(1, 256);
+      if (ok && t_mine == 0) {
+        tc_fence_after();
+#pragma unroll
+        for (int a = 0; a < kAccs; ++a) {
+          uint32_t acc[32];
           tmem_ld_32x32b_x32(tmem + lane_base + (kDKDV && a == 0 ? kTmAcc0 : kTmAcc1) + 32 * ch, acc);
           tc_wait_ld();
-          // lanes 64..127 are never unwritten, even for a single-tile list: the first
-          // accumulate-off MMA sweeps all lanes, and theirs hold zeros for tile a
-          store_half_row<kBf16>(out, off, acc, &sm->xfer[a][32 * ch][r_blk], 65, scale);
-        } else {
-          uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(out) + off);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) dst[i] = make_uint4(0u, 0u, 0u, 0u);
+          if (a == kAccs - 1) {
+            // the accumulators are in registers: the next item may start accumulating
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&sm->acc_free));
+          }
+          store_half_row<kBf16>((kDKDV && a == 0) ? p.out0 : p.out1, off, acc,
+                                &sm->xfer[a][32 * ch][r_blk], 65,
+                                (kDKDV && a == 0) ? 1.0f : p.sm_scale);
         }
       }
+      // xfer may be overwritten by the next item now; all eight warps leave together on a give-up
+      if (named_barrier_or(1, 256, !ok)) break;
     }
+    if (!ok) bwd_give_up(sm, p.status, 3);
   }
 
   tc_fence_before();
@@ -447,6 +515,7 @@ static int launch_bwd(const void* q, const void* k, const void* v, const void* d
   prm.H = H;
   prm.N = N;
   prm.nb = nb;
+  prm.items = B * H * nb;
   prm.list_b_stride = list_b_stride;
   prm.list_h_stride = list_h_stride;
   prm.scale_log2 = sm_scale * 1.4426950408889634f;
@@ -457,7 +526,9 @@ static int launch_bwd(const void* q, const void* k, const void* v, const void* d
   auto kern = dtype == BSA_BF16 ? attn_bwd_kernel<true, kDKDV> : attn_bwd_kernel<false, kDKDV>;
   if ((rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes)) != BSA_OK)
     return rc;
-  const dim3 grid(static_cast<unsigned>(B * H * nb));
+  int sms = 0;
+  if ((rc = sm_count(&sms)) != BSA_OK) return rc;
+  const dim3 grid(static_cast<unsigned>(prm.items < sms ? prm.items : sms));  // one CTA per SM
   kern<<<grid, kBwdThreads, smem_bytes, static_cast<cudaStream_t>(stream)>>>(tm_a0, tm_a1, tm_b0,
                                                                              tm_b1, prm);
   return cudaGetLastError() == cudaSuccess ? BSA_OK : BSA_ERR_CUDA;
