@@ -20,8 +20,8 @@
 // M replaced by a true base-2 log-sum-exp; the iteration space is the tile lists, not the
 // reference's causal loops.  dK and dQ carry the factor sm_scale.
 //
-// Persistent: one CTA per SM walks the blocks w = blockIdx.x, blockIdx.x + gridDim.x, ... (long
-// lists first when the mask is causal).
+// Persistent: one CTA per SM starts with block blockIdx.x and draws further blocks from an
+// optional work counter (or walks a fixed stride); long lists first when the mask is causal.
 // Roles: warps 0..7 compute (lane quarter = warp % 4, column half = warp / 4), warp 8 TMA
 // producer, warp 9 issues the S/dP MMAs and owns TMEM, warp 10 issues the accumulating MMAs (two
 // issuers, so neither waits behind the other's barrier round trips; both run warp-wide with one
@@ -52,6 +52,8 @@ struct BwdSmem {
   float lse[kBwdStages][2][64];             // dK/dV: LSE2 and delta of the streamed query tiles
   float delta[kBwdStages][2][64];
   float xfer[2][64][65];                    // write-out: lanes 64..127 hand over, [acc][col][row]
+  int item[2];                              // by item parity: the work item, -1 = no more work
+  uint64_t item_full[2], item_free[2];      // header published; header read by all ten readers
   uint64_t stat_full, stat_free;            // own operands loaded; their S/dP instructions complete
   uint64_t acc_free;                        // the compute warps hold the accumulators in registers
   uint64_t in_full[kBwdStages];
@@ -76,6 +78,7 @@ struct BwdParams {
   float scale_log2;
   float sm_scale;
   int32_t* status;
+  int32_t* ticket;  // optional work counter (0 at kernel start, left 0): dynamic item hand-out
 };
 
 __device__ __forceinline__ void bwd_give_up(BwdSmem* sm, int32_t* status, int code) {
@@ -101,6 +104,17 @@ __device__ __forceinline__ void store_half_row(void* base, int64_t elem_off, con
   }
 }
 
+// Readers of the item header: wait for item i, read it, tell the producer the slot was read.
+__device__ __forceinline__ bool bwd_next_item(BwdSmem* sm, int i, int lane, volatile int* abort_flag,
+                                              int* w) {
+  const int par = i & 1;
+  if (!mbar_wait_warp(smem_u32(&sm->item_full[par]), (i >> 1) & 1, abort_flag)) return false;
+  *w = *const_cast<volatile int*>(&sm->item[par]);
+  __syncwarp();
+  if (lane == 0) mbar_arrive(smem_u32(&sm->item_free[par]));
+  return true;
+}
+
 // Work item w -> (batch, head, block) and the block's list.
 // dQ: long (late) rows first; dK/dV: long (early) key columns first when the mask is causal.
 struct BwdItem {
@@ -124,9 +138,11 @@ __device__ __forceinline__ BwdItem bwd_item(int w, const BwdParams& p) {
   return it;
 }
 
-// Persistent: one CTA per SM walks the items w = blockIdx.x, blockIdx.x + gridDim.x, ...; every
-// role walks the same sequence and counts supersteps (gs) and non-empty items (ni) the same way,
-// so barrier phases follow from those counts.
+// Persistent: one CTA per SM.  The producer starts with item blockIdx.x and then draws further
+// items from the optional work counter (or walks a fixed stride), and hands each item's index to
+// the other roles through shared memory; every role walks the same sequence and counts
+// supersteps (gs) and non-empty items (ni) the same way, so barrier phases follow from the counts.
+
 template <bool kBf16, bool kDKDV>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
@@ -142,6 +158,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
   const int stride = gridDim.x;
 
   if (threadIdx.x == 0) {
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&sm->item_full[i]), 1);
+      mbar_init(smem_u32(&sm->item_free[i]), 10);  // 8 compute warps and the two issuers
+    }
     mbar_init(smem_u32(&sm->stat_full), 1);
     mbar_init(smem_u32(&sm->stat_free), 1);
     for (int s = 0; s < kBwdStages; ++s) {
@@ -177,7 +197,31 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
     const bool leader = elect_one();
     bool ok = true;
     int gs = 0, ni = 0;
-    for (int w = blockIdx.x; ok && w < p.items; w += stride) {
+    for (int i = 0, w = blockIdx.x; ok; ++i) {
+      const int par = i & 1;
+      if (i > 0) {
+        if (p.ticket != nullptr) {
+          int t = 0;
+          if (lane == 0) {
+            t = atomicAdd(p.ticket, 1);
+            // every CTA draws until its first ticket past the end, so the launch draws exactly
+            // `items` tickets in all; whoever draws the last one leaves the counter at zero
+            if (t == p.items - 1) atomicExch(p.ticket, 0);
+          }
+          w = stride + __shfl_sync(0xffffffffu, t, 0);
+        } else {
+          w += stride;
+        }
+      }
+      // the header slot of item i-2 must have been read by everyone
+      if (i >= 2)
+        ok = mbar_wait_warp(smem_u32(&sm->item_free[par]), ((i - 2) >> 1) & 1, abort_flag);
+      if (!ok) break;
+      if (lane == 0) {
+        sm->item[par] = w < p.items ? w : -1;
+        mbar_arrive(smem_u32(&sm->item_full[par]));  // release: the header is visible
+      }
+      if (w >= p.items) break;
       const BwdItem it = bwd_item<kDKDV>(w, p);
       const int n_super = (it.n_tiles + 1) >> 1;
       if (n_super == 0) continue;
@@ -232,7 +276,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
     const uint64_t desc_b1 = smem_desc_sw128(smem_u32(sm->str1[0][0]), 16, 1024);
     bool ok = true;
     int gs = 0, ni = 0;
-    for (int w = blockIdx.x; ok && w < p.items; w += stride) {
+    for (int i = 0; ok; ++i) {
+      int w;
+      ok = bwd_next_item(sm, i, lane, abort_flag, &w);
+      if (!ok || w < 0) break;
       const BwdItem it = bwd_item<kDKDV>(w, p);
       const int n_super = (it.n_tiles + 1) >> 1;
       if (n_super == 0) continue;
@@ -272,7 +319,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
     const uint64_t desc_m1 = smem_desc_sw128(smem_u32(sm->str1[0][0]), 8192, 1024);
     bool ok = true;
     int gs = 0, ni = 0;
-    for (int w = blockIdx.x; ok && w < p.items; w += stride) {
+    for (int i = 0; ok; ++i) {
+      int w;
+      ok = bwd_next_item(sm, i, lane, abort_flag, &w);
+      if (!ok || w < 0) break;
       const BwdItem it = bwd_item<kDKDV>(w, p);
       const int n_super = (it.n_tiles + 1) >> 1;
       if (n_super == 0) continue;
@@ -329,8 +379,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
     }
     bool ok = true;
     int gs = 0;
-    for (int w = blockIdx.x; w < p.items; w += stride) {
-      const BwdItem it = bwd_item<kDKDV>(w, p);
+    for (int i = 0;; ++i) {
+      int w;
+      ok = bwd_next_item(sm, i, lane, abort_flag, &w);
+      // on a give-up the warp goes on to the barriers below with an empty item, so that no warp
+      // of this role is left waiting at one; the vote there makes all eight leave
+      if (ok && w < 0) break;  // no more work: the same for all eight warps
+      BwdItem it = bwd_item<kDKDV>(ok ? w : 0, p);
+      if (!ok) it.n_tiles = 1;
       const int n_super = (it.n_tiles + 1) >> 1;
       const int row = it.blk * 64 + r_blk;
       const int64_t off =
@@ -477,7 +533,7 @@ static int launch_bwd(const void* q, const void* k, const void* v, const void* d
                       const int64_t strides[4], const float* lse2, const float* delta, void* out0,
                       void* out1, const int32_t* list_ptr, const int32_t* list_idx,
                       int list_b_stride, int list_h_stride, float sm_scale, int dtype, int B, int H,
-                      int N, int D, int32_t* status, void* stream) {
+                      int N, int D, int32_t* ticket, int32_t* status, void* stream) {
   if (B <= 0 || H <= 0 || N <= 0 || (N % kBlock) != 0 || D != kHeadDim) return BSA_ERR_BAD_SHAPE;
   if (dtype != BSA_F16 && dtype != BSA_BF16) return BSA_ERR_BAD_DTYPE;
   if (!lse2 || !delta || !list_ptr || !list_idx || !is_aligned(lse2, 16) || !is_aligned(delta, 16))
@@ -521,6 +577,7 @@ static int launch_bwd(const void* q, const void* k, const void* v, const void* d
   prm.scale_log2 = sm_scale * 1.4426950408889634f;
   prm.sm_scale = sm_scale;
   prm.status = status;
+  prm.ticket = ticket;
 
   const size_t smem_bytes = sizeof(BwdSmem) + 1024;
   auto kern = dtype == BSA_BF16 ? attn_bwd_kernel<true, kDKDV> : attn_bwd_kernel<false, kDKDV>;
@@ -541,18 +598,19 @@ extern "C" int bsa_attn_bwd_dkdv(const void* q, const void* k, const void* v, co
                                  void* dk, void* dv, const int32_t* col_ptr,
                                  const int32_t* row_idx, int list_b_stride, int list_h_stride,
                                  float sm_scale, int dtype, int B, int H, int N, int D,
-                                 int32_t* status, void* stream) {
+                                 int32_t* work_counter, int32_t* status, void* stream) {
   return bsa::launch_bwd<true>(q, k, v, dout, strides, lse2, delta, dv, dk, col_ptr, row_idx,
-                               list_b_stride, list_h_stride, sm_scale, dtype, B, H, N, D, status,
-                               stream);
+                               list_b_stride, list_h_stride, sm_scale, dtype, B, H, N, D,
+                               work_counter, status, stream);
 }
 
 extern "C" int bsa_attn_bwd_dq(const void* q, const void* k, const void* v, const void* dout,
                                const int64_t strides[4], const float* lse2, const float* delta,
                                void* dq, const int32_t* row_ptr, const int32_t* col_idx,
                                int list_b_stride, int list_h_stride, float sm_scale, int dtype,
-                               int B, int H, int N, int D, int32_t* status, void* stream) {
+                               int B, int H, int N, int D, int32_t* work_counter, int32_t* status,
+                               void* stream) {
   return bsa::launch_bwd<false>(q, k, v, dout, strides, lse2, delta, nullptr, dq, row_ptr,
                                 col_idx, list_b_stride, list_h_stride, sm_scale, dtype, B, H, N,
-                                D, status, stream);
+                                D, work_counter, status, stream);
 }

@@ -47,9 +47,9 @@ SIGNATURES = {
                                 _f, _i, _i, _i, _i, _i, _vp, _vp, _vp],
     "bsa_attn_bwd_delta": [_vp, _vp, _s4, _vp, _i, _i, _i, _i, _i, _vp],
     "bsa_attn_bwd_dkdv": [_vp, _vp, _vp, _vp, _s4, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i,
-                          _i, _i, _i, _i, _vp, _vp],
+                          _i, _i, _i, _i, _vp, _vp, _vp],
     "bsa_attn_bwd_dq": [_vp, _vp, _vp, _vp, _s4, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i,
-                        _i, _i, _i, _i, _vp, _vp],
+                        _i, _i, _i, _i, _vp, _vp, _vp],
     "bsa_reorder": [_vp, _vp, _s4, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "bsa_inv_reorder": [_vp, _vp, _s4, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "bsa_attn_fwd_block_mask_static": [_vp, _s4, _vp, _s4, _vp, _s4, _vp, _s4, _vp, _vp, _s4, _i,

@@ -296,17 +296,19 @@ def attention_backward(q, k, v, o, lse2, dout, lists: TileLists, sm_scale: float
     st = _lib.strides4(q)
     with _on_device(q.device):
         stream = _lib.stream_ptr(q.device)
+        counter = _work_counter(q.device, stream.value or 0)
         _lib.check("bsa_attn_bwd_delta", lib.bsa_attn_bwd_delta(
             _lib.ptr(o), _lib.ptr(dout), st, _lib.ptr(delta), code, B, H, N, D, stream))
         _lib.check("bsa_attn_bwd_dkdv", lib.bsa_attn_bwd_dkdv(
             _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(dout), st, _lib.ptr(lse2),
             _lib.ptr(delta), _lib.ptr(dk), _lib.ptr(dv), _lib.ptr(lists.col_ptr),
             _lib.ptr(lists.row_idx), sb, sh, float(sm_scale), code, B, H, N, D,
-            _lib.ptr(status), stream))
+            _lib.ptr(counter), _lib.ptr(status), stream))
         _lib.check("bsa_attn_bwd_dq", lib.bsa_attn_bwd_dq(
             _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(dout), st, _lib.ptr(lse2),
             _lib.ptr(delta), _lib.ptr(dq), _lib.ptr(lists.row_ptr), _lib.ptr(lists.col_idx),
-            sb, sh, float(sm_scale), code, B, H, N, D, _lib.ptr(status), stream))
+            sb, sh, float(sm_scale), code, B, H, N, D, _lib.ptr(counter), _lib.ptr(status),
+            stream))
     return dq, dk, dv
 
 

@@ -164,13 +164,14 @@ int bsa_attn_bwd_delta(const void* o, const void* dout, const int64_t o_strides[
  * All of q,k,v,dout,dk,dv share `strides`.  lse2 and delta are the outputs of bsa_attn_fwd and
  * bsa_attn_bwd_delta.  col_ptr/row_idx are the column lists of bsa_tile_lists_build (for every key
  * block the query blocks that list it), addressed like the row lists of bsa_attn_fwd.  Key blocks
- * that no query block lists get dk = dv = 0.
+ * that no query block lists get dk = dv = 0.  work_counter: as in bsa_attn_fwd (both backward
+ * kernels are persistent too; the same zeroed word can serve all calls of one stream).
  */
 int bsa_attn_bwd_dkdv(const void* q, const void* k, const void* v, const void* dout,
                       const int64_t strides[4], const float* lse2, const float* delta, void* dk,
                       void* dv, const int32_t* col_ptr, const int32_t* row_idx,
                       int list_b_stride, int list_h_stride, float sm_scale, int dtype, int B, int H,
-                      int N, int D, int32_t* status, void* stream);
+                      int N, int D, int32_t* work_counter, int32_t* status, void* stream);
 
 /*
  * dQ over the row lists (row_ptr/col_idx, as in bsa_attn_fwd); replaces _attn_bwd_dq
@@ -180,7 +181,7 @@ int bsa_attn_bwd_dq(const void* q, const void* k, const void* v, const void* dou
                     const int64_t strides[4], const float* lse2, const float* delta, void* dq,
                     const int32_t* row_ptr, const int32_t* col_idx, int list_b_stride,
                     int list_h_stride, float sm_scale, int dtype, int B, int H, int N, int D,
-                    int32_t* status, void* stream);
+                    int32_t* work_counter, int32_t* status, void* stream);
 
 /*
  * Head-wise token reorder; replaces reorder_kernel (fa2_custom_mask/permute.py:5-58, launched from
