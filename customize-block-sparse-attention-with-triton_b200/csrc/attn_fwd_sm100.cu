@@ -9,7 +9,7 @@
 // has the same amount of exp2 work, whatever the sparsity pattern — the exponentials, not the
 // tensor pipe, bound this kernel at head dimension 64.
 //
-// Roles (16 warps); every role walks the same item sequence, so set-up of item i+1 and write-out
+// Roles (15 warps); every role walks the same item sequence, so set-up of item i+1 and write-out
 // of item i-1 overlap the arithmetic of item i:
 //   warp 8      : producer — draws the item, lists its key blocks (from the mask row, or copies the
 //                 CSR row), TMA-loads Q (twice) and only the listed K/V tiles: K into a 3-deep ring
@@ -29,12 +29,12 @@
 //                 its own S slot, P buffer, accumulator, and (m, l) per lane, so while one team does
 //                 its exponentials the other waits, loads or stores.  A warp loads its 64 S columns
 //                 (which frees the slot for the team's next S at once), takes the row maximum, exp2,
-//                 stores P as 16-bit, and rescales its own accumulator rows when the maximum moved.
-//   warps 12..15: write-out — merge the four partial results (m, l, O) of every query row (teams
+//                 stores P as 16-bit (in two halves, to keep the warp within 128 registers: with
+//                 nothing else on its sub-partition to hide a spill behind, a spilling softmax
+//                 loop ran its arithmetic 2.5x slower), and rescales its own accumulator rows when
+//                 the maximum moved.
+//   warps 11..14: write-out — merge the four partial results (m, l, O) of every query row (teams
 //                 0/1 x lanes r / r+64), normalise, store O, LSE and the row maximum.
-// Warpgroup register re-allocation gives the softmax warps 152 registers (they hold 64 logits and
-// 32 packed probabilities per thread and have nothing to hide a spill behind), the issuing warps 80.
-//
 // TMEM (512 columns): S slots 2 x 128, accumulators 2 x 64, P buffers 2 x 64.
 //
 // Numerics follow the reference's loop (fa2_custom_mask/fa2_fwd.py:150-196): logits scaled by
@@ -59,11 +59,8 @@ constexpr int kKStages = 3;     // K superstages (2 tiles) in flight: held from 
 constexpr int kVStages = 5;     // V superstages (2 tiles) in flight: held from load to P V complete
 constexpr int kSSlots = 2;      // S supertiles (128 TMEM columns), one per softmax team: held from
                                 // S issue to tcgen05.ld
-constexpr int kFwdThreads = 512;  // 16 warps x 128 registers = the whole register file
-constexpr int kSoftmaxWarps = 8, kProducerWarp = 8, kSWarp = 9, kPvWarp = 10, kOutWarp0 = 12;
-// registers per thread after re-allocation: softmax warps 0..7, warps 8..11, write-out warps 12..15
-constexpr int kRegsSoftmax = 152, kRegsIssue = 80, kRegsOut = 128;
-static_assert(256 * kRegsSoftmax + 128 * kRegsIssue + 128 * kRegsOut == 512 * 128, "register file");
+constexpr int kFwdThreads = 480;
+constexpr int kSoftmaxWarps = 8, kProducerWarp = 8, kSWarp = 9, kPvWarp = 10;  // warps 11..14 write out
 constexpr uint32_t kTileBytes = 64 * 64 * 2;       // one Q, K or V tile
 constexpr uint32_t kFwdTmemCols = 512;
 // TMEM columns: S slot r at 128 r; accumulator of softmax team T at 256 + 64 T; P of team T at
@@ -231,12 +228,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const uint32_t tmem = sm->tmem_base;
   volatile int* abort_flag = &sm->abort_flag;
 
-  // The softmax warps keep 64 logits and 32 packed probabilities per thread in registers and have
-  // nothing else on their sub-partition to hide a spill behind; the issuing warps need few.
-  // (Each role's code sits inside the branch that holds its warpgroup's re-allocation, so that
-  // the compiler allots the role that many registers.)
-  if (warp >= kSoftmaxWarps && warp < kOutWarp0) {
-  warpgroup_reg_release<kRegsIssue>();
   if (warp == kProducerWarp) {
     // =========================== producer ===========================
     const bool leader = elect_one();
@@ -448,10 +439,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
     }
     if (!ok) fwd_give_up(sm, p.status, kFailMma);
-  }  // warp 11 only fills the warpgroup of the issuing warps
   } else if (warp < kSoftmaxWarps) {
     // =========================== softmax ===========================
-    warpgroup_reg_acquire<kRegsSoftmax>();
     const int team = warp >> 2;       // supersteps alternate between the two teams of four warps
     const int quarter = warp & 3;     // TMEM lane quarter this warp may touch
     const int t_mine = quarter >> 1;  // lanes 0..63 own tile a of a superstep, 64..127 tile b
@@ -483,19 +472,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       // phase from the one two before it): the S slot is the team's own, phase = the team's count.
       const uint32_t sfull_bar = smem_u32(&sm->s_full[team]);
       const uint32_t s_addr = tmem + lane_base + 128 * team + 64 * t_mine;  // columns [64 t, +64)
-      uint32_t sr[64];
-      bool have_s = false;  // S of the coming superstep is already on its way into sr
 
       for (int u = team; u < n_super; u += 2) {
         const int nt = min(2, n_tiles - 2 * u);
-        if (!have_s) {
-          ok = mbar_wait_warp(sfull_bar, kt & 1, abort_flag);
-          if (!ok) break;
-          tc_fence_after();
-          if (t_mine < nt) {
-            tmem_ld_32x32b_x32(s_addr, sr);
-            tmem_ld_32x32b_x32(s_addr + 32, sr + 32);
-          }
+        ok = mbar_wait_warp(sfull_bar, kt & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        uint32_t sr[64];
+        if (t_mine < nt) {
+          tmem_ld_32x32b_x32(s_addr, sr);
+          tmem_ld_32x32b_x32(s_addr + 32, sr + 32);
         }
         tc_wait_ld();
         // S is in registers: the slot may take the team's next S
@@ -508,7 +494,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const uint32_t pfree_bar = smem_u32(&sm->p_free[team]);
         const uint32_t pfree_par = (kt & 1) ^ 1;  // phase kt-1; passes at once for kt = 0
         bool pfree = mbar_try_wait(pfree_bar, pfree_par);
-        uint32_t pk[32];
+        uint32_t pk[16];
         if (t_mine < nt) {
           const float zmax = fmaxf(max_chunk(sr), max_chunk(sr + 32)) * c;
           m_true = fmaxf(m_true, zmax);
@@ -530,19 +516,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
               pfree = true;
             }
             tc_fence_after();
-#pragma unroll
-            for (int part = 0; part < 2; ++part) {
-              uint32_t orow[32];
-              tmem_ld_32x32b_x32(o_addr + 32 * part, orow);
+#pragma unroll 1
+            for (int part = 0; part < 4; ++part) {
+              uint32_t orow[16];
+              tmem_ld_32x32b_x16(o_addr + 16 * part, orow);
               tc_wait_ld();
 #pragma unroll
-              for (int j = 0; j < 32; ++j)
+              for (int j = 0; j < 16; ++j)
                 orow[j] = __float_as_uint(__uint_as_float(orow[j]) * alpha);
-              tmem_st_32x32b_x32(o_addr + 32 * part, orow);
+              tmem_st_32x32b_x16(o_addr + 16 * part, orow);
             }
           }
           exp_chunk<kBf16>(sr, c, -m_ref, pk, l);
-          exp_chunk<kBf16>(sr + 32, c, -m_ref, pk + 16, l);
         }
         if (!__all_sync(0xffffffffu, pfree)) {
           ok = mbar_wait_warp(pfree_bar, pfree_par, abort_flag);
@@ -550,20 +535,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
         if (t_mine < nt) {
           tc_fence_after();
-          tmem_st_32x32b_x32(p_addr, pk);
-        }
-        // While the P store drains: if the team's next S of this item is complete (it normally
-        // is), start loading it, so that its latency hides behind the store and the arrive.
-        have_s = false;
-        if (u + 2 < n_super) {
-          have_s = __all_sync(0xffffffffu, mbar_try_wait(sfull_bar, (kt + 1) & 1));
-          if (have_s) {
-            tc_fence_after();
-            if (t_mine < min(2, n_tiles - 2 * (u + 2))) {
-              tmem_ld_32x32b_x32(s_addr, sr);
-              tmem_ld_32x32b_x32(s_addr + 32, sr + 32);
-            }
-          }
+          tmem_st_32x32b_x16(p_addr, pk);
+          exp_chunk<kBf16>(sr + 32, c, -m_ref, pk, l);
+          tmem_st_32x32b_x16(p_addr + 16, pk);
         }
         tc_wait_st();
         tc_fence_before();
@@ -584,7 +558,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
     if (!ok) fwd_give_up(sm, p.status, kFailSoftmax);
   } else {
-    warpgroup_reg_release<kRegsOut>();
     // =========================== write-out ===========================
     // Merges the four partial results of every query row (key groups 0/1 x lanes r / r+64).  A warp
     // reads both accumulators of its own lanes from TMEM; lanes 64..127 hand their weighted rows

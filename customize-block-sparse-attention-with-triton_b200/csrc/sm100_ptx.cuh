@@ -26,17 +26,6 @@ __device__ __forceinline__ bool elect_one() {
 __device__ __forceinline__ int uniform_warp_index() {
   return __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
 }
-// Register re-allocation between warpgroups (four consecutive warps, all of which must execute
-// the same instruction): a warpgroup that needs few registers hands some back, one that needs
-// many takes them.  The counts must add up to what the CTA was launched with.
-template <int kRegs>
-__device__ __forceinline__ void warpgroup_reg_release() {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegs));
-}
-template <int kRegs>
-__device__ __forceinline__ void warpgroup_reg_acquire() {
-  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegs));
-}
 __device__ __forceinline__ void named_barrier_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
