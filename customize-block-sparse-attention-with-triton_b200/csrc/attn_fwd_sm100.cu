@@ -69,6 +69,7 @@ constexpr uint32_t kTmemO = 256;
 constexpr uint32_t kTmemP = 384;
 constexpr float kRescaleThreshold = 8.0f;
 constexpr int kFwdMaxTiles = 2048;  // key blocks per row that a CTA can list (N <= 131072)
+constexpr int kMaxSorted = 320;     // items beyond the first round that a CTA can put in order
 
 struct FwdSmem {
   uint8_t q[2][2][kTileBytes];                // by item parity: the query block, twice
@@ -76,11 +77,14 @@ struct FwdSmem {
   uint8_t v[kVStages][2][kTileBytes];
   float xfer[64][65];                         // write-out: lanes 64..127 hand over, [col][row]
   int32_t cols[2][kFwdMaxTiles];              // by item parity: the item's key-block list
+  int cnt[kMaxSorted];                        // tile counts of the items beyond the first round
+  int order[kMaxSorted];                      // those items, longest first
   int ntiles[2];
   int item[2];                                // by item parity: the work item, -1 = no more work
   float mref[2][2][128];                      // by item parity, softmax team, lane
   float lsum[2][2][128];
   float mtrue[2][2][128];
+  uint64_t order_full;                        // `order` is ready
   uint64_t list_full[2];                      // producer -> everyone: list and tile count ready
   uint64_t q_full[2], q_free[2];
   uint64_t k_full[kKStages];
@@ -173,6 +177,68 @@ __device__ __forceinline__ FwdItem fwd_item(int w, const FwdParams& p) {
   return it;
 }
 
+// Mask row of a work item (mask mode); list_*_stride are 0 for a broadcast axis and 1 otherwise.
+__device__ __forceinline__ const uint8_t* fwd_mask_row(const FwdItem& it, const FwdParams& p) {
+  return p.block + (it.b * p.list_b_stride) * p.ms0 + (it.h * p.list_h_stride) * p.ms1 +
+         static_cast<int64_t>(it.mb) * p.ms2;
+}
+
+// Number of kept blocks in a contiguous mask row of nb bytes, read by ONE thread: bytes up to the
+// first 4-byte boundary, then words (a word's non-zero bytes are counted with a byte-wise
+// compare), then the tail.
+__device__ __forceinline__ int fwd_count_row(const uint8_t* row, int nb) {
+  int n = 0, c = 0;
+  const int head = static_cast<int>((4u - (reinterpret_cast<uintptr_t>(row) & 3u)) & 3u);
+  for (; c < head && c < nb; ++c) n += __ldg(row + c) != 0 ? 1 : 0;
+  const uint32_t* w = reinterpret_cast<const uint32_t*>(row + c);
+  const int words = (nb - c) >> 2;
+  int k = 0;
+  for (; k + 4 <= words; k += 4) {
+    const uint32_t a0 = __ldg(w + k), a1 = __ldg(w + k + 1), a2 = __ldg(w + k + 2),
+                   a3 = __ldg(w + k + 3);
+    n += (__popc(__vcmpne4(a0, 0u)) + __popc(__vcmpne4(a1, 0u)) + __popc(__vcmpne4(a2, 0u)) +
+          __popc(__vcmpne4(a3, 0u))) >> 3;
+  }
+  for (; k < words; ++k) n += __popc(__vcmpne4(__ldg(w + k), 0u)) >> 3;
+  for (c += 4 * words; c < nb; ++c) n += __ldg(row + c) != 0 ? 1 : 0;
+  return n;
+}
+
+// When the items are handed out through the work counter and there are at most a few per CTA, it
+// matters who gets which: rows of a random mask differ in length, and the kernel is as slow as
+// the CTA with the largest sum.  The first round is fixed (CTA c takes item c); the remaining
+// items are handed out longest first, so that the CTAs that finish their first item early take
+// the long ones.  Every CTA works the order out for itself (same input, same result) with the
+// four write-out warps, which have nothing to do during the first item: one thread per row counts
+// the row's kept blocks, then every thread ranks its row among all.
+__device__ __forceinline__ void fwd_build_order(FwdSmem* sm, const FwdParams& p, int tid, int first,
+                                                int n2) {
+  for (int j = tid; j < n2; j += 128) {
+    const FwdItem it = fwd_item(first + j, p);
+    int n;
+    if (p.block != nullptr) {
+      n = fwd_count_row(fwd_mask_row(it, p), p.nb);
+    } else {
+      const int64_t li =
+          static_cast<int64_t>(it.b * p.list_b_stride + it.h * p.list_h_stride) * p.nb + it.mb;
+      n = __ldg(p.row_ptr + li + 1) - __ldg(p.row_ptr + li);
+    }
+    sm->cnt[j] = n;
+  }
+  named_barrier_sync(2, 128);
+  for (int j = tid; j < n2; j += 128) {
+    const int cj = sm->cnt[j];
+    int rank = 0;
+    for (int k = 0; k < n2; ++k) {
+      const int ck = sm->cnt[k];
+      rank += (ck > cj || (ck == cj && k < j)) ? 1 : 0;
+    }
+    sm->order[rank] = j;
+  }
+  named_barrier_sync(2, 128);
+  if (tid == 0) mbar_arrive(smem_u32(&sm->order_full));
+}
+
 template <bool kBf16>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -184,6 +250,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int warp = uniform_warp_index();
   const int lane = threadIdx.x & 31;
   const int stride = gridDim.x;
+  // items beyond the first round; few enough per CTA for their order to matter?  (mask mode
+  // needs contiguous mask rows for the count)
+  const int n2 = p.items - stride;
+  const bool sorted = p.ticket != nullptr && n2 > 1 && n2 <= kMaxSorted &&
+                      (p.block == nullptr || p.ms3 == 1);
 
   // ---- set-up ----
   if (threadIdx.x == 0) {
@@ -210,6 +281,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_init(smem_u32(&sm->p_full[i]), kSoftmaxWarps / 2);
       mbar_init(smem_u32(&sm->p_free[i]), 1);
     }
+    mbar_init(smem_u32(&sm->order_full), 1);
     sm->abort_flag = 0;
     mbar_fence_init();
   }
@@ -246,7 +318,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             // `items` tickets in all; whoever draws the last one leaves the counter at zero
             if (t == p.items - 1) atomicExch(p.ticket, 0);
           }
-          w = stride + __shfl_sync(0xffffffffu, t, 0);
+          t = __shfl_sync(0xffffffffu, t, 0);
+          if (sorted && t < n2) {
+            if (i == 1) ok = mbar_wait_warp(smem_u32(&sm->order_full), 0, abort_flag);
+            if (!ok) break;
+            t = *const_cast<volatile int*>(&sm->order[t]);
+          }
+          w = stride + t;
         } else {
           w += stride;
         }
@@ -266,10 +344,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       int32_t* cols = sm->cols[par];
       int n_tiles = 0;
       if (p.block != nullptr) {
-        // mask mode: ordered compaction of the kept blocks of mask row (b, h, mb);
-        // list_*_stride are 0 for a broadcast axis and 1 otherwise here
-        const uint8_t* mrow = p.block + (it.b * p.list_b_stride) * p.ms0 +
-                              (it.h * p.list_h_stride) * p.ms1 + static_cast<int64_t>(it.mb) * p.ms2;
+        // mask mode: ordered compaction of the kept blocks of mask row (b, h, mb)
+        const uint8_t* mrow = fwd_mask_row(it, p);
         for (int c0 = 0; c0 < p.nb; c0 += 128) {
           // four independent loads per lane before the ballots
           bool keep[4];
@@ -565,6 +641,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     // executed, also after a give-up, and the second one carries the give-up vote, so that no warp
     // of this role can be left waiting at one.
     const int quarter = warp & 3;  // lane quarter a warp may touch = its index mod 4
+    if (sorted) fwd_build_order(sm, p, quarter * 32 + lane, stride, n2);
     const int t_mine = quarter >> 1;
     const int lane_row = quarter * 32 + lane;
     const int r_blk = (quarter & 1) * 32 + lane;  // row of the query block

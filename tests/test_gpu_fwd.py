@@ -174,11 +174,14 @@ def test_baseline_sizes_against_gpu_fp32_reference(lib, N, p, dtype):
     assert (o2.float() - 2 * o.float()).abs().max().item() <= 2e-2
 
 
-def test_work_counter_hand_out_equals_fixed_stride(lib):
+@pytest.mark.parametrize("B,H,N", [
+    (2, 8, 2048),     # 512 query blocks: several per CTA, handed out in index order
+    (1, 4, 4096),     # 256 query blocks: at most two per CTA, the second round longest first
+])
+def test_work_counter_hand_out_equals_fixed_stride(lib, B, H, N):
     """With a work counter the CTAs draw query blocks dynamically; the result must not depend on
     who computes which block, and the counter must be back at zero for the next call."""
     from fa2_custom_mask import _lib, fa2_custom_mask as host
-    B, H, N = 2, 8, 2048          # 512 query blocks: several per CTA
     q, k, v = (t.cuda() for t in oracle.make_qkv(B, H, N, 64, seed=5, dtype=torch.float16))
     mask = oracle.make_block_mask(B, H, N // 64, 0.3, seed=6, diagonal=False).cuda()
     m4 = host._as_4d(host._as_bytes(mask))
