@@ -13,7 +13,7 @@
 // of item i-1 overlap the arithmetic of item i:
 //   warp 8      : producer — draws the item, lists its key blocks (from the mask row, or copies the
 //                 CSR row), TMA-loads Q (twice) and only the listed K/V tiles: K into a 3-deep ring
-//                 of superstages (held until S is complete), V into a 5-deep one (held until P V is)
+//                 of superstages (held until S is complete), V into a 6-deep one (held until P V is)
 //   warp 9      : S issuer and TMEM owner — S = [Q;Q] [K_a;K_b]^T as four M=128,N=128,K=16 MMAs
 //                 into the S slot of the softmax team whose superstep it is (lanes 0..63 use columns
 //                 0..63, lanes 64..127 columns 64..127; an N=128 instruction occupies the tensor
@@ -56,7 +56,9 @@
 namespace bsa {
 
 constexpr int kKStages = 3;     // K superstages (2 tiles) in flight: held from load to S complete
-constexpr int kVStages = 5;     // V superstages (2 tiles) in flight: held from load to P V complete
+constexpr int kVStages = 6;     // V superstages (2 tiles) in flight: held from load to P V complete
+                                // (with 5 the producer, which loads K and V of a superstep in
+                                // turn, often waited for a V stage and so held the next K back)
 constexpr int kSSlots = 2;      // S supertiles (128 TMEM columns), one per softmax team: held from
                                 // S issue to tcgen05.ld
 constexpr int kFwdThreads = 480;
