@@ -238,3 +238,41 @@ def test_two_streams_and_graph_replay(lib):
             graph.replay()
             torch.cuda.synchronize()
             assert torch.equal(out, ref)
+
+
+def test_maximum_sequence_length(lib):
+    """N = 131072 (2048 key blocks per row, the most a CTA can list) runs and is right on sampled
+    query blocks; one block more is refused with BSA_ERR_TOO_LARGE before any launch."""
+    from fa2_custom_mask import _lib, attention_forward_masked
+    N, nb = 131072, 2048
+    g = torch.Generator(device="cuda").manual_seed(3)
+    q, k, v = (torch.randn(1, 1, N, 64, device="cuda", generator=g).half() for _ in range(3))
+    mask = torch.rand(1, 1, nb, nb, device="cuda", generator=g) < 0.003
+    mask |= torch.eye(nb, dtype=torch.bool, device="cuda")
+    mask[0, 0, 7, :] = True                       # one row that lists every key block
+    mask[0, 0, 9, :] = False                      # and one that lists none
+    o, lse2, _ = attention_forward_masked(q, k, v, mask, 0.125)
+    torch.cuda.synchronize()
+    for mb in (0, 7, 9, 1000, nb - 1):
+        rows = slice(64 * mb, 64 * mb + 64)
+        s = (q[0, 0, rows].float() @ k[0, 0].float().T) * 0.125
+        dense = mask[0, 0, mb].repeat_interleave(64)[None, :].expand(64, N)
+        s = s.masked_fill(~dense, float("-inf"))
+        if mb == 9:
+            assert (o[0, 0, rows] == 0).all() and (lse2[0, 0, rows] == -math.inf).all()
+            continue
+        ref = torch.softmax(s, -1) @ v[0, 0].float()
+        assert (o[0, 0, rows].float() - ref).abs().max().item() <= O_TOL
+        lse_ref = torch.logsumexp(s, -1)
+        assert (lse2[0, 0, rows] * math.log(2.0) - lse_ref).abs().max().item() <= LSE_TOL
+    # one block more than a CTA can list
+    N2 = N + 64
+    big = torch.empty(1, 1, N2, 64, device="cuda", dtype=torch.float16)
+    m2 = torch.zeros(1, 1, nb + 1, nb + 1, dtype=torch.uint8, device="cuda")
+    lse = torch.empty(1, 1, N2, dtype=torch.float32, device="cuda")
+    rc = lib.bsa_attn_fwd_block_mask(
+        _lib.ptr(big), _lib.strides4(big), _lib.ptr(big), _lib.strides4(big), _lib.ptr(big),
+        _lib.strides4(big), _lib.ptr(big), _lib.strides4(big), _lib.ptr(lse), None, _lib.ptr(m2),
+        _lib.strides4(m2), 1, 1, 0.125, _lib.dtype_code(big.dtype), 1, 1, N2, 64, None, None,
+        _lib.stream_ptr(big.device))
+    assert rc == -8   # BSA_ERR_TOO_LARGE
