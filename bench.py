@@ -248,6 +248,15 @@ def extra_measurements(dev, peak_tf, peak_gbs):
             bms = timed(lambda: attention_backward(q, k, v, o, lse2, do, lists, SM_SCALE), iters)
             btf = tiles * 10 * 64 * 64 * HEAD_DIM / (bms * 1e-3) / 1e12
             rec.update({"bwd_ms": bms, "bwd_tflops": btf, "bwd_frac_of_measured_peak": btf / peak_tf})
+            # the delta kernel alone (HBM-bound: O and dO read once, one float per row written)
+            from fa2_custom_mask import _lib
+            lib = _lib.load()
+            delta = torch.empty((B, H, N), dtype=torch.float32, device=dev)
+            dms = timed(lambda: lib.bsa_attn_bwd_delta(
+                _lib.ptr(o), _lib.ptr(do), _lib.strides4(o), _lib.ptr(delta),
+                _lib.dtype_code(o.dtype), B, H, N, HEAD_DIM, _lib.stream_ptr(dev)), iters)
+            dgb = (2 * o.numel() * o.element_size() + delta.numel() * 4) / (dms * 1e-3) / 1e9
+            rec.update({"delta_ms": dms, "delta_GBps": dgb, "delta_frac_of_measured_hbm": dgb / peak_gbs})
         out[name] = rec
         del q, k, v, do, m, lists
     for N in (17536, 32000):

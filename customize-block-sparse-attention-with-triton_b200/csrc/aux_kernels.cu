@@ -43,16 +43,21 @@ bwd_delta_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ do
                  int64_t sh, int64_t sn, float* __restrict__ delta, int H, int N, int64_t rows) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int sub = lane >> 3, chunk = lane & 7;
-  const int64_t row0 = static_cast<int64_t>(blockIdx.x) * kDeltaRowsPerCta + warp * 16 + sub;
+  // A warp's 16 rows lie in one (batch, head): N is a multiple of 64 and the warp starts at a
+  // multiple of 16, so the division is done once per thread, not once per row.
+  const int64_t warp_row = static_cast<int64_t>(blockIdx.x) * kDeltaRowsPerCta + warp * 16;
+  const int64_t row0 = warp_row + sub;
+  const int64_t bh = warp_row / N;
+  const int64_t n0 = warp_row - bh * N + sub;
+  const int64_t b = bh / H;
+  const int64_t base = b * sb + (bh - b * H) * sh + chunk * 8;
   uint4 xo[4], xd[4];
   bool live[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const int64_t r = row0 + 4 * i;
-    live[i] = r < rows;
+    live[i] = row0 + 4 * i < rows;
     if (live[i]) {
-      const int64_t bh = r / N;
-      const int64_t off = (bh / H) * sb + (bh % H) * sh + (r % N) * sn + chunk * 8;
+      const int64_t off = base + (n0 + 4 * i) * sn;
       xo[i] = __ldg(reinterpret_cast<const uint4*>(o + off));
       xd[i] = __ldg(reinterpret_cast<const uint4*>(dout + off));
     } else {
