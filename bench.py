@@ -276,6 +276,18 @@ def extra_measurements(dev, peak_tf, peak_gbs):
     gbs = 2 * x.numel() * x.element_size() / (ms * 1e-3) / 1e9
     out["reorder_B2_H48_T17550_f16"] = {"ms": ms, "GBps": gbs, "frac_of_measured_hbm": gbs / peak_gbs}
     del x
+    # the whole wrapper as a model calls it: q, k, v with 226 text tokens in front, image tokens
+    # gathered out of the slice and copied back in place (two passes per tensor; bytes counted are
+    # those of one pass, so 0.5 of the copy bandwidth is the ceiling)
+    from fa2_custom_mask import permute_qkv_triton
+    qkv = [torch.randn(Bv, Hv, 226 + Fv * Yv * Xv, HEAD_DIM, device=dev, dtype=torch.float16)
+           for _ in range(3)]
+    plan = {"permute": (torch.arange(Hv, device=dev) % 6)[None]}
+    ms = timed(lambda: permute_qkv_triton(*qkv, plan, 0, Fv, Yv, Xv, 226), 10)
+    gbs = 3 * 2 * Bv * Hv * Fv * Yv * Xv * HEAD_DIM * 2 / (ms * 1e-3) / 1e9
+    out["permute_qkv_B2_H48_T226+17550_f16"] = {"ms": ms, "GBps_one_pass": gbs,
+                                                "frac_of_measured_hbm": gbs / peak_gbs}
+    del qkv
     return out
 
 

@@ -110,7 +110,7 @@ constexpr int kReorderPieces = 4;  // independent loads in flight per thread
 template <typename Vec, bool kInverse>
 __global__ void __launch_bounds__(kReorderThreads)
 reorder_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, int64_t sb, int64_t sh,
-               int64_t st, const int32_t* __restrict__ orders,
+               int64_t st, int64_t ob, int64_t oh, int64_t ot, const int32_t* __restrict__ orders,
                const int32_t* __restrict__ inv_orders, int heads, int n_bh, int T, int F, int Hh,
                int W, int vec_per_row) {
   const uint32_t per_head = static_cast<uint32_t>(T) * static_cast<uint32_t>(vec_per_row);
@@ -130,7 +130,7 @@ reorder_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, int64_
       p2 = __ldg(inv_orders + 3 * h + 2);
     }
     const uint8_t* src = in + b * sb + h * sh;  // byte offsets
-    uint8_t* dst = out + b * sb + h * sh;
+    uint8_t* dst = out + b * ob + h * oh;
     Vec val[kReorderPieces];
     int64_t to[kReorderPieces];
 #pragma unroll
@@ -141,7 +141,7 @@ reorder_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, int64_
         const int t = static_cast<int>(idx / static_cast<uint32_t>(vec_per_row));
         const int piece = static_cast<int>(idx - static_cast<uint32_t>(t) * vec_per_row);
         val[i] = *reinterpret_cast<const Vec*>(src + t * st + piece * sizeof(Vec));
-        to[i] = permuted_token(t, e0, e1, e2, p0, p1, p2) * st + piece * sizeof(Vec);
+        to[i] = permuted_token(t, e0, e1, e2, p0, p1, p2) * ot + piece * sizeof(Vec);
       }
     }
 #pragma unroll
@@ -151,8 +151,8 @@ reorder_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, int64_
 }
 
 template <bool kInverse>
-static int launch_reorder(const void* in, void* out, const int64_t s[4], const int32_t* orders,
-                          const int32_t* inv_orders, int B, int heads, int T, int D, int F, int Hh,
+static int launch_reorder(const void* in, const int64_t s[4], void* out, const int64_t so[4],
+                          const int32_t* orders, const int32_t* inv_orders, int B, int heads, int T, int D, int F, int Hh,
                           int W, int elem_bytes, void* stream) {
   if (B <= 0 || heads <= 0 || T <= 0 || D <= 0 || F <= 0 || Hh <= 0 || W <= 0 ||
       static_cast<int64_t>(F) * Hh * W != T)
@@ -160,14 +160,17 @@ static int launch_reorder(const void* in, void* out, const int64_t s[4], const i
   if (elem_bytes != 1 && elem_bytes != 2 && elem_bytes != 4 && elem_bytes != 8)
     return BSA_ERR_BAD_DTYPE;
   if (!in || !out || !orders || (kInverse && !inv_orders)) return BSA_ERR_BAD_POINTER;
+  if (!s || !so) return BSA_ERR_BAD_POINTER;
   if (s[3] != 1 || s[0] < 0 || s[1] < 0 || s[2] < 0) return BSA_ERR_BAD_STRIDE;
+  if (so[3] != 1 || so[0] < 0 || so[1] < 0 || so[2] < 0) return BSA_ERR_BAD_STRIDE;
   const int64_t row_bytes = static_cast<int64_t>(D) * elem_bytes;
   const int64_t sb = s[0] * elem_bytes, sh = s[1] * elem_bytes, st = s[2] * elem_bytes;
+  const int64_t ob = so[0] * elem_bytes, oh = so[1] * elem_bytes, ot = so[2] * elem_bytes;
   // widest piece that divides the row and keeps every access aligned
   int vec = 16;
   auto fits = [&](int v) {
-    return row_bytes % v == 0 && sb % v == 0 && sh % v == 0 && st % v == 0 && is_aligned(in, v) &&
-           is_aligned(out, v);
+    return row_bytes % v == 0 && sb % v == 0 && sh % v == 0 && st % v == 0 && ob % v == 0 &&
+           oh % v == 0 && ot % v == 0 && is_aligned(in, v) && is_aligned(out, v);
   };
   while (vec > elem_bytes && !fits(vec)) vec >>= 1;
   if (!fits(vec)) return BSA_ERR_BAD_POINTER;
@@ -182,8 +185,8 @@ static int launch_reorder(const void* in, void* out, const int64_t s[4], const i
   const uint8_t* pi = static_cast<const uint8_t*>(in);
   uint8_t* po = static_cast<uint8_t*>(out);
 #define BSA_LAUNCH_REORDER(V)                                                                      \
-  reorder_kernel<V, kInverse><<<g, kReorderThreads, 0, cs>>>(pi, po, sb, sh, st, orders,           \
-                                                             inv_orders, heads,                    \
+  reorder_kernel<V, kInverse><<<g, kReorderThreads, 0, cs>>>(pi, po, sb, sh, st, ob, oh, ot,       \
+                                                             orders, inv_orders, heads,            \
                                                              static_cast<int>(n_bh), T, F, Hh, W,  \
                                                              vec_per_row)
   switch (vec) {
@@ -226,13 +229,29 @@ extern "C" int bsa_attn_bwd_delta(const void* o, const void* dout, const int64_t
 extern "C" int bsa_reorder(const void* in, void* out, const int64_t strides[4],
                            const int32_t* orders, int B, int heads, int T, int D, int F, int Hh,
                            int W, int elem_bytes, void* stream) {
-  return bsa::launch_reorder<false>(in, out, strides, orders, nullptr, B, heads, T, D, F, Hh, W,
-                                    elem_bytes, stream);
+  return bsa::launch_reorder<false>(in, strides, out, strides, orders, nullptr, B, heads, T, D, F,
+                                    Hh, W, elem_bytes, stream);
+}
+
+extern "C" int bsa_reorder_strided(const void* in, const int64_t in_strides[4], void* out,
+                                   const int64_t out_strides[4], const int32_t* orders, int B,
+                                   int heads, int T, int D, int F, int Hh, int W, int elem_bytes,
+                                   void* stream) {
+  return bsa::launch_reorder<false>(in, in_strides, out, out_strides, orders, nullptr, B, heads, T,
+                                    D, F, Hh, W, elem_bytes, stream);
 }
 
 extern "C" int bsa_inv_reorder(const void* in, void* out, const int64_t strides[4],
                                const int32_t* orders, const int32_t* inv_orders, int B, int heads,
                                int T, int D, int F, int Hh, int W, int elem_bytes, void* stream) {
-  return bsa::launch_reorder<true>(in, out, strides, orders, inv_orders, B, heads, T, D, F, Hh, W,
-                                   elem_bytes, stream);
+  return bsa::launch_reorder<true>(in, strides, out, strides, orders, inv_orders, B, heads, T, D, F,
+                                   Hh, W, elem_bytes, stream);
+}
+
+extern "C" int bsa_inv_reorder_strided(const void* in, const int64_t in_strides[4], void* out,
+                                       const int64_t out_strides[4], const int32_t* orders,
+                                       const int32_t* inv_orders, int B, int heads, int T, int D,
+                                       int F, int Hh, int W, int elem_bytes, void* stream) {
+  return bsa::launch_reorder<true>(in, in_strides, out, out_strides, orders, inv_orders, B, heads,
+                                   T, D, F, Hh, W, elem_bytes, stream);
 }

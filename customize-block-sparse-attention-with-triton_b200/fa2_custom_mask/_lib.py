@@ -52,6 +52,8 @@ SIGNATURES = {
                         _i, _i, _i, _i, _vp, _vp, _vp],
     "bsa_reorder": [_vp, _vp, _s4, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "bsa_inv_reorder": [_vp, _vp, _s4, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "bsa_reorder_strided": [_vp, _s4, _vp, _s4, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "bsa_inv_reorder_strided": [_vp, _s4, _vp, _s4, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "bsa_attn_fwd_block_mask_static": [_vp, _s4, _vp, _s4, _vp, _s4, _vp, _s4, _vp, _vp, _s4, _i,
                                        _i, _f, _i, _i, _i, _i, _i, _vp],
     "bsa_check_status": [_vp, _vp],

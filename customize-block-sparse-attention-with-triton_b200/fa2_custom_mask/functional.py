@@ -46,15 +46,13 @@ def apply_head_wise_reorder(tensor, permute_orders, F, H, W):
     axis order permute_orders[h] (reorder_kernel, fa2_custom_mask/permute.py:5-58)."""
     lib = _lib.load()
     tensor, BS, N_head, N_token, D = _check(tensor, F, H, W)
-    output = torch.empty_like(tensor)
-    if output.stride() != tensor.stride():  # the kernel shares one stride set, as the reference does
-        tensor = tensor.contiguous()
-        output = torch.empty_like(tensor)
+    # a slice or any other view with unit last stride is read where it lies; the result is dense
+    output = torch.empty(tensor.shape, dtype=tensor.dtype, device=tensor.device)
     orders = _orders_i32(permute_orders, tensor.device)
     with torch.cuda.device(tensor.device):
-        _lib.check("bsa_reorder", lib.bsa_reorder(
-            _lib.ptr(tensor), _lib.ptr(output), _lib.strides4(tensor), _lib.ptr(orders),
-            BS, N_head, N_token, D, F, H, W, tensor.element_size(),
+        _lib.check("bsa_reorder_strided", lib.bsa_reorder_strided(
+            _lib.ptr(tensor), _lib.strides4(tensor), _lib.ptr(output), _lib.strides4(output),
+            _lib.ptr(orders), BS, N_head, N_token, D, F, H, W, tensor.element_size(),
             _lib.stream_ptr(tensor.device)))
     return output
 
@@ -67,7 +65,7 @@ def permute_qkv_triton(query, key, value, permute_plan, i_block, F=13, H=30, W=4
     permute_orders = permutations[idx]      # [N_head, 3]
     for t in (query, key, value):
         image = t[:, :, n_text_tokens:, :]
-        t[:, :, n_text_tokens:, :] = apply_head_wise_reorder(image.contiguous(), permute_orders, F, H, W)
+        t[:, :, n_text_tokens:, :] = apply_head_wise_reorder(image, permute_orders, F, H, W)
     return query, key, value
 
 
@@ -76,17 +74,14 @@ def apply_inv_reorder(tensor, permute_orders, inv_permute_orders, F, H, W):
     in the order permute_orders[h]; inv_permute_orders[h] lays it back to (F, H, W)."""
     lib = _lib.load()
     tensor, BS, N_head, N_token, D = _check(tensor, F, H, W)
-    output = torch.empty_like(tensor)
-    if output.stride() != tensor.stride():
-        tensor = tensor.contiguous()
-        output = torch.empty_like(tensor)
+    output = torch.empty(tensor.shape, dtype=tensor.dtype, device=tensor.device)
     orders = _orders_i32(permute_orders, tensor.device)
     inv_orders = _orders_i32(inv_permute_orders, tensor.device)
     with torch.cuda.device(tensor.device):
-        _lib.check("bsa_inv_reorder", lib.bsa_inv_reorder(
-            _lib.ptr(tensor), _lib.ptr(output), _lib.strides4(tensor), _lib.ptr(orders),
-            _lib.ptr(inv_orders), BS, N_head, N_token, D, F, H, W, tensor.element_size(),
-            _lib.stream_ptr(tensor.device)))
+        _lib.check("bsa_inv_reorder_strided", lib.bsa_inv_reorder_strided(
+            _lib.ptr(tensor), _lib.strides4(tensor), _lib.ptr(output), _lib.strides4(output),
+            _lib.ptr(orders), _lib.ptr(inv_orders), BS, N_head, N_token, D, F, H, W,
+            tensor.element_size(), _lib.stream_ptr(tensor.device)))
     return output
 
 
@@ -99,5 +94,5 @@ def inv_permute_attn_triton(attn_out, permute_plan, i_block, F=13, H=30, W=45, n
     inv_permute_orders = permutations_inv[idx]
     attn_image = attn_out[:, :, n_text_tokens:, :]
     attn_out[:, :, n_text_tokens:, :] = apply_inv_reorder(
-        attn_image.contiguous(), permute_orders, inv_permute_orders, F, H, W)
+        attn_image, permute_orders, inv_permute_orders, F, H, W)
     return attn_out

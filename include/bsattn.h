@@ -205,6 +205,21 @@ int bsa_inv_reorder(const void* in, void* out, const int64_t strides[4], const i
                     int elem_bytes, void* stream);
 
 /*
+ * The same two gathers with separate element strides for `in` and `out` (last stride 1 in both).
+ * The reference's kernels share one stride set, so its wrappers first copy the image-token slice
+ * of q, k, v to a contiguous tensor (fa2_custom_mask/functional.py:35-37, 82); with these entry
+ * points the slice is read where it lies and that copy disappears.  `in` and `out` must not
+ * overlap.
+ */
+int bsa_reorder_strided(const void* in, const int64_t in_strides[4], void* out,
+                        const int64_t out_strides[4], const int32_t* orders, int B, int heads, int T,
+                        int D, int F, int Hh, int W, int elem_bytes, void* stream);
+int bsa_inv_reorder_strided(const void* in, const int64_t in_strides[4], void* out,
+                            const int64_t out_strides[4], const int32_t* orders,
+                            const int32_t* inv_orders, int B, int heads, int T, int D, int F, int Hh,
+                            int W, int elem_bytes, void* stream);
+
+/*
  * Forward attention directly from a block mask, allocating nothing.  It has no counterpart in the
  * reference; it exists for hosts that cannot hand the library device buffers at call time, such as
  * an inference-engine plugin whose workspace was sized when the engine was built, or a process
