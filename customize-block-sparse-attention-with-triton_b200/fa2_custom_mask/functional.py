@@ -41,6 +41,28 @@ def _orders_i32(orders, device):
     return orders.to(device=device, dtype=torch.int32).contiguous()
 
 
+def _identity_orders(device, n_head):
+    key = (device.type, device.index, n_head)
+    if key not in _table_cache:
+        _table_cache[key] = torch.tensor([[0, 1, 2]], dtype=torch.int32, device=device).repeat(n_head, 1)
+    return _table_cache[key]
+
+
+def _write_back(view, dense, F, H, W):
+    """view[...] = dense for a slice `view` of a caller's tensor, through the gather kernel with
+    the identity order (it moves 16-byte pieces at the copy bandwidth whatever the strides)."""
+    lib = _lib.load()
+    BS, N_head, N_token, D = view.shape
+    if view.stride(3) != 1 or dense.stride(3) != 1:
+        view.copy_(dense)
+        return
+    with torch.cuda.device(view.device):
+        _lib.check("bsa_reorder_strided", lib.bsa_reorder_strided(
+            _lib.ptr(dense), _lib.strides4(dense), _lib.ptr(view), _lib.strides4(view),
+            _lib.ptr(_identity_orders(view.device, N_head)), BS, N_head, N_token, D, F, H, W,
+            view.element_size(), _lib.stream_ptr(view.device)))
+
+
 def apply_head_wise_reorder(tensor, permute_orders, F, H, W):
     """out[b, h, new_t] = tensor[b, h, t]; new_t re-lays-out t's (f, y, x) grid coordinate in the
     axis order permute_orders[h] (reorder_kernel, fa2_custom_mask/permute.py:5-58)."""
@@ -65,7 +87,7 @@ def permute_qkv_triton(query, key, value, permute_plan, i_block, F=13, H=30, W=4
     permute_orders = permutations[idx]      # [N_head, 3]
     for t in (query, key, value):
         image = t[:, :, n_text_tokens:, :]
-        t[:, :, n_text_tokens:, :] = apply_head_wise_reorder(image, permute_orders, F, H, W)
+        _write_back(image, apply_head_wise_reorder(image, permute_orders, F, H, W), F, H, W)
     return query, key, value
 
 
@@ -93,6 +115,6 @@ def inv_permute_attn_triton(attn_out, permute_plan, i_block, F=13, H=30, W=45, n
     permute_orders = permutations[idx]
     inv_permute_orders = permutations_inv[idx]
     attn_image = attn_out[:, :, n_text_tokens:, :]
-    attn_out[:, :, n_text_tokens:, :] = apply_inv_reorder(
-        attn_image, permute_orders, inv_permute_orders, F, H, W)
+    _write_back(attn_image, apply_inv_reorder(attn_image, permute_orders, inv_permute_orders, F, H, W),
+                F, H, W)
     return attn_out
