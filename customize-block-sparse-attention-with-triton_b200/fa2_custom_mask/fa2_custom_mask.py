@@ -323,7 +323,8 @@ class _attention(torch.autograd.Function):
         assert q.shape[-1] == k.shape[-1] == v.shape[-1]
         assert D in {16, 32, 64, 128, 256}  # the reference's own check (fa2_custom_mask.py:58)
         if D != 64:
-            raise NotImplementedError("this build supports head dimension 64 only")
+            raise NotImplementedError("the kernels are built for head dimension 64 (16 and 32 are "
+                                      "zero-padded to it by flash_attention_custom_mask)")
         if N % BLOCK:
             raise AssertionError("sequence length must be a multiple of 64")
         if not q.is_cuda:
@@ -352,4 +353,15 @@ class _attention(torch.autograd.Function):
         return dq, dk, dv, None, None
 
 
-flash_attention_custom_mask = _attention.apply
+def flash_attention_custom_mask(q, k, v, mask=None, sm_scale=1.3):
+    """The reference's public op (fa2_custom_mask/fa2_custom_mask.py:157, `_attention.apply`), same
+    positional arguments.  Head dimensions 16 and 32 run on the D = 64 kernels with zero columns
+    appended to q, k, v (Q K^T is unchanged, the extra columns of P V are zero and are cut off
+    again; autograd slices the gradients); 128 and 256, which the reference also lists, are not
+    built."""
+    D = q.shape[-1] if q.dim() == 4 else 0
+    if D in (16, 32) and k.shape == q.shape and v.shape == q.shape:
+        pad = (0, 64 - D)
+        qp, kp, vp = (torch.nn.functional.pad(t, pad) for t in (q, k, v))
+        return _attention.apply(qp, kp, vp, mask, sm_scale)[..., :D].contiguous()
+    return _attention.apply(q, k, v, mask, sm_scale)

@@ -90,3 +90,25 @@ def test_baseline_config5_shape_one_head(lib):
     assert worst_dq <= G_TOL
     assert (kc.grad[0, 0].float() - dk_ref).abs().max().item() <= G_TOL
     assert (vc.grad[0, 0].float() - dv_ref).abs().max().item() <= G_TOL
+
+
+@pytest.mark.parametrize("D", [16, 32])
+def test_small_head_dimensions_are_padded(lib, D):
+    """The reference accepts D in {16, 32, 64, 128, 256} (fa2_custom_mask.py:58); 16 and 32 run on
+    the D = 64 kernels with zero columns appended."""
+    q, k, v, do = oracle.make_qkv(1, 2, 256, D, seed=D, dtype=torch.float16, n=4)
+    mask = oracle.make_block_mask(1, 2, 4, 0.5, seed=D)
+    sm_scale = D ** -0.5
+    o, dq, dk, dv = _grads(q, k, v, do, mask, sm_scale)
+    assert o.shape == q.shape and dq.shape == q.shape and dv.shape == v.shape
+    o_ref, _, dq_ref, dk_ref, dv_ref = oracle.attn_forward_backward(q, k, v, mask, sm_scale, do)
+    assert (o - o_ref).abs().max() <= 2e-2
+    for got, ref in ((dq, dq_ref), (dk, dk_ref), (dv, dv_ref)):
+        assert (got - ref).abs().max().item() <= G_TOL
+
+
+def test_large_head_dimensions_are_refused(lib):
+    from fa2_custom_mask import flash_attention_custom_mask
+    q = torch.zeros(1, 1, 64, 128, dtype=torch.float16, device="cuda")
+    with pytest.raises(NotImplementedError):
+        flash_attention_custom_mask(q, q, q, None, 0.1)
