@@ -240,6 +240,33 @@ def test_two_streams_and_graph_replay(lib):
             assert torch.equal(out, ref)
 
 
+def test_public_op_with_dense_mask_in_a_graph(lib):
+    """Dense mask -> block mask -> forward, the whole public call, holds no host synchronisation:
+    it can be captured into a CUDA graph and replays on new inputs (mask included) written into
+    the same buffers."""
+    from fa2_custom_mask import flash_attention_custom_mask
+    B, H, N = 1, 2, 1024
+    q, k, v = (t.cuda() for t in oracle.make_qkv(B, H, N, 64, seed=21, dtype=torch.bfloat16))
+    block = oracle.make_block_mask(B, H, N // 64, 0.4, seed=21)
+    dense = oracle.expand_block_mask(block).cuda()
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s), torch.no_grad():
+        flash_attention_custom_mask(q, k, v, dense, 0.125)   # loads the library outside the capture
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=s):
+            out = flash_attention_custom_mask(q, k, v, dense, 0.125)
+        for seed in (22, 23):
+            q2, k2, v2 = oracle.make_qkv(B, H, N, 64, seed=seed, dtype=torch.bfloat16)
+            block2 = oracle.make_block_mask(B, H, N // 64, 0.3, seed=seed)
+            q.copy_(q2); k.copy_(k2); v.copy_(v2)
+            dense.copy_(oracle.expand_block_mask(block2))
+            graph.replay()
+            torch.cuda.synchronize()
+            ref, _ = oracle.attn_forward(q2, k2, v2, block2, 0.125)
+            assert (out.float().cpu() - ref).abs().max() <= O_TOL
+
+
 def test_maximum_sequence_length(lib):
     """N = 131072 (2048 key blocks per row, the most a CTA can list) runs and is right on sampled
     query blocks; one block more is refused with BSA_ERR_TOO_LARGE before any launch."""
