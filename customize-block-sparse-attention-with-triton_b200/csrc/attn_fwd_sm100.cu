@@ -79,7 +79,7 @@ struct FwdSmem {
   uint8_t v[kVStages][2][kTileBytes];
   float xfer[64][65];                         // write-out: lanes 64..127 hand over, [col][row]
   int32_t cols[2][kFwdMaxTiles];              // by item parity: the item's key-block list
-  int cnt[kMaxSorted];                        // tile counts of the items beyond the first round
+  alignas(16) int cnt[kMaxSorted];            // sort keys (tile count, item) of the items beyond the first round
   int order[kMaxSorted];                      // those items, longest first
   int ntiles[2];
   int item[2];                                // by item parity: the work item, -1 = no more work
@@ -195,6 +195,15 @@ __device__ __forceinline__ int fwd_count_row(const uint8_t* row, int nb) {
   const uint32_t* w = reinterpret_cast<const uint32_t*>(row + c);
   const int words = (nb - c) >> 2;
   int k = 0;
+  for (; k + 16 <= words; k += 16) {
+    uint32_t a[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) a[j] = __ldg(w + k + j);
+    int bits = 0;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) bits += __popc(__vcmpne4(a[j], 0u));
+    n += bits >> 3;
+  }
   for (; k + 4 <= words; k += 4) {
     const uint32_t a0 = __ldg(w + k), a1 = __ldg(w + k + 1), a2 = __ldg(w + k + 2),
                    a3 = __ldg(w + k + 3);
@@ -225,17 +234,23 @@ __device__ __forceinline__ void fwd_build_order(FwdSmem* sm, const FwdParams& p,
           static_cast<int64_t>(it.b * p.list_b_stride + it.h * p.list_h_stride) * p.nb + it.mb;
       n = __ldg(p.row_ptr + li + 1) - __ldg(p.row_ptr + li);
     }
-    sm->cnt[j] = n;
+    // one key per item, all different: longer rows first, equal rows in item order
+    sm->cnt[j] = n * 512 + (511 - j);
   }
+  const int n4 = (n2 + 3) & ~3;
+  for (int j = n2 + tid; j < n4; j += 128) sm->cnt[j] = -1;  // padding ranks behind every item
   named_barrier_sync(2, 128);
   for (int j = tid; j < n2; j += 128) {
-    const int cj = sm->cnt[j];
-    int rank = 0;
-    for (int k = 0; k < n2; ++k) {
-      const int ck = sm->cnt[k];
-      rank += (ck > cj || (ck == cj && k < j)) ? 1 : 0;
+    const int kj = sm->cnt[j];
+    int r0 = 0, r1 = 0, r2 = 0, r3 = 0;
+    for (int k = 0; k < n4; k += 4) {
+      const int4 c = *reinterpret_cast<const int4*>(&sm->cnt[k]);
+      r0 += c.x > kj ? 1 : 0;
+      r1 += c.y > kj ? 1 : 0;
+      r2 += c.z > kj ? 1 : 0;
+      r3 += c.w > kj ? 1 : 0;
     }
-    sm->order[rank] = j;
+    sm->order[(r0 + r1) + (r2 + r3)] = j;
   }
   named_barrier_sync(2, 128);
   if (tid == 0) mbar_arrive(smem_u32(&sm->order_full));
