@@ -57,6 +57,7 @@ SIGNATURES = {
     "bsa_attn_fwd_block_mask_static": [_vp, _s4, _vp, _s4, _vp, _s4, _vp, _s4, _vp, _vp, _s4, _i,
                                        _i, _f, _i, _i, _i, _i, _i, _vp],
     "bsa_check_status": [_vp, _vp],
+    "bsa_selftest_bounded_wait": [_vp, _vp, _vp],
 }
 
 

@@ -251,6 +251,18 @@ int bsa_attn_fwd_block_mask_static(const void* q, const int64_t q_strides[4], co
  */
 int bsa_check_status(const int32_t* status, void* stream);
 
+/*
+ * Self-test of the kernels' bounded waits; no reference counterpart.  Launches one small CTA in
+ * which one warp waits on a barrier that nothing ever completes and a second warp waits beside
+ * it.  The first wait runs out after the library's wait limit (about two seconds), records 99 in
+ * `status` (optional) and raises the CTA's give-up flag, which releases the second warp; both
+ * leave through the end of the kernel.  `report` (device, 4 x int32) receives: [0] 1 if the first
+ * wait was satisfied (never), [1] the same for the second, [2] 1 once both warps reached the end
+ * of the kernel, [3] milliseconds spent.  The context stays usable; bsa_check_status on the same
+ * word then returns BSA_ERR_DEVICE_TIMEOUT.
+ */
+int bsa_selftest_bounded_wait(int32_t* status, int32_t* report, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

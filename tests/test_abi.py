@@ -61,6 +61,7 @@ def test_shape_and_dtype_checks_come_before_any_cuda_call(lib):
     assert lib.bsa_mask_reduce(fake, s4, 1, 1, 100, fake, None, None) == -1
     assert lib.bsa_reorder(fake, fake, s4, fake, 1, 1, 10, 8, 2, 2, 2, 2, None) == -1  # F*H*W != T
     assert lib.bsa_reorder(fake, fake, s4, fake, 1, 1, 8, 8, 2, 2, 2, 3, None) == -2   # elem size
+    assert lib.bsa_selftest_bounded_wait(None, None, None) == -4
     bad_out = (ctypes.c_int64 * 4)(64, 64, 8, 2)
     assert lib.bsa_reorder_strided(fake, s4, fake, bad_out, fake, 1, 1, 8, 8, 2, 2, 2, 2, None) == -3
     assert lib.bsa_inv_reorder_strided(fake, s4, fake, s4, fake, None, 1, 1, 8, 8, 2, 2, 2, 2,

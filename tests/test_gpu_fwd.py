@@ -303,3 +303,32 @@ def test_maximum_sequence_length(lib):
         _lib.strides4(m2), 1, 1, 0.125, _lib.dtype_code(big.dtype), 1, 1, N2, 64, None, None,
         _lib.stream_ptr(big.device))
     assert rc == -8   # BSA_ERR_TOO_LARGE
+
+
+def test_bounded_wait_runs_out_and_reports(lib):
+    """A wait that nothing satisfies gives up after the wait limit, reports through the status
+    word and leaves the context usable (no trap, no endless loop); the host-side check raises and
+    forgets the device's work counters, and the next launch is right again."""
+    import time
+    from fa2_custom_mask import _lib, attention_forward_masked, check_status, new_status_word
+    from fa2_custom_mask import fa2_custom_mask as host
+    q, k, v = (t.cuda() for t in oracle.make_qkv(1, 2, 512, 64, seed=31, dtype=torch.float16))
+    mask = oracle.make_block_mask(1, 2, 8, 0.5, seed=31).cuda()
+    ref = attention_forward_masked(q, k, v, mask, 0.125)[0]      # creates this stream's counter
+    assert any(key[0] == q.device.index for key in host._work_counters)
+    status = new_status_word(q.device)
+    report = torch.full((4,), -1, dtype=torch.int32, device="cuda")
+    t0 = time.time()
+    rc = lib.bsa_selftest_bounded_wait(_lib.ptr(status), _lib.ptr(report), _lib.stream_ptr(q.device))
+    assert rc == 0
+    with pytest.raises(_lib.BsaError) as err:
+        check_status(status)
+    assert err.value.status == -9                                 # BSA_ERR_DEVICE_TIMEOUT
+    assert time.time() - t0 < 30
+    r = report.cpu().tolist()
+    assert r[:3] == [0, 0, 1] and 1000 <= r[3] <= 10000           # gave up after about 2 s
+    assert int(status.item()) == 99
+    assert not any(key[0] == q.device.index for key in host._work_counters)
+    out = attention_forward_masked(q, k, v, mask, 0.125)[0]       # the context is still usable
+    torch.cuda.synchronize()
+    assert torch.equal(out, ref)
