@@ -446,11 +446,29 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
               l[0] = l[1] = l[2] = l[3] = my_lse;
               d[0] = d[1] = d[2] = d[3] = my_delta;
             }
+            // two columns per instruction where the operands allow it (same rounding as scalar)
             float pv[4], dsv[4];
 #pragma unroll
-            for (int t = 0; t < 4; ++t) {
-              pv[t] = ex2_approx(fmaf(__uint_as_float(xs[i + t]), c, -l[t]));
-              dsv[t] = pv[t] * (__uint_as_float(xd[i + t]) - d[t]);
+            for (int t = 0; t < 4; t += 2) {
+              const uint64_t dp2 =
+                  pack_f32x2(__uint_as_float(xd[i + t]), __uint_as_float(xd[i + t + 1]));
+              uint64_t diff2;
+              if constexpr (kDKDV) {
+                // LSE and delta differ from column to column here
+                pv[t] = ex2_approx(fmaf(__uint_as_float(xs[i + t]), c, -l[t]));
+                pv[t + 1] = ex2_approx(fmaf(__uint_as_float(xs[i + t + 1]), c, -l[t + 1]));
+                diff2 = fma_f32x2(pack_f32x2(d[t], d[t + 1]), pack_f32x2(-1.f, -1.f), dp2);
+              } else {
+                float z0, z1;
+                unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(xs[i + t]),
+                                                  __uint_as_float(xs[i + t + 1])),
+                                       pack_f32x2(c, c), pack_f32x2(-my_lse, -my_lse)),
+                             z0, z1);
+                pv[t] = ex2_approx(z0);
+                pv[t + 1] = ex2_approx(z1);
+                diff2 = add_f32x2(dp2, pack_f32x2(-my_delta, -my_delta));
+              }
+              unpack_f32x2(mul_f32x2(pack_f32x2(pv[t], pv[t + 1]), diff2), dsv[t], dsv[t + 1]);
             }
             pk_p[i / 2] = pack_2x16<kBf16>(pv[0], pv[1]);
             pk_p[i / 2 + 1] = pack_2x16<kBf16>(pv[2], pv[3]);
