@@ -135,7 +135,7 @@ template <bool kBf16>
 __device__ __forceinline__ void exp_chunk(const uint32_t* sr, float c, float neg_m, uint32_t* pk,
                                           float& l) {
   const uint64_t c2 = pack_f32x2(c, c), m2 = pack_f32x2(neg_m, neg_m);
-  uint64_t l01 = pack_f32x2(0.f, 0.f), l23 = l01;
+  uint64_t l01 = pack_f32x2(0.f, 0.f);
 #pragma unroll
   for (int i = 0; i < 32; i += 4) {
     float z0, z1, z2, z3;
@@ -145,15 +145,13 @@ __device__ __forceinline__ void exp_chunk(const uint32_t* sr, float c, float neg
         fma_f32x2(pack_f32x2(__uint_as_float(sr[i + 2]), __uint_as_float(sr[i + 3])), c2, m2), z2,
         z3);
     const float p0 = ex2_approx(z0), p1 = ex2_approx(z1), p2 = ex2_approx(z2), p3 = ex2_approx(z3);
-    l01 = add_f32x2(l01, pack_f32x2(p0, p1));
-    l23 = add_f32x2(l23, pack_f32x2(p2, p3));
+    l01 = add_f32x2(add_f32x2(l01, pack_f32x2(p0, p1)), pack_f32x2(p2, p3));
     pk[i / 2] = pack_2x16<kBf16>(p0, p1);
     pk[i / 2 + 1] = pack_2x16<kBf16>(p2, p3);
   }
-  float a0, a1, a2, a3;
+  float a0, a1;
   unpack_f32x2(l01, a0, a1);
-  unpack_f32x2(l23, a2, a3);
-  l += (a0 + a1) + (a2 + a3);
+  l += a0 + a1;
 }
 
 __device__ __forceinline__ float max3(float a, float b, float c) {
