@@ -83,7 +83,7 @@ struct BwdParams {
 
 __device__ __forceinline__ void bwd_give_up(BwdSmem* sm, int32_t* status, int code) {
   sm->abort_flag = 1;
-  if (status) atomicCAS(status, 0, code);
+  report_status(status, code);
 }
 
 // Stores 32 columns of one output row: (own[i] + other[i]) * scale as 16-bit.
@@ -196,6 +196,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
     // =========================== TMA producer ===========================
     const bool leader = elect_one();
     bool ok = true;
+    bool terminal = p.ticket == nullptr;  // drew a ticket past the end (or draws none)
     int gs = 0, ni = 0;
     for (int i = 0, w = blockIdx.x; ok; ++i) {
       const int par = i & 1;
@@ -209,6 +210,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
             if (t == p.items - 1) atomicExch(p.ticket, 0);
           }
           w = stride + __shfl_sync(0xffffffffu, t, 0);
+          terminal = w >= p.items;
         } else {
           w += stride;
         }
@@ -265,6 +267,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
       ++ni;
     }
     if (!ok) bwd_give_up(sm, p.status, 1);
+    if (!terminal && lane == 0) {
+      // gave up before the last draw: draw on (without working) until this CTA's first ticket past
+      // the end, so that the launch still draws `items` tickets and the counter returns to zero
+      int t;
+      do {
+        t = atomicAdd(p.ticket, 1);
+        if (t == p.items - 1) atomicExch(p.ticket, 0);
+      } while (stride + t < p.items);
+    }
   } else if (warp == 9) {
     // =========================== S / dP issuer ===========================
     constexpr uint32_t idesc_x128 = umma_idesc(kBf16, 0, 0, 128, 128);

@@ -2,83 +2,84 @@
 //
 // Persistent kernel: one CTA per SM.  A work item is ONE query block (64 rows) of one (batch, head)
 // with its list of key blocks; CTA c starts with item c and then draws further items from an
-// optional work counter (or walks a fixed stride).  The list is taken two key tiles at a time
-// ("supersteps").  The 64 query rows are loaded twice, as rows 0..63 and 64..127 of the tcgen05 A
-// operand, so that the 128 TMEM lanes split the two key tiles of a superstep between them: lanes
-// 0..63 own tile a, lanes 64..127 own tile b.  Every SM sub-partition (32 lanes) therefore always
-// has the same amount of exp2 work, whatever the sparsity pattern — the exponentials, not the
-// tensor pipe, bound this kernel at head dimension 64.
+// optional work counter (or walks a fixed stride).  The list is taken FOUR key tiles at a time
+// ("supersteps": tiles a, b, c, d in list order).  The 128 TMEM lanes are split between the
+// tiles: lanes 0..63 own tiles a and c, lanes 64..127 own tiles b and d, so that every SM
+// sub-partition (32 lanes) has the same amount of exp2 work whatever the sparsity pattern, and a
+// softmax warp works through 128 logits per row between two barrier round trips.
+//
+// The query block sits in shared memory once, between blocks of zero rows: [Z; Q; Z].  The
+// 128-row A operand [Q; Z] (Q in rows 0..63) multiplied with [K_a; K_c]^T fills lanes 0..63 of an
+// S slot with the logits of tiles a (columns 0..63) and c (columns 64..127) and lanes 64..127 with
+// zeros; the operand [Z; Q] with [K_b; K_d]^T then adds the logits of tiles b and d to lanes
+// 64..127 (and zeros to the others): eight M=128, N=128, K=16 MMAs per superstep, none of whose
+// 128 x 128 outputs is thrown away.
 //
 // Roles (15 warps); every role walks the same item sequence, so set-up of item i+1 and write-out
 // of item i-1 overlap the arithmetic of item i:
 //   warp 8      : producer — draws the item, lists its key blocks (from the mask row, or copies the
-//                 CSR row), TMA-loads Q (twice) and only the listed K/V tiles: K into a 3-deep ring
-//                 of superstages (held until S is complete), V into a 6-deep one (held until P V is)
-//   warp 9      : S issuer and TMEM owner — S = [Q;Q] [K_a;K_b]^T as four M=128,N=128,K=16 MMAs
-//                 into the S slot of the softmax team whose superstep it is (lanes 0..63 use columns
-//                 0..63, lanes 64..127 columns 64..127; an N=128 instruction occupies the tensor
-//                 pipe no longer than an N=64 one)
-//   warp 10     : P V issuer — O[T] += P_a V_a + P_b V_b for the team T of the superstep, P read from
-//                 the team's P buffer in TMEM, V an MN-major shared-memory operand.  Lanes 64..127
-//                 hold zeros where tile a's P lives and lanes 0..63 where tile b's does, so row r of
-//                 an accumulator only sums tile-a products and row r+64 only tile-b products.  The
-//                 first P V of an item waits until the previous item is written out; the softmax
-//                 warps meanwhile work ahead.
+//                 CSR row), TMA-loads Q and only the listed K/V tiles: K into a 2-deep ring of
+//                 superstages (4 tiles, held until S is complete; loaded one superstep ahead of
+//                 V), V into a 3-deep one (held until P V is complete)
+//   warp 9      : S issuer and TMEM owner
+//   warp 10     : P V issuer — O[T] += P_t V_t for the tiles t of the superstep, T the softmax team
+//                 of the superstep.  P is read from TMEM, V is an MN-major shared-memory operand.
+//                 The lanes that do not own tile t hold zeros in t's P columns, so row r of an
+//                 accumulator only sums products of tiles a, c and row r+64 only of tiles b, d.
 //   warps 0..7  : online softmax in two teams of four warps (team = warp / 4, TMEM lane quarter =
-//                 warp % 4).  The supersteps of an item alternate between the teams; each team has
-//                 its own S slot, P buffer, accumulator, and (m, l) per lane, so while one team does
-//                 its exponentials the other waits, loads or stores.  A warp loads its 64 S columns
-//                 (which frees the slot for the team's next S at once), takes the row maximum, exp2,
-//                 stores P as 16-bit (in two halves, to keep the warp within 128 registers: with
-//                 nothing else on its sub-partition to hide a spill behind, a spilling softmax
-//                 loop ran its arithmetic 2.5x slower), and rescales its own accumulator rows when
-//                 the maximum moved.
-//   warps 11..14: write-out — merge the four partial results (m, l, O) of every query row (teams
-//                 0/1 x lanes r / r+64), normalise, store O, LSE and the row maximum.
-// TMEM (512 columns): S slots 2 x 128, accumulators 2 x 64, P buffers 2 x 64.
+//                 warp % 4).  Supersteps alternate between the teams; each team has its own
+//                 accumulator and (m, l) per lane.  Three S slots (128 TMEM columns) rotate over
+//                 the supersteps; a slot is held from the S MMAs until the P V MMAs that read the
+//                 probabilities, which overwrite the logits in place, are complete.  A warp takes
+//                 the maximum of its lanes' logits (64 columns at a time), moves the lane's
+//                 reference maximum if need be (rescaling its accumulator rows), then exponentiates:
+//                 first the tile still in registers from the maximum pass, then the other one,
+//                 loaded a second time.  Lanes 0..63 put P_c, P_a into columns 64..127 and zeros
+//                 into 0..63; lanes 64..127 put P_b, P_d into columns 0..63 and zeros into 64..127.
+//   warps 11..14: write-out — merge the four partial results (m, l, O) of every query row (teams x
+//                 lanes r / r+64), normalise, store O, LSE and the row maximum.
+// TMEM (512 columns): S/P slots 3 x 128, accumulators 2 x 64.
 //
 // Numerics follow the reference's loop (fa2_custom_mask/fa2_fwd.py:150-196): logits scaled by
 // sm_scale*log2(e), exp2 domain, fp32 row sums of the fp32 probabilities, P rounded to the input
 // dtype before P V.  The running maximum is only advanced when it grew by more than 8 (a factor
-// 256), which leaves O = acc / l unchanged because both use the same reference maximum.  Which
-// team takes which superstep depends on the item alone, so results do not depend on which CTA
-// computes an item.
+// 256), which leaves O = acc / l unchanged because both use the same reference maximum.  The
+// partial results are merged in the order (even supersteps, odd supersteps) of the item, whichever
+// team computed them, so results do not depend on which CTA computes an item.
 //
 // Every wait is bounded; a wait that gives up raises a CTA-wide flag, every role then falls
 // through its loops without touching barriers' data again, and TMEM is always released.  Every
-// barrier is waited on only by warps that see each of its phases (a parity wait cannot tell a
-// phase from the one two before it).
+// barrier is waited on only by warps that see each of its phases, or that know the barrier to be
+// at most one phase behind (a parity wait cannot tell a phase from the one two before it): the
+// barriers of the S slots come in sets of six, the least common multiple of slots and teams.
 #include <math.h>
+#include <string.h>
 
 #include "host_common.h"
 #include "sm100_ptx.cuh"
 
 namespace bsa {
 
-constexpr int kKStages = 3;     // K superstages (2 tiles) in flight: held from load to S complete
-constexpr int kVStages = 6;     // V superstages (2 tiles) in flight: held from load to P V complete
-                                // (with 5 the producer, which loads K and V of a superstep in
-                                // turn, often waited for a V stage and so held the next K back)
-constexpr int kSSlots = 2;      // S supertiles (128 TMEM columns), one per softmax team: held from
-                                // S issue to tcgen05.ld
+constexpr int kKStages = 2;     // K superstages (4 tiles) in flight: held from load to S complete
+constexpr int kVStages = 3;     // V superstages (4 tiles) in flight: held from load to P V complete
+constexpr int kSlots = 3;       // S/P slots (128 TMEM columns): held from S issue to P V complete
+constexpr int kSets = 6;        // barrier sets of the slots: lcm(kSlots, 2 teams)
 constexpr int kFwdThreads = 480;
 constexpr int kSoftmaxWarps = 8, kProducerWarp = 8, kSWarp = 9, kPvWarp = 10;  // warps 11..14 write out
 constexpr uint32_t kTileBytes = 64 * 64 * 2;       // one Q, K or V tile
 constexpr uint32_t kFwdTmemCols = 512;
-// TMEM columns: S slot r at 128 r; accumulator of softmax team T at 256 + 64 T; P of team T at
-// 384 + 64 T (tile a's 64 keys as 32 columns of 16-bit pairs, then tile b's)
-constexpr uint32_t kTmemO = 256;
-constexpr uint32_t kTmemP = 384;
+// TMEM columns: slot r at 128 r; accumulator of softmax team T at 384 + 64 T.
+constexpr uint32_t kTmemO = 384;
 constexpr float kRescaleThreshold = 8.0f;
 constexpr int kFwdMaxTiles = 2048;  // key blocks per row that a CTA can list (N <= 131072)
 constexpr int kMaxSorted = 320;     // items beyond the first round that a CTA can put in order
 
 struct FwdSmem {
-  uint8_t q[2][2][kTileBytes];                // by item parity: the query block, twice
-  uint8_t k[kKStages][2][kTileBytes];
-  uint8_t v[kVStages][2][kTileBytes];
-  float xfer[64][65];                         // write-out: lanes 64..127 hand over, [col][row]
-  int32_t cols[2][kFwdMaxTiles];              // by item parity: the item's key-block list
+  uint8_t qz[5][kTileBytes];                  // Z, Q (even items), Z, Q (odd items), Z
+  uint8_t k[kKStages][4][kTileBytes];         // tiles in the order a, c, b, d
+  uint8_t v[kVStages][4][kTileBytes];         // tiles in the order a, b, c, d
+  float xfer[32][65];                         // write-out: lanes 64..127 hand over, [col][row]
+  uint16_t cols[2][kFwdMaxTiles];             // by item parity: the item's key-block list
   alignas(16) int cnt[kMaxSorted];            // sort keys (tile count, item) of the items beyond the first round
   int order[kMaxSorted];                      // those items, longest first
   int ntiles[2];
@@ -93,16 +94,16 @@ struct FwdSmem {
   uint64_t k_empty[kKStages];                 // S of the superstep complete
   uint64_t v_full[kVStages];
   uint64_t v_empty[kVStages];                 // P V of the superstep complete
-  uint64_t s_full[kSSlots];
-  uint64_t s_free[kSSlots];                   // the four warps of the team have S in registers
-  uint64_t p_full[2];                         // by team: P of its current superstep stored
-  uint64_t p_free[2];                         // by team: P V of its latest superstep complete
+  uint64_t s_full[kSets];                     // S of the superstep complete
+  uint64_t p_full[kSets];                     // the team's four warps stored P of the superstep
+  uint64_t pv_done[kSets];                    // P V of the superstep complete: slot free, O current
   uint64_t o_full[2];                         // last P V of the item done
   uint64_t stats_full[2];                     // softmax warps published (m, l) of the item
   uint64_t o_free[2];                         // write-out holds accumulators/stats/header in registers
   uint32_t tmem_base;
   int abort_flag;
 };
+static_assert(sizeof(FwdSmem) + 1024 <= 232448, "FwdSmem exceeds the shared memory of one CTA");
 
 struct FwdParams {
   const int32_t* row_ptr;   // list mode: CSR row lists
@@ -114,8 +115,9 @@ struct FwdParams {
   float* lse2;
   float* rowmax;
   int B, H, N, nb;
+  int row_begin, nrows;     // the query-block rows [row_begin, row_begin + nrows) of every head
   int list_b_stride, list_h_stride;
-  int items;                // B * H * nb
+  int items;                // B * H * nrows
   float scale_log2;
   int32_t* status;
   int32_t* ticket;          // optional work counter (0 at kernel start, left 0): dynamic item hand-out
@@ -125,7 +127,7 @@ enum FwdFail : int { kFailProducer = 1, kFailMma = 2, kFailSoftmax = 3, kFailOut
 
 __device__ __forceinline__ void fwd_give_up(FwdSmem* sm, int32_t* status, int code) {
   sm->abort_flag = 1;
-  if (status) atomicCAS(status, 0, code);
+  report_status(status, code);
 }
 
 // exp2 of one 32-column chunk of S against the row's reference maximum; returns the packed
@@ -154,6 +156,17 @@ __device__ __forceinline__ void exp_chunk(const uint32_t* sr, float c, float neg
   l += a0 + a1;
 }
 
+// exp2 of the 64 logits of one tile held in sr; the probabilities go to 32 TMEM columns at p_addr.
+template <bool kBf16>
+__device__ __forceinline__ void exp_tile(const uint32_t* sr, float c, float neg_m, uint32_t p_addr,
+                                         float& l) {
+  uint32_t pk[16];
+  exp_chunk<kBf16>(sr, c, neg_m, pk, l);
+  tmem_st_32x32b_x16(p_addr, pk);
+  exp_chunk<kBf16>(sr + 32, c, neg_m, pk, l);
+  tmem_st_32x32b_x16(p_addr + 16, pk);
+}
+
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));  // one instruction on sm_100
@@ -175,9 +188,9 @@ struct FwdItem {
   int b, h, mb;
 };
 __device__ __forceinline__ FwdItem fwd_item(int w, const FwdParams& p) {
-  const int bh = w / p.nb;
+  const int bh = w / p.nrows;
   FwdItem it;
-  it.mb = p.nb - 1 - (w - bh * p.nb);
+  it.mb = p.row_begin + p.nrows - 1 - (w - bh * p.nrows);
   it.b = bh / p.H;
   it.h = bh - it.b * p.H;
   return it;
@@ -279,7 +292,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
   // ---- set-up ----
   if (threadIdx.x == 0) {
-    BSA_TR_CTA(0, global_timer_ns());
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&sm->list_full[i]), 1);
       mbar_init(smem_u32(&sm->q_full[i]), 1);
@@ -296,15 +308,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_init(smem_u32(&sm->v_full[s]), 1);
       mbar_init(smem_u32(&sm->v_empty[s]), 1);
     }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(smem_u32(&sm->s_full[i]), 1);
-      mbar_init(smem_u32(&sm->s_free[i]), kSoftmaxWarps / 2);  // the four warps of one team
-      mbar_init(smem_u32(&sm->p_full[i]), kSoftmaxWarps / 2);
-      mbar_init(smem_u32(&sm->p_free[i]), 1);
+    for (int s = 0; s < kSets; ++s) {
+      mbar_init(smem_u32(&sm->s_full[s]), 1);
+      mbar_init(smem_u32(&sm->p_full[s]), kSoftmaxWarps / 2);  // the four warps of one team
+      mbar_init(smem_u32(&sm->pv_done[s]), 1);
     }
     mbar_init(smem_u32(&sm->order_full), 1);
     sm->abort_flag = 0;
     mbar_fence_init();
+  }
+  {
+    // the three blocks of zero rows around the two query buffers; the MMAs read them through the
+    // async proxy
+    const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+    constexpr int kVecs = kTileBytes / 16;
+    for (int i = threadIdx.x; i < 3 * kVecs; i += kFwdThreads)
+      reinterpret_cast<uint4*>(sm->qz[2 * (i / kVecs)])[i % kVecs] = z;
+    fence_proxy_async_smem();
   }
   if (warp == kSWarp) {
     tmem_alloc(smem_u32(&sm->tmem_base), kFwdTmemCols);
@@ -325,6 +345,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     // =========================== producer ===========================
     const bool leader = elect_one();
     bool ok = true;
+    bool terminal = p.ticket == nullptr;  // drew a ticket past the end (or draws none)
     int gs = 0;  // supersteps issued so far by this CTA (ring position)
     int qi = 0;  // non-empty items so far (Q buffer position)
     for (int i = 0, w = blockIdx.x; ok; ++i) {
@@ -340,6 +361,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             if (t == p.items - 1) atomicExch(p.ticket, 0);
           }
           t = __shfl_sync(0xffffffffu, t, 0);
+          terminal = t >= n2;
           if (sorted && t < n2) {
             if (i == 1) ok = mbar_wait_warp(smem_u32(&sm->order_full), 0, abort_flag);
             if (!ok) break;
@@ -362,7 +384,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         break;
       }
       const FwdItem it = fwd_item(w, p);
-      int32_t* cols = sm->cols[par];
+      uint16_t* cols = sm->cols[par];
       int n_tiles = 0;
       if (p.block != nullptr) {
         // mask mode: ordered compaction of the kept blocks of mask row (b, h, mb)
@@ -378,7 +400,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const unsigned bal = __ballot_sync(0xffffffffu, keep[j]);
-            if (keep[j]) cols[n_tiles + __popc(bal & ((1u << lane) - 1u))] = c0 + 32 * j + lane;
+            if (keep[j])
+              cols[n_tiles + __popc(bal & ((1u << lane) - 1u))] =
+                  static_cast<uint16_t>(c0 + 32 * j + lane);
             n_tiles += __popc(bal);
           }
         }
@@ -387,7 +411,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             static_cast<int64_t>(it.b * p.list_b_stride + it.h * p.list_h_stride) * p.nb + it.mb;
         const int beg = __ldg(p.row_ptr + li);
         n_tiles = __ldg(p.row_ptr + li + 1) - beg;
-        for (int j = lane; j < n_tiles; j += 32) cols[j] = __ldg(p.col_idx + beg + j);
+        for (int j = lane; j < n_tiles; j += 32)
+          cols[j] = static_cast<uint16_t>(__ldg(p.col_idx + beg + j));
       }
       __syncwarp();
       if (lane == 0) {
@@ -395,84 +420,108 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         sm->item[par] = w;
         mbar_arrive(smem_u32(&sm->list_full[par]));  // release: count and list are visible
       }
-      const int n_super = (n_tiles + 1) >> 1;
+      const int n_super = (n_tiles + 3) >> 2;
       if (n_super == 0) continue;
       const int qpar = qi & 1;
       if (qi >= 2) ok = mbar_wait_warp(smem_u32(&sm->q_free[qpar]), ((qi - 2) >> 1) & 1, abort_flag);
       if (!ok) break;
       if (leader) {
         const uint32_t bar = smem_u32(&sm->q_full[qpar]);
-        mbar_expect_tx(bar, 2 * kTileBytes);
-        tma_load_4d(smem_u32(sm->q[qpar][0]), &tm_q, bar, 0, it.mb * 64, it.h, it.b);
-        tma_load_4d(smem_u32(sm->q[qpar][1]), &tm_q, bar, 0, it.mb * 64, it.h, it.b);
+        mbar_expect_tx(bar, kTileBytes);
+        tma_load_4d(smem_u32(sm->qz[1 + 2 * qpar]), &tm_q, bar, 0, it.mb * 64, it.h, it.b);
       }
       ++qi;
-      for (int u = 0; u < n_super; ++u, ++gs) {
-        const int ks = gs % kKStages, vs = gs % kVStages;
-        const int nt = min(2, n_tiles - 2 * u);
-        const int n0 = cols[2 * u];
-        const int n1 = nt == 2 ? cols[2 * u + 1] : 0;
-        ok = mbar_wait_warp(smem_u32(&sm->k_empty[ks]), ((gs / kKStages) & 1) ^ 1, abort_flag);
-        if (!ok) break;
-        if (leader) {
-          const uint32_t bar = smem_u32(&sm->k_full[ks]);
-          mbar_expect_tx(bar, kTileBytes * nt);
-          tma_load_4d(smem_u32(sm->k[ks][0]), &tm_k, bar, 0, n0 * 64, it.h, it.b);
-          if (nt == 2) tma_load_4d(smem_u32(sm->k[ks][1]), &tm_k, bar, 0, n1 * 64, it.h, it.b);
+      // K runs one superstep ahead of V: a K stage is free as soon as its S is complete, a V stage
+      // only when the superstep's P V is, and the wait for the latter must not hold back the K
+      // tiles that the next S needs.
+      for (int u = 0; u <= n_super && ok; ++u) {
+        if (u < n_super) {
+          const int g = gs + u, ks = g % kKStages;
+          const int nt = min(4, n_tiles - 4 * u);
+          ok = mbar_wait_warp(smem_u32(&sm->k_empty[ks]), ((g / kKStages) & 1) ^ 1, abort_flag);
+          if (!ok) break;
+          if (leader) {
+            const uint32_t bar = smem_u32(&sm->k_full[ks]);
+            mbar_expect_tx(bar, kTileBytes * nt);
+            for (int t = 0; t < nt; ++t)  // shared-memory order a, c, b, d
+              tma_load_4d(smem_u32(sm->k[ks][((t & 1) << 1) | (t >> 1)]), &tm_k, bar, 0,
+                          static_cast<int>(cols[4 * u + t]) * 64, it.h, it.b);
+          }
         }
-        ok = mbar_wait_warp(smem_u32(&sm->v_empty[vs]), ((gs / kVStages) & 1) ^ 1, abort_flag);
-        if (!ok) break;
-        if (leader) {
-          const uint32_t bar = smem_u32(&sm->v_full[vs]);
-          mbar_expect_tx(bar, kTileBytes * nt);
-          tma_load_4d(smem_u32(sm->v[vs][0]), &tm_v, bar, 0, n0 * 64, it.h, it.b);
-          if (nt == 2) tma_load_4d(smem_u32(sm->v[vs][1]), &tm_v, bar, 0, n1 * 64, it.h, it.b);
+        if (u > 0) {
+          const int g = gs + u - 1, vs = g % kVStages;
+          const int nt = min(4, n_tiles - 4 * (u - 1));
+          ok = mbar_wait_warp(smem_u32(&sm->v_empty[vs]), ((g / kVStages) & 1) ^ 1, abort_flag);
+          if (!ok) break;
+          if (leader) {
+            const uint32_t bar = smem_u32(&sm->v_full[vs]);
+            mbar_expect_tx(bar, kTileBytes * nt);
+            for (int t = 0; t < nt; ++t)
+              tma_load_4d(smem_u32(sm->v[vs][t]), &tm_v, bar, 0,
+                          static_cast<int>(cols[4 * (u - 1) + t]) * 64, it.h, it.b);
+          }
         }
       }
+      gs += n_super;
     }
     if (!ok) fwd_give_up(sm, p.status, kFailProducer);
+    if (!terminal && lane == 0) {
+      // gave up before the last draw: draw on (without working) until this CTA's first ticket past
+      // the end, so that the launch still draws `items` tickets and the counter returns to zero
+      int t;
+      do {
+        t = atomicAdd(p.ticket, 1);
+        if (t == p.items - 1) atomicExch(p.ticket, 0);
+      } while (t < n2);
+    }
   } else if (warp == kSWarp) {
     // =========================== S issuer ===========================
-    constexpr uint32_t idesc_s128 = umma_idesc(kBf16, 0, 0, 128, 128);  // [Q;Q] x [K_a;K_b]
-    constexpr uint32_t idesc_s64 = umma_idesc(kBf16, 0, 0, 128, 64);    // odd tail: one tile
+    constexpr uint32_t idesc_n128 = umma_idesc(kBf16, 0, 0, 128, 128);
+    constexpr uint32_t idesc_n64 = umma_idesc(kBf16, 0, 0, 128, 64);
     const bool leader = elect_one();
-    const uint64_t desc_q0 = smem_desc_sw128(smem_u32(sm->q[0][0]), 16, 1024);
+    const uint64_t desc_qz = smem_desc_sw128(smem_u32(sm->qz[0]), 16, 1024);
     const uint64_t desc_k0 = smem_desc_sw128(smem_u32(sm->k[0][0]), 16, 1024);
+    constexpr uint64_t kTileDesc = kTileBytes >> 4;  // one tile further, in descriptor units
     bool ok = true;
     int gs = 0, qi = 0;
-    int kt0 = 0, kt1 = 0;  // supersteps issued for each softmax team so far
     for (int i = 0; ok; ++i) {
       const int par = i & 1;
       ok = mbar_wait_warp(smem_u32(&sm->list_full[par]), (i >> 1) & 1, abort_flag);
       if (!ok) break;
       if (*const_cast<volatile int*>(&sm->item[par]) < 0) break;  // no more work
       const int n_tiles = *const_cast<volatile int*>(&sm->ntiles[par]);
-      const int n_super = (n_tiles + 1) >> 1;
+      const int n_super = (n_tiles + 3) >> 2;
       if (n_super == 0) continue;
       const int qpar = qi & 1;
       ok = mbar_wait_warp(smem_u32(&sm->q_full[qpar]), (qi >> 1) & 1, abort_flag);
       if (!ok) break;
-      const uint64_t desc_q = desc_q0 + static_cast<uint64_t>(qpar * ((2 * kTileBytes) >> 4));
+      // [Z; Q] starts at the zero block in front of the query buffer, [Q; Z] at the buffer itself
+      const uint64_t desc_bot = desc_qz + static_cast<uint64_t>(2 * qpar) * kTileDesc;
+      const uint64_t desc_top = desc_bot + kTileDesc;
       for (int u = 0; u < n_super; ++u, ++gs) {
-        const int ks = gs % kKStages;
-        const int slot = u & 1;  // the S slot of the softmax team whose superstep this is
-        const int nt = min(2, n_tiles - 2 * u);
+        const int ks = gs % kKStages, slot = gs % kSlots, set = gs % kSets;
+        const int nt = min(4, n_tiles - 4 * u);
         ok = mbar_wait_warp(smem_u32(&sm->k_full[ks]), (gs / kKStages) & 1, abort_flag);
         if (!ok) break;
-        // the team's previous S must be in its registers; on the slot's first use this asks for
-        // the phase before the first one, which counts as complete
-        const int kts = slot ? kt1 : kt0;
-        ok = mbar_wait_warp(smem_u32(&sm->s_free[slot]), (kts & 1) ^ 1, abort_flag);
+        // the slot's previous user, three supersteps ago, must have had its P V completed
+        if (gs >= kSlots)
+          ok = mbar_wait_warp(smem_u32(&sm->pv_done[(gs - kSlots) % kSets]),
+                              ((gs - kSlots) / kSets) & 1, abort_flag);
         if (!ok) break;
-        if (slot) ++kt1; else ++kt0;
         tc_fence_after();
         if (leader) {
-          const uint64_t desc_k = desc_k0 + static_cast<uint64_t>(ks * ((2 * kTileBytes) >> 4));
-          const uint32_t idesc = nt == 2 ? idesc_s128 : idesc_s64;
+          const uint32_t d = tmem + 128 * slot;
+          const uint64_t desc_ac = desc_k0 + static_cast<uint64_t>(ks * 4) * kTileDesc;
+          const uint64_t desc_bd = desc_ac + 2 * kTileDesc;
+          const uint32_t id_ac = nt >= 3 ? idesc_n128 : idesc_n64;
+          const uint32_t id_bd = nt >= 4 ? idesc_n128 : idesc_n64;
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk)
-            umma_ss(tmem + 128 * slot, desc_q + 2 * kk, desc_k + 2 * kk, idesc, kk > 0);
-          tc_commit(smem_u32(&sm->s_full[slot]));
+          for (int kk = 0; kk < 4; ++kk) umma_ss(d, desc_top + 2 * kk, desc_ac + 2 * kk, id_ac, kk > 0);
+          if (nt >= 2) {
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) umma_ss(d, desc_bot + 2 * kk, desc_bd + 2 * kk, id_bd, 1);
+          }
+          tc_commit(smem_u32(&sm->s_full[set]));
           tc_commit(smem_u32(&sm->k_empty[ks]));
           if (u == n_super - 1) tc_commit(smem_u32(&sm->q_free[qpar]));  // Q buffer reusable
         }
@@ -487,14 +536,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const uint64_t desc_v0 = smem_desc_sw128(smem_u32(sm->v[0][0]), 8192, 1024);
     bool ok = true;
     int gs = 0;
-    int kt[2] = {0, 0};  // supersteps taken by each softmax team so far
     for (int i = 0; ok; ++i) {
       const int par = i & 1;
       ok = mbar_wait_warp(smem_u32(&sm->list_full[par]), (i >> 1) & 1, abort_flag);
       if (!ok) break;
       if (*const_cast<volatile int*>(&sm->item[par]) < 0) break;  // no more work
       const int n_tiles = *const_cast<volatile int*>(&sm->ntiles[par]);
-      const int n_super = (n_tiles + 1) >> 1;
+      const int n_super = (n_tiles + 3) >> 2;
       // the accumulators are free once the previous item has been written out; the softmax warps
       // meanwhile work ahead
       if (i >= 1)
@@ -505,34 +553,32 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         continue;
       }
       for (int u = 0; u < n_super; ++u, ++gs) {
-        const int vs = gs % kVStages;
-        const int team = u & 1;
-        const int nt = min(2, n_tiles - 2 * u);
+        const int vs = gs % kVStages, slot = gs % kSlots, set = gs % kSets;
+        const int team = gs & 1;
+        const int nt = min(4, n_tiles - 4 * u);
         ok = mbar_wait_warp(smem_u32(&sm->v_full[vs]), (gs / kVStages) & 1, abort_flag);
         if (!ok) break;
-        ok = mbar_wait_warp(smem_u32(&sm->p_full[team]), kt[team] & 1, abort_flag);
+        ok = mbar_wait_warp(smem_u32(&sm->p_full[set]), (gs / kSets) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
         if (leader) {
-          // The supersteps of an item alternate between the two softmax teams (by u, so that the
-          // grouping of the sums does not depend on which CTA computes the item); each team has
-          // its own P buffer and accumulator, and its first superstep of an item (u = 0 or 1)
-          // starts the accumulator afresh.  Keys [16 kk, +16) of tile t sit at column 32 t + 8 kk
-          // of the P buffer; the other half of the lanes holds zeros there.
+          // A team's first superstep of an item (u = 0 or 1) starts its accumulator afresh.  Keys
+          // [16 kk, +16) of tile t sit 8 kk columns into the tile's P columns: a at 96, b at 0, c at
+          // 64, d at 32; the lanes that do not own the tile hold zeros there.
           const uint32_t o_acc = tmem + kTmemO + 64 * team;
-          const uint32_t p_buf = tmem + kTmemP + 64 * team;
+          const uint32_t p_slot = tmem + 128 * slot;
           for (int t = 0; t < nt; ++t) {
-            const uint64_t desc_v = desc_v0 + static_cast<uint64_t>((vs * 2 + t) * (kTileBytes >> 4));
+            const uint32_t p_cols = p_slot + ((t & 1) ? 0u : 64u) + ((t >> 1) == (t & 1) ? 32u : 0u);
+            const uint64_t desc_v = desc_v0 + static_cast<uint64_t>((vs * 4 + t) * (kTileBytes >> 4));
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk)
-              umma_ts(o_acc, p_buf + 32 * t + 8 * kk, desc_v + 128 * kk, idesc_pv,
+              umma_ts(o_acc, p_cols + 8 * kk, desc_v + 128 * kk, idesc_pv,
                       (u > 1) || (t > 0) || (kk > 0));
           }
           tc_commit(smem_u32(&sm->v_empty[vs]));
-          tc_commit(smem_u32(&sm->p_free[team]));
+          tc_commit(smem_u32(&sm->pv_done[set]));
           if (u == n_super - 1) tc_commit(smem_u32(&sm->o_full[par]));
         }
-        ++kt[team];
       }
     }
     if (!ok) fwd_give_up(sm, p.status, kFailMma);
@@ -540,60 +586,53 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     // =========================== softmax ===========================
     const int team = warp >> 2;       // supersteps alternate between the two teams of four warps
     const int quarter = warp & 3;     // TMEM lane quarter this warp may touch
-    const int t_mine = quarter >> 1;  // lanes 0..63 own tile a of a superstep, 64..127 tile b
+    const int half = quarter >> 1;    // lanes 0..63 own tiles a, c of a superstep, 64..127 b, d
     const int lane_row = quarter * 32 + lane;  // TMEM lane
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
     const uint32_t o_addr = tmem + lane_base + kTmemO + 64 * team;
-    const uint32_t p_addr = tmem + lane_base + kTmemP + 64 * team + 32 * t_mine;
+    // Columns of a slot.  "Kept" tile: the one whose logits stay in registers after the maximum
+    // pass (c for lanes 0..63, b for lanes 64..127); its columns also take this half's P.  The
+    // other tile (a or d) is loaded a second time for its exponentials; its columns take zeros.
+    const uint32_t col_keep = half ? 0u : 64u;
+    const uint32_t col_re = col_keep ^ 64u;
     const float c = p.scale_log2;
-    {
-      // P V of a tile sweeps all 128 lanes: the half of the lanes that does not own the tile holds
-      // zeros where that tile's P lives.  Nothing else ever writes there, so once is enough.
-      uint32_t z[32];
-#pragma unroll
-      for (int j = 0; j < 32; ++j) z[j] = 0u;
-      tmem_st_32x32b_x32(tmem + lane_base + kTmemP + 64 * team + 32 * (1 - t_mine), z);
-      tc_wait_st();
-    }
     bool ok = true;
-    int kt = 0;  // supersteps this team has taken so far (P buffer phase)
+    int g0 = 0;  // supersteps of all earlier items of this CTA
     for (int i = 0; ok; ++i) {
       const int par = i & 1;
       ok = mbar_wait_warp(smem_u32(&sm->list_full[par]), (i >> 1) & 1, abort_flag);
       if (!ok) break;
       if (*const_cast<volatile int*>(&sm->item[par]) < 0) break;  // no more work
       const int n_tiles = *const_cast<volatile int*>(&sm->ntiles[par]);
-      const int n_super = (n_tiles + 1) >> 1;
+      const int n_super = (n_tiles + 3) >> 2;
       float m_ref = -INFINITY, m_true = -INFINITY, l = 0.f;
-      // Every barrier a warp waits on is one whose every phase it sees (a parity wait cannot tell a
-      // phase from the one two before it): the S slot is the team's own, phase = the team's count.
-      const uint32_t sfull_bar = smem_u32(&sm->s_full[team]);
-      const uint32_t s_addr = tmem + lane_base + 128 * team + 64 * t_mine;  // columns [64 t, +64)
 
-      for (int u = team; u < n_super; u += 2) {
-        const int nt = min(2, n_tiles - 2 * u);
-        ok = mbar_wait_warp(sfull_bar, kt & 1, abort_flag);
+      for (int u = team ^ (g0 & 1); u < n_super; u += 2) {
+        const int g = g0 + u;
+        const int set = g % kSets;
+        const uint32_t s_addr = tmem + lane_base + 128 * (g % kSlots);
+        const int nt = min(4, n_tiles - 4 * u);
+        const bool keep = half ? nt >= 2 : nt >= 3;
+        const bool re = half ? nt >= 4 : nt >= 1;
+        ok = mbar_wait_warp(smem_u32(&sm->s_full[set]), (g / kSets) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
-        uint32_t sr[64];
-        if (t_mine < nt) {
-          tmem_ld_32x32b_x32(s_addr, sr);
-          tmem_ld_32x32b_x32(s_addr + 32, sr + 32);
-        }
-        tc_wait_ld();
-        // S is in registers: the slot may take the team's next S
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&sm->s_free[team]));
-        // The team's previous P V must be complete before its P buffer is overwritten (and before
-        // a rescale touches the accumulator).  It normally completed long ago: test now, so that
-        // the round trip to the barrier overlaps the arithmetic, and wait only if need be.
-        const uint32_t pfree_bar = smem_u32(&sm->p_free[team]);
-        const uint32_t pfree_par = (kt & 1) ^ 1;  // phase kt-1; passes at once for kt = 0
-        bool pfree = mbar_try_wait(pfree_bar, pfree_par);
-        uint32_t pk[16];
-        if (t_mine < nt) {
-          const float zmax = fmaxf(max_chunk(sr), max_chunk(sr + 32)) * c;
+        if (keep || re) {
+          uint32_t sr[64];
+          float mx = -INFINITY;
+          if (re) {
+            tmem_ld_32x32b_x32(s_addr + col_re, sr);
+            tmem_ld_32x32b_x32(s_addr + col_re + 32, sr + 32);
+            tc_wait_ld();
+            mx = fmaxf(max_chunk(sr), max_chunk(sr + 32));
+          }
+          if (keep) {
+            tmem_ld_32x32b_x32(s_addr + col_keep, sr);
+            tmem_ld_32x32b_x32(s_addr + col_keep + 32, sr + 32);
+            tc_wait_ld();
+            mx = max3(mx, max_chunk(sr), max_chunk(sr + 32));
+          }
+          const float zmax = mx * c;
           m_true = fmaxf(m_true, zmax);
           float alpha = 1.f;
           bool rescale = false;
@@ -606,12 +645,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             rescale = true;
           }
           if (__any_sync(0xffffffffu, rescale)) {
-            // this warp's O rows must hold the team's previous product first
-            if (!__all_sync(0xffffffffu, pfree)) {
-              ok = mbar_wait_warp(pfree_bar, pfree_par, abort_flag);
-              if (!ok) break;
-              pfree = true;
-            }
+            // this warp's O rows must hold the team's previous product (two supersteps ago) first
+            ok = mbar_wait_warp(smem_u32(&sm->pv_done[(g - 2) % kSets]), ((g - 2) / kSets) & 1,
+                                abort_flag);
+            if (!ok) break;
             tc_fence_after();
 #pragma unroll 1
             for (int part = 0; part < 4; ++part) {
@@ -624,23 +661,26 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
               tmem_st_32x32b_x16(o_addr + 16 * part, orow);
             }
           }
-          exp_chunk<kBf16>(sr, c, -m_ref, pk, l);
+          const float neg_m = -m_ref;
+          if (keep) {
+            exp_tile<kBf16>(sr, c, neg_m, s_addr + col_keep, l);
+            if (re) {
+              tmem_ld_32x32b_x32(s_addr + col_re, sr);
+              tmem_ld_32x32b_x32(s_addr + col_re + 32, sr + 32);
+              tc_wait_ld();
+              exp_tile<kBf16>(sr, c, neg_m, s_addr + col_keep + 32, l);
+            }
+          } else {
+            exp_tile<kBf16>(sr, c, neg_m, s_addr + col_keep + 32, l);
+          }
         }
-        if (!__all_sync(0xffffffffu, pfree)) {
-          ok = mbar_wait_warp(pfree_bar, pfree_par, abort_flag);
-          if (!ok) break;
-        }
-        if (t_mine < nt) {
-          tc_fence_after();
-          tmem_st_32x32b_x16(p_addr, pk);
-          exp_chunk<kBf16>(sr + 32, c, -m_ref, pk, l);
-          tmem_st_32x32b_x16(p_addr + 16, pk);
-        }
+        // the other half's P columns: zeros in these lanes (the logits there are used up)
+        tmem_st_zero_32x32b_x32(s_addr + col_re);
+        tmem_st_zero_32x32b_x32(s_addr + col_re + 32);
         tc_wait_st();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&sm->p_full[team]));
-        ++kt;
+        if (lane == 0) mbar_arrive(smem_u32(&sm->p_full[set]));
       }
       if (!ok) break;
 
@@ -652,22 +692,24 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       sm->mtrue[par][team][lane_row] = m_true;
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&sm->stats_full[par]));
+      g0 += n_super;
     }
     if (!ok) fwd_give_up(sm, p.status, kFailSoftmax);
   } else {
     // =========================== write-out ===========================
-    // Merges the four partial results of every query row (key groups 0/1 x lanes r / r+64).  A warp
-    // reads both accumulators of its own lanes from TMEM; lanes 64..127 hand their weighted rows
-    // to lanes 0..63 through shared memory.  Both named barriers of an iteration are always
-    // executed, also after a give-up, and the second one carries the give-up vote, so that no warp
-    // of this role can be left waiting at one.
+    // Merges the four partial results of every query row (even / odd supersteps x lanes r / r+64).
+    // A warp reads both accumulators of its own lanes from TMEM; lanes 64..127 hand their weighted
+    // rows to lanes 0..63 through shared memory, 32 columns at a time.  All named barriers of an
+    // iteration are always executed, also after a give-up, and the last one carries the give-up
+    // vote, so that no warp of this role can be left waiting at one.
     const int quarter = warp & 3;  // lane quarter a warp may touch = its index mod 4
     if (sorted) fwd_build_order(sm, p, quarter * 32 + lane, stride, n2);
-    const int t_mine = quarter >> 1;
+    const int half = quarter >> 1;
     const int lane_row = quarter * 32 + lane;
     const int r_blk = (quarter & 1) * 32 + lane;  // row of the query block
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
     bool ok = true;
+    int g0 = 0;
     for (int i = 0;; ++i) {
       const int par = i & 1;
       ok = mbar_wait_warp_idle(smem_u32(&sm->list_full[par]), (i >> 1) & 1, abort_flag, 256);
@@ -675,6 +717,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (w < 0) break;  // no more work: the same for all four warps
       const FwdItem it = fwd_item(w, p);
       const int n_tiles = ok ? *const_cast<volatile int*>(&sm->ntiles[par]) : 0;
+      const int n_super = (n_tiles + 3) >> 2;
+      // the team that took the item's even supersteps comes first in every sum
+      const int t_even = g0 & 1, t_odd = t_even ^ 1;
+      g0 += n_super;
       if (ok) ok = mbar_wait_warp_idle(smem_u32(&sm->stats_full[par]), (i >> 1) & 1, abort_flag, 256);
       if (ok) ok = mbar_wait_warp(smem_u32(&sm->o_full[par]), (i >> 1) & 1, abort_flag);
       float acc[64];
@@ -682,33 +728,35 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (ok) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          m_all = fmaxf(m_all, sm->mref[par][j & 1][r_blk + 64 * (j >> 1)]);
-          mt = fmaxf(mt, sm->mtrue[par][j & 1][r_blk + 64 * (j >> 1)]);
+          const int tm = (j & 1) ? t_odd : t_even;
+          m_all = fmaxf(m_all, sm->mref[par][tm][r_blk + 64 * (j >> 1)]);
+          mt = fmaxf(mt, sm->mtrue[par][tm][r_blk + 64 * (j >> 1)]);
         }
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const float mi = sm->mref[par][j & 1][r_blk + 64 * (j >> 1)];
+          const int tm = (j & 1) ? t_odd : t_even;
+          const float mi = sm->mref[par][tm][r_blk + 64 * (j >> 1)];
           if (mi != -INFINITY)
-            l_all += ex2_approx(mi - m_all) * sm->lsum[par][j & 1][r_blk + 64 * (j >> 1)];
+            l_all += ex2_approx(mi - m_all) * sm->lsum[par][tm][r_blk + 64 * (j >> 1)];
         }
         const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
-        const float m0 = sm->mref[par][0][lane_row], m1 = sm->mref[par][1][lane_row];
+        const float m0 = sm->mref[par][t_even][lane_row], m1 = sm->mref[par][t_odd][lane_row];
         const float w0 = m0 == -INFINITY ? 0.f : ex2_approx(m0 - m_all) * inv;
         const float w1 = m1 == -INFINITY ? 0.f : ex2_approx(m1 - m_all) * inv;
         if (n_tiles > 0) {  // warp-uniform
           // a team's accumulator holds this item's sums only if the team had a superstep in it
-          const bool live1 = n_tiles > 2;  // team 1 takes the odd supersteps
+          const bool live1 = n_super > 1;
           tc_fence_after();
 #pragma unroll
-          for (int part = 0; part < 2; ++part) {
-            uint32_t a0[32], a1[32];
-            tmem_ld_32x32b_x32(tmem + lane_base + kTmemO + 32 * part, a0);
-            tmem_ld_32x32b_x32(tmem + lane_base + kTmemO + 64 + 32 * part, a1);
+          for (int part = 0; part < 4; ++part) {
+            uint32_t a0[16], a1[16];
+            tmem_ld_32x32b_x16(tmem + lane_base + kTmemO + 64 * t_even + 16 * part, a0);
+            tmem_ld_32x32b_x16(tmem + lane_base + kTmemO + 64 * t_odd + 16 * part, a1);
             tc_wait_ld();
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
+            for (int j = 0; j < 16; ++j) {
               const float x0 = __uint_as_float(a0[j]) * w0;
-              acc[32 * part + j] = live1 ? fmaf(__uint_as_float(a1[j]), w1, x0) : x0;
+              acc[16 * part + j] = live1 ? fmaf(__uint_as_float(a1[j]), w1, x0) : x0;
             }
           }
         } else {
@@ -720,33 +768,39 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&sm->o_free[par]));
-        if (t_mine == 1) {
-#pragma unroll
-          for (int j = 0; j < 64; ++j) sm->xfer[j][r_blk] = acc[j];
-        }
       }
-      named_barrier_sync(2, 128);
-      if (ok && t_mine == 0) {
-        const int row = it.mb * 64 + r_blk;
-        uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.o) + it.b * p.o_sb +
-                                              it.h * p.o_sh + static_cast<int64_t>(row) * p.o_sn);
+      const int row = it.mb * 64 + r_blk;
+      uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.o) + it.b * p.o_sb +
+                                            it.h * p.o_sh + static_cast<int64_t>(row) * p.o_sn);
+      bool any_failed = false;
 #pragma unroll
-        for (int v4 = 0; v4 < 8; ++v4) {
-          uint32_t pkd[4];
+      for (int part = 0; part < 2; ++part) {
+        if (ok && half == 1) {
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int col = 8 * v4 + 2 * j;
-            pkd[j] = pack_2x16<kBf16>(acc[col] + sm->xfer[col][r_blk],
-                                      acc[col + 1] + sm->xfer[col + 1][r_blk]);
-          }
-          dst[v4] = make_uint4(pkd[0], pkd[1], pkd[2], pkd[3]);
+          for (int j = 0; j < 32; ++j) sm->xfer[j][r_blk] = acc[32 * part + j];
         }
+        named_barrier_sync(2, 128);
+        if (ok && half == 0) {
+#pragma unroll
+          for (int v4 = 0; v4 < 4; ++v4) {
+            uint32_t pkd[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int col = 8 * v4 + 2 * j;
+              pkd[j] = pack_2x16<kBf16>(acc[32 * part + col] + sm->xfer[col][r_blk],
+                                        acc[32 * part + col + 1] + sm->xfer[col + 1][r_blk]);
+            }
+            dst[4 * part + v4] = make_uint4(pkd[0], pkd[1], pkd[2], pkd[3]);
+          }
+        }
+        // xfer may be overwritten now; all four warps leave together if any gave up
+        any_failed = named_barrier_or(2, 128, !ok);
+      }
+      if (ok && half == 0) {
         const int64_t ri = (static_cast<int64_t>(it.b) * p.H + it.h) * p.N + row;
         p.lse2[ri] = l_all > 0.f ? m_all + lg2_approx(l_all) : -INFINITY;
         if (p.rowmax) p.rowmax[ri] = mt;
       }
-      // xfer may be overwritten by the next item now; all four warps leave together if any gave up
-      const bool any_failed = named_barrier_or(2, 128, !ok);
       if (any_failed) break;
     }
     if (!ok) fwd_give_up(sm, p.status, kFailOut);
@@ -760,30 +814,58 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     tc_fence_after();
     tmem_dealloc(tmem, kFwdTmemCols);
   }
-  if (threadIdx.x == 0) BSA_TR_CTA(1, global_timer_ns());
 }
 
-}  // namespace bsa
+// Tensor maps of recent operands.  Encoding one takes the driver about a microsecond, and a
+// forward call needs three; a model calls the op with the same few buffers over and over.
+struct TmapKey {
+  const void* base;
+  int64_t s[4];
+  int B, H, N, dtype;
+};
+struct TmapEntry {
+  TmapKey key;
+  CUtensorMap map;
+  bool valid;
+};
 
-#ifdef BSA_TRACE
-extern "C" int bsa_debug_copy_cta_times(unsigned long long* host) {
-  return cudaMemcpyFromSymbol(host, bsa::g_bsa_cta_times, sizeof(bsa::g_bsa_cta_times)) ==
-                 cudaSuccess
-             ? 0
-             : -5;
+static int cached_qkv_tmap(CUtensorMap* out, const void* base, const int64_t s[4], int B, int H,
+                           int N, int dtype) {
+  constexpr int kEntries = 12;
+  static thread_local TmapEntry cache[kEntries];
+  static thread_local int next = 0;
+  TmapKey key;
+  memset(&key, 0, sizeof(key));
+  key.base = base;
+  for (int i = 0; i < 4; ++i) key.s[i] = s[i];
+  key.B = B;
+  key.H = H;
+  key.N = N;
+  key.dtype = dtype;
+  for (int i = 0; i < kEntries; ++i)
+    if (cache[i].valid && memcmp(&cache[i].key, &key, sizeof(key)) == 0) {
+      *out = cache[i].map;
+      return BSA_OK;
+    }
+  const int rc = make_qkv_tmap(out, base, s, B, H, N, dtype, 64);
+  if (rc != BSA_OK) return rc;
+  TmapEntry& e = cache[next];
+  next = (next + 1) % kEntries;
+  e.key = key;
+  e.map = *out;
+  e.valid = true;
+  return BSA_OK;
 }
-#endif
-
-namespace bsa {
 
 static int launch_fwd(const void* q, const int64_t q_strides[4], const void* k,
                       const int64_t k_strides[4], const void* v, const int64_t v_strides[4], void* o,
                       const int64_t o_strides[4], float* lse2, float* rowmax,
                       const int32_t* row_ptr, const int32_t* col_idx, const uint8_t* block,
                       const int64_t* block_strides, int list_b_stride, int list_h_stride,
-                      float sm_scale, int dtype, int B, int H, int N, int D, int32_t* status,
-                      int32_t* ticket, void* stream) {
+                      float sm_scale, int dtype, int B, int H, int N, int D, int row_begin,
+                      int row_end, int32_t* status, int32_t* ticket, void* stream) {
   if (B <= 0 || H <= 0 || N <= 0 || (N % kBlock) != 0 || D != kHeadDim) return BSA_ERR_BAD_SHAPE;
+  if (!(sm_scale >= 0.f)) return BSA_ERR_BAD_SHAPE;  // the row maximum is taken before scaling
   if (dtype != BSA_F16 && dtype != BSA_BF16) return BSA_ERR_BAD_DTYPE;
   if (!lse2 || (block == nullptr && (!row_ptr || !col_idx))) return BSA_ERR_BAD_POINTER;
   int rc;
@@ -795,12 +877,15 @@ static int launch_fwd(const void* q, const int64_t q_strides[4], const void* k,
 
   const int nb = N / kBlock;
   if (nb > kFwdMaxTiles) return BSA_ERR_TOO_LARGE;
-  if (static_cast<int64_t>(B) * H * nb > 0x7fffffffLL) return BSA_ERR_TOO_LARGE;
+  if (row_begin < 0 || row_end > nb || row_begin > row_end) return BSA_ERR_BAD_SHAPE;
+  const int nrows = row_end - row_begin;
+  if (nrows == 0) return BSA_OK;  // an empty share of the rows: nothing to launch
+  if (static_cast<int64_t>(B) * H * nrows > 0x7fffffffLL) return BSA_ERR_TOO_LARGE;
 
   CUtensorMap tm_q, tm_k, tm_v;
-  if ((rc = make_qkv_tmap(&tm_q, q, q_strides, B, H, N, dtype, 64)) != BSA_OK) return rc;
-  if ((rc = make_qkv_tmap(&tm_k, k, k_strides, B, H, N, dtype, 64)) != BSA_OK) return rc;
-  if ((rc = make_qkv_tmap(&tm_v, v, v_strides, B, H, N, dtype, 64)) != BSA_OK) return rc;
+  if ((rc = cached_qkv_tmap(&tm_q, q, q_strides, B, H, N, dtype)) != BSA_OK) return rc;
+  if ((rc = cached_qkv_tmap(&tm_k, k, k_strides, B, H, N, dtype)) != BSA_OK) return rc;
+  if ((rc = cached_qkv_tmap(&tm_v, v, v_strides, B, H, N, dtype)) != BSA_OK) return rc;
 
   FwdParams prm;
   prm.row_ptr = row_ptr;
@@ -820,9 +905,11 @@ static int launch_fwd(const void* q, const int64_t q_strides[4], const void* k,
   prm.H = H;
   prm.N = N;
   prm.nb = nb;
+  prm.row_begin = row_begin;
+  prm.nrows = nrows;
   prm.list_b_stride = list_b_stride;
   prm.list_h_stride = list_h_stride;
-  prm.items = B * H * nb;
+  prm.items = B * H * nrows;
   prm.scale_log2 = sm_scale * 1.4426950408889634f;
   prm.status = status;
   prm.ticket = ticket;
@@ -841,16 +928,45 @@ static int launch_fwd(const void* q, const int64_t q_strides[4], const void* k,
 
 }  // namespace bsa
 
+extern "C" int bsa_attn_fwd_rows(const void* q, const int64_t q_strides[4], const void* k,
+                                 const int64_t k_strides[4], const void* v,
+                                 const int64_t v_strides[4], void* o, const int64_t o_strides[4],
+                                 float* lse2, float* rowmax, const int32_t* row_ptr,
+                                 const int32_t* col_idx, int list_b_stride, int list_h_stride,
+                                 float sm_scale, int dtype, int B, int H, int N, int D,
+                                 int row_begin, int row_end, int32_t* work_counter,
+                                 int32_t* status, void* stream) {
+  if (!row_ptr || !col_idx) return BSA_ERR_BAD_POINTER;
+  return bsa::launch_fwd(q, q_strides, k, k_strides, v, v_strides, o, o_strides, lse2, rowmax,
+                         row_ptr, col_idx, nullptr, nullptr, list_b_stride, list_h_stride, sm_scale,
+                         dtype, B, H, N, D, row_begin, row_end, status, work_counter, stream);
+}
+
 extern "C" int bsa_attn_fwd(const void* q, const int64_t q_strides[4], const void* k,
                             const int64_t k_strides[4], const void* v, const int64_t v_strides[4],
                             void* o, const int64_t o_strides[4], float* lse2, float* rowmax,
                             const int32_t* row_ptr, const int32_t* col_idx, int list_b_stride,
                             int list_h_stride, float sm_scale, int dtype, int B, int H, int N,
                             int D, int32_t* work_counter, int32_t* status, void* stream) {
-  if (!row_ptr || !col_idx) return BSA_ERR_BAD_POINTER;
+  return bsa_attn_fwd_rows(q, q_strides, k, k_strides, v, v_strides, o, o_strides, lse2, rowmax,
+                           row_ptr, col_idx, list_b_stride, list_h_stride, sm_scale, dtype, B, H,
+                           N, D, 0, N / bsa::kBlock, work_counter, status, stream);
+}
+
+extern "C" int bsa_attn_fwd_block_mask_rows(
+    const void* q, const int64_t q_strides[4], const void* k, const int64_t k_strides[4],
+    const void* v, const int64_t v_strides[4], void* o, const int64_t o_strides[4], float* lse2,
+    float* rowmax, const uint8_t* block, const int64_t block_strides[4], int Bm, int Hm,
+    float sm_scale, int dtype, int B, int H, int N, int D, int row_begin, int row_end,
+    int32_t* work_counter, int32_t* status, void* stream) {
+  if (!block || !block_strides) return BSA_ERR_BAD_POINTER;
+  if ((Bm != 1 && Bm != B) || (Hm != 1 && Hm != H)) return BSA_ERR_BAD_SHAPE;
+  for (int i = 0; i < 4; ++i)
+    if (block_strides[i] < 0) return BSA_ERR_BAD_STRIDE;
   return bsa::launch_fwd(q, q_strides, k, k_strides, v, v_strides, o, o_strides, lse2, rowmax,
-                         row_ptr, col_idx, nullptr, nullptr, list_b_stride, list_h_stride, sm_scale,
-                         dtype, B, H, N, D, status, work_counter, stream);
+                         nullptr, nullptr, block, block_strides, Bm > 1 ? 1 : 0, Hm > 1 ? 1 : 0,
+                         sm_scale, dtype, B, H, N, D, row_begin, row_end, status, work_counter,
+                         stream);
 }
 
 extern "C" int bsa_attn_fwd_block_mask(const void* q, const int64_t q_strides[4], const void* k,
@@ -861,11 +977,8 @@ extern "C" int bsa_attn_fwd_block_mask(const void* q, const int64_t q_strides[4]
                                        int Bm, int Hm, float sm_scale, int dtype, int B, int H,
                                        int N, int D, int32_t* work_counter, int32_t* status,
                                        void* stream) {
-  if (!block || !block_strides) return BSA_ERR_BAD_POINTER;
-  if ((Bm != 1 && Bm != B) || (Hm != 1 && Hm != H)) return BSA_ERR_BAD_SHAPE;
-  for (int i = 0; i < 4; ++i)
-    if (block_strides[i] < 0) return BSA_ERR_BAD_STRIDE;
-  return bsa::launch_fwd(q, q_strides, k, k_strides, v, v_strides, o, o_strides, lse2, rowmax,
-                         nullptr, nullptr, block, block_strides, Bm > 1 ? 1 : 0, Hm > 1 ? 1 : 0,
-                         sm_scale, dtype, B, H, N, D, status, work_counter, stream);
+  return bsa_attn_fwd_block_mask_rows(q, q_strides, k, k_strides, v, v_strides, o, o_strides, lse2,
+                                      rowmax, block, block_strides, Bm, Hm, sm_scale, dtype, B, H,
+                                      N, D, 0, N > 0 ? N / bsa::kBlock : 0, work_counter, status,
+                                      stream);
 }

@@ -18,7 +18,8 @@ constexpr int64_t kStaticScratchInts = BSA_STATIC_SCRATCH_INTS;
 static __device__ __align__(256) int32_t g_static_lists[kStaticScratchInts];
 
 // The array's name is only a host-side handle; kernels need its device address, which differs per
-// device.  Looked up once per device, with that device current.
+// device.  Looked up once per device, with that device current; with lazy module loading this
+// look-up is also what makes the driver load the module and reserve the array on the device.
 int32_t* static_lists_for_current_device(int* status) {
   static std::atomic<int32_t*> cached[64];
   int dev = -1;
@@ -51,7 +52,7 @@ extern "C" int bsa_attn_fwd_block_mask_static(
   using namespace bsa;
   if (B <= 0 || H <= 0 || N <= 0 || (N % kBlock) != 0 || D != kHeadDim) return BSA_ERR_BAD_SHAPE;
   if ((Bm != 1 && Bm != B) || (Hm != 1 && Hm != H)) return BSA_ERR_BAD_SHAPE;
-  if (!block) return BSA_ERR_BAD_POINTER;
+  if (!block || !block_strides) return BSA_ERR_BAD_POINTER;
   const int64_t nb = N / kBlock;
   const int64_t rows = static_cast<int64_t>(Bm) * Hm * nb;
   // worst case: every block of every mask row is kept
@@ -67,10 +68,15 @@ extern "C" int bsa_attn_fwd_block_mask_static(
   // The builder writes every word it later reads (counts, offsets, entries, meta), so nothing of
   // the previous call's contents has to be cleared first.
   rc = bsa_tile_lists_build(block, block_strides, Bm, Hm, static_cast<int>(nb), row_ptr, col_idx,
-                            nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, meta,
-                            stream);
+                            nullptr, nullptr, nullptr, meta, stream);
   if (rc != BSA_OK) return rc;
   return bsa_attn_fwd(q, q_strides, k, k_strides, v, v_strides, o, o_strides, lse2, nullptr,
                       row_ptr, col_idx, Bm > 1 ? Hm : 0, Hm > 1 ? 1 : 0, sm_scale, dtype, B, H, N,
                       D, nullptr, nullptr, stream);
+}
+
+extern "C" int bsa_static_warmup(void) {
+  int rc = BSA_OK;
+  (void)static_lists_for_current_device(&rc);
+  return rc;
 }

@@ -129,6 +129,11 @@ reorder_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, int64_
       p1 = __ldg(inv_orders + 3 * h + 1);
       p2 = __ldg(inv_orders + 3 * h + 2);
     }
+    // An order row that is not a permutation of (0, 1, 2) would send tokens past the end of the
+    // head (the reference has no check either): such a head's rows are left unwritten.
+    const bool valid = ((1 << p0) | (1 << p1) | (1 << p2)) == 7 && (p0 | p1 | p2) >= 0 &&
+                       (!kInverse || (((1 << o0) | (1 << o1) | (1 << o2)) == 7 && (o0 | o1 | o2) >= 0));
+    if (!valid) continue;
     const uint8_t* src = in + b * sb + h * sh;  // byte offsets
     uint8_t* dst = out + b * ob + h * oh;
     Vec val[kReorderPieces];

@@ -1,8 +1,8 @@
 // Mask preprocessing on the device (HBM-bound byte/integer work):
 //   bsa_mask_reduce      dense [.., N, N] boolean mask  ->  [.., nb, nb] block mask (any over 64x64)
-//   bsa_tile_lists_build block mask -> CSR, transposed CSR, pair lists, and the reference's
-//                        (groups, n_list) layout, with three launches (one, for the row lists of
-//                        a small mask alone) and no host synchronisation.
+//   bsa_tile_lists_build block mask -> CSR, transposed CSR and the reference's (groups, n_list)
+//                        layout, with three launches (one, for the row lists of a small mask
+//                        alone) and no host synchronisation.
 #include "host_common.h"
 
 namespace bsa {
@@ -74,89 +74,66 @@ mask_reduce_kernel(const uint8_t* __restrict__ dense, int64_t sb, int64_t sh, in
 // ---------------------------------------------------------------------------------------------
 // block mask -> tile lists
 // ---------------------------------------------------------------------------------------------
-// Four list kinds share one code path.  "major" is the axis a list belongs to, "minor" the axis
+// Two list kinds share one code path.  "major" is the axis a list belongs to, "minor" the axis
 // it enumerates (ascending).
 //   kind 0 rows   : major = query block,      minor = key block     -> row_ptr / col_idx
 //   kind 1 cols   : major = key block,        minor = query block   -> col_ptr / row_idx
-//   kind 2 qpairs : major = query-block pair, minor = key block     -> qpair_ptr / qpair_ent
-//   kind 3 kpairs : major = key-block pair,   minor = query block   -> kpair_ptr / kpair_ent
 // Pass 1 writes per-major counts into ptr[], the scan turns them into offsets in place (ptr[n] =
 // total), pass 2 writes the entries.
 struct ListArgs {
   const uint8_t* block;
   int64_t s0, s1, s2, s3;
-  int B, H, nb, npair;
-  int32_t* ptr[4];
-  int32_t* ent[4];
+  int B, H, nb;
+  int32_t* ptr[2];
+  int32_t* ent[2];
   int32_t* groups;
   int32_t* meta;
 };
 
 constexpr int kListThreads = 256;
 
-__device__ __forceinline__ int kind_majors(const ListArgs& a, int kind) {
-  return a.B * a.H * (kind < 2 ? a.nb : a.npair);
-}
-
-// 0 = not kept; for pair kinds bit0 / bit1 = first / second block of the pair keeps it.
-template <bool kTransposed, bool kPair>
-__device__ __forceinline__ int list_flags(const ListArgs& a, const uint8_t* head, int major,
-                                          int minor) {
-  if constexpr (!kPair) {
-    const int64_t off = kTransposed ? minor * a.s2 + major * a.s3 : major * a.s2 + minor * a.s3;
-    return head[off] != 0;
-  } else {
-    const int m0 = 2 * major, m1 = 2 * major + 1;
-    const int64_t off0 = kTransposed ? minor * a.s2 + m0 * a.s3 : m0 * a.s2 + minor * a.s3;
-    int f = head[off0] != 0;
-    if (m1 < a.nb) {
-      const int64_t off1 = kTransposed ? minor * a.s2 + m1 * a.s3 : m1 * a.s2 + minor * a.s3;
-      f |= (head[off1] != 0) << 1;
-    }
-    return f;
-  }
+__device__ __forceinline__ bool list_kept(const ListArgs& a, const uint8_t* head, int row, int col) {
+  return head[row * a.s2 + col * a.s3] != 0;
 }
 
 // Lists along the mask's rows: one warp per major unit, lanes sweep the minor axis 32 at a time.
-template <bool kPair, bool kFill>
-__device__ __forceinline__ void lists_along_rows(const ListArgs& a, int kind) {
-  const int per_head = kPair ? a.npair : a.nb;
+template <bool kFill>
+__device__ __forceinline__ void lists_along_rows(const ListArgs& a) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t unit = static_cast<int64_t>(blockIdx.x) * (kListThreads / 32) + warp;
-  if (unit >= static_cast<int64_t>(a.B) * a.H * per_head) return;
-  const int bh = static_cast<int>(unit / per_head);
-  const int major = static_cast<int>(unit % per_head);
+  if (unit >= static_cast<int64_t>(a.B) * a.H * a.nb) return;
+  const int bh = static_cast<int>(unit / a.nb);
+  const int major = static_cast<int>(unit % a.nb);
   const uint8_t* head = a.block + (bh / a.H) * a.s0 + (bh % a.H) * a.s1;
   int count = 0;
   int32_t* out = nullptr;
-  if constexpr (kFill) out = a.ent[kind] + a.ptr[kind][unit];
+  if constexpr (kFill) out = a.ent[0] + a.ptr[0][unit];
   for (int c0 = 0; c0 < a.nb; c0 += 32) {
     const int c = c0 + lane;
-    const int f = c < a.nb ? list_flags<false, kPair>(a, head, major, c) : 0;
-    const unsigned m = __ballot_sync(0xffffffffu, f != 0);
+    const bool f = c < a.nb && list_kept(a, head, major, c);
+    const unsigned m = __ballot_sync(0xffffffffu, f);
     if constexpr (kFill) {
-      if (f) out[count + __popc(m & ((1u << lane) - 1u))] = kPair ? ((c << 2) | f) : c;
+      if (f) out[count + __popc(m & ((1u << lane) - 1u))] = c;
     }
     count += __popc(m);
   }
   if constexpr (!kFill) {
-    if (lane == 0) a.ptr[kind][unit] = count;
+    if (lane == 0) a.ptr[0][unit] = count;
   }
 }
 
 // Lists along the mask's columns: one CTA per 32 major units (lane = unit, so a warp reads
 // consecutive bytes of a mask row); the 8 warps split the minor axis into contiguous chunks.
-template <bool kPair, bool kFill>
-__device__ __forceinline__ void lists_along_cols(const ListArgs& a, int kind) {
+template <bool kFill>
+__device__ __forceinline__ void lists_along_cols(const ListArgs& a) {
   __shared__ int s_cnt[kListThreads / 32][33];
-  const int per_head = kPair ? a.npair : a.nb;
-  const int groups_per_head = (per_head + 31) / 32;
+  const int groups_per_head = (a.nb + 31) / 32;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t g = blockIdx.x;
   if (g >= static_cast<int64_t>(a.B) * a.H * groups_per_head) return;  // whole CTA leaves
   const int bh = static_cast<int>(g / groups_per_head);
   const int major = static_cast<int>(g % groups_per_head) * 32 + lane;
-  const bool valid = major < per_head;
+  const bool valid = major < a.nb;
   const uint8_t* head = a.block + (bh / a.H) * a.s0 + (bh % a.H) * a.s1;
   constexpr int kWarps = kListThreads / 32;
   const int chunk = (a.nb + kWarps - 1) / kWarps;
@@ -164,27 +141,25 @@ __device__ __forceinline__ void lists_along_cols(const ListArgs& a, int kind) {
   const int r1 = min(a.nb, r0 + chunk);
   int count = 0;
   if (valid)
-    for (int r = r0; r < r1; ++r) count += list_flags<true, kPair>(a, head, major, r) != 0;
+    for (int r = r0; r < r1; ++r) count += list_kept(a, head, r, major) ? 1 : 0;
   s_cnt[warp][lane] = count;
   __syncthreads();
-  const int64_t unit = static_cast<int64_t>(bh) * per_head + major;
+  const int64_t unit = static_cast<int64_t>(bh) * a.nb + major;
   if constexpr (!kFill) {
     if (warp == 0 && valid) {
       int total = 0;
 #pragma unroll
       for (int w = 0; w < kWarps; ++w) total += s_cnt[w][lane];
-      a.ptr[kind][unit] = total;
+      a.ptr[1][unit] = total;
     }
   } else {
     if (valid) {
       int before = 0;
       for (int w = 0; w < warp; ++w) before += s_cnt[w][lane];
-      int32_t* out = a.ent[kind] + a.ptr[kind][unit] + before;
+      int32_t* out = a.ent[1] + a.ptr[1][unit] + before;
       int k = 0;
-      for (int r = r0; r < r1; ++r) {
-        const int f = list_flags<true, kPair>(a, head, major, r);
-        if (f) out[k++] = kPair ? ((r << 2) | f) : r;
-      }
+      for (int r = r0; r < r1; ++r)
+        if (list_kept(a, head, r, major)) out[k++] = r;
     }
   }
 }
@@ -193,12 +168,8 @@ template <bool kFill>
 __global__ void __launch_bounds__(kListThreads) lists_pass_kernel(const ListArgs a) {
   const int kind = blockIdx.y;
   if (a.ptr[kind] == nullptr) return;
-  switch (kind) {
-    case 0: lists_along_rows<false, kFill>(a, 0); break;
-    case 1: lists_along_cols<false, kFill>(a, 1); break;
-    case 2: lists_along_rows<true, kFill>(a, 2); break;
-    default: lists_along_cols<true, kFill>(a, 3); break;
-  }
+  if (kind == 0) lists_along_rows<kFill>(a);
+  else lists_along_cols<kFill>(a);
 }
 
 // In-place exclusive scan of the counts of one list kind per CTA; kind 0 also emits the
@@ -237,7 +208,7 @@ __global__ void __launch_bounds__(kScanThreads) lists_scan_kernel(const ListArgs
   const int kind = blockIdx.x;
   int32_t* ptr = a.ptr[kind];
   if (ptr == nullptr) return;  // meta was cleared by the host side
-  const int64_t n = kind_majors(a, kind);
+  const int64_t n = static_cast<int64_t>(a.B) * a.H * a.nb;
   const int64_t per = (n + kScanThreads - 1) / kScanThreads;
   const int64_t i0 = min(n, threadIdx.x * per), i1 = min(n, i0 + per);
   int sum = 0, nonempty = 0;
@@ -269,12 +240,10 @@ __global__ void __launch_bounds__(kScanThreads) lists_scan_kernel(const ListArgs
   }
   if (threadIdx.x == 0) {
     ptr[n] = total;
-    // meta = {nnz, G, qpair entries, kpair entries}; the transposed CSR holds nnz entries too
+    // meta = {nnz, G, 0, ...}; the transposed CSR holds nnz entries too
     if (kind == 0) {
       a.meta[0] = total;
       a.meta[1] = gtotal;
-    } else if (kind >= 2) {
-      a.meta[kind] = total;
     }
   }
 }
@@ -397,15 +366,10 @@ extern "C" int bsa_mask_reduce(const uint8_t* dense, const int64_t s[4], int B, 
 extern "C" int bsa_tile_list_sizes(int B, int H, int nb, bsa_list_sizes* out) {
   if (B <= 0 || H <= 0 || nb <= 0 || !out) return BSA_ERR_BAD_SHAPE;
   const int64_t rows = static_cast<int64_t>(B) * H * nb;
-  const int64_t pairs = static_cast<int64_t>(B) * H * ((nb + 1) / 2);
   out->row_ptr = rows + 1;
   out->col_idx = rows * nb;
   out->col_ptr = rows + 1;
   out->row_idx = rows * nb;
-  out->qpair_ptr = pairs + 1;
-  out->qpair_ent = pairs * nb;
-  out->kpair_ptr = pairs + 1;
-  out->kpair_ent = pairs * nb;
   out->groups = rows * 5;
   out->meta = 8;
   return BSA_OK;
@@ -413,15 +377,13 @@ extern "C" int bsa_tile_list_sizes(int B, int H, int nb, bsa_list_sizes* out) {
 
 extern "C" int bsa_tile_lists_build(const uint8_t* block, const int64_t s[4], int B, int H, int nb,
                                     int32_t* row_ptr, int32_t* col_idx, int32_t* col_ptr,
-                                    int32_t* row_idx, int32_t* qpair_ptr, int32_t* qpair_ent,
-                                    int32_t* kpair_ptr, int32_t* kpair_ent, int32_t* groups,
-                                    int32_t* meta, void* stream) {
+                                    int32_t* row_idx, int32_t* groups, int32_t* meta,
+                                    void* stream) {
   using namespace bsa;
   if (B <= 0 || H <= 0 || nb <= 0) return BSA_ERR_BAD_SHAPE;
   if (!block || !meta) return BSA_ERR_BAD_POINTER;
   if ((row_ptr == nullptr) != (col_idx == nullptr) || (col_ptr == nullptr) != (row_idx == nullptr) ||
-      (qpair_ptr == nullptr) != (qpair_ent == nullptr) ||
-      (kpair_ptr == nullptr) != (kpair_ent == nullptr) || (groups != nullptr && row_ptr == nullptr))
+      (groups != nullptr && row_ptr == nullptr))
     return BSA_ERR_BAD_POINTER;
   for (int i = 0; i < 4; ++i)
     if (s[i] < 0) return BSA_ERR_BAD_STRIDE;
@@ -437,15 +399,10 @@ extern "C" int bsa_tile_lists_build(const uint8_t* block, const int64_t s[4], in
   a.B = B;
   a.H = H;
   a.nb = nb;
-  a.npair = (nb + 1) / 2;
   a.ptr[0] = row_ptr;
   a.ent[0] = col_idx;
   a.ptr[1] = col_ptr;
   a.ent[1] = row_idx;
-  a.ptr[2] = qpair_ptr;
-  a.ent[2] = qpair_ent;
-  a.ptr[3] = kpair_ptr;
-  a.ent[3] = kpair_ent;
   a.groups = groups;
   a.meta = meta;
 
@@ -455,12 +412,10 @@ extern "C" int bsa_tile_lists_build(const uint8_t* block, const int64_t s[4], in
   auto upd = [&](int64_t v) { blocks = v > blocks ? v : blocks; };
   if (row_ptr) upd((bh * nb + warps_per_cta - 1) / warps_per_cta);
   if (col_ptr) upd(bh * ((nb + 31) / 32));
-  if (qpair_ptr) upd((bh * a.npair + warps_per_cta - 1) / warps_per_cta);
-  if (kpair_ptr) upd(bh * ((a.npair + 31) / 32));
   if (blocks > 0x7fffffffLL) return BSA_ERR_TOO_LARGE;
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (row_ptr && !col_ptr && !qpair_ptr && !kpair_ptr && bh * nb <= kSmallRows &&
+  if (row_ptr && !col_ptr && bh * nb <= kSmallRows &&
       bh * nb * nb <= kSmallBytes) {
     const size_t smem = static_cast<size_t>((bh * nb * nb + 15) & ~15LL);
     int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(lists_rows_small_kernel),
@@ -470,9 +425,9 @@ extern "C" int bsa_tile_lists_build(const uint8_t* block, const int64_t s[4], in
     return cudaGetLastError() == cudaSuccess ? BSA_OK : BSA_ERR_CUDA;
   }
   if (cudaMemsetAsync(meta, 0, 8 * sizeof(int32_t), st) != cudaSuccess) return BSA_ERR_CUDA;
-  const dim3 grid(static_cast<unsigned>(blocks), 4);
+  const dim3 grid(static_cast<unsigned>(blocks), 2);
   lists_pass_kernel<false><<<grid, kListThreads, 0, st>>>(a);
-  lists_scan_kernel<<<4, kScanThreads, 0, st>>>(a);
+  lists_scan_kernel<<<2, kScanThreads, 0, st>>>(a);
   lists_pass_kernel<true><<<grid, kListThreads, 0, st>>>(a);
   return cudaGetLastError() == cudaSuccess ? BSA_OK : BSA_ERR_CUDA;
 }

@@ -50,30 +50,16 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
   return t;
 }
 
-// ---------------------------------------------------------------------------------------------
-// Optional timeline trace (builds with -DBSA_TRACE only): one CTA records clock64() at chosen
-// points into a device array that a debug entry point copies out.  Compiled out otherwise.
-// ---------------------------------------------------------------------------------------------
-#ifdef BSA_TRACE
-#ifndef BSA_TRACE_CTA
-#define BSA_TRACE_CTA 0
-#endif
-constexpr int kTraceRoles = 8, kTraceSteps = 96, kTraceSlots = 4;
-static __device__ long long g_bsa_trace[kTraceRoles * kTraceSteps * kTraceSlots];  // per file
-static __device__ unsigned long long g_bsa_cta_times[4096 * 4];  // start, end (ns), smid, steps
-#define BSA_TR_CTA(idx, val)                                                           \
-  do {                                                                                 \
-    if (blockIdx.x < 4096) bsa::g_bsa_cta_times[blockIdx.x * 4 + (idx)] = (val);       \
-  } while (0)
-#define BSA_TR(role, step, slot)                                                       \
-  do {                                                                                 \
-    if (blockIdx.x == BSA_TRACE_CTA && (step) < bsa::kTraceSteps)                      \
-      bsa::g_bsa_trace[((role) * bsa::kTraceSteps + (step)) * bsa::kTraceSlots + (slot)] = clock64(); \
-  } while (0)
-#else
-#define BSA_TR(role, step, slot) ((void)0)
-#define BSA_TR_CTA(idx, val) ((void)0)
-#endif
+// Records a give-up code in the optional status word unless one is there already.  Plain loads
+// and stores on purpose: the word may live in pinned host memory that the device reaches over
+// PCIe, and which of several simultaneous reports wins does not matter.
+__device__ __forceinline__ void report_status(int32_t* status, int code) {
+  if (status != nullptr) {
+    volatile int32_t* w = status;
+    if (*w == 0) *w = code;
+    __threadfence_system();
+  }
+}
 
 // ---------------------------------------------------------------------------------------------
 // mbarrier
@@ -169,29 +155,6 @@ __device__ __forceinline__ bool mbar_wait_warp_idle(uint32_t bar, uint32_t parit
   return __all_sync(0xffffffffu, ok);
 }
 
-// Bounded wait of a whole warp until a shared-memory counter (written by another warp after a
-// __threadfence_block) reaches `target`.  Same give-up rules as mbar_wait.
-__device__ __forceinline__ bool flag_wait_warp(const int* flag, int target,
-                                               volatile int* abort_flag) {
-  const volatile int* f = flag;
-  bool ok = true;
-  if (*f < target) {
-    uint64_t t0 = 0;
-    uint32_t spins = 0;
-    while (*f < target) {
-      if ((++spins & 255u) == 0u) {
-        if (*abort_flag) { ok = false; break; }
-        const uint64_t now = global_timer_ns();
-        if (t0 == 0) t0 = now;
-        else if (now - t0 > BSA_WAIT_LIMIT_NS) { ok = false; break; }
-      }
-    }
-  }
-  ok = __all_sync(0xffffffffu, ok);
-  __threadfence_block();
-  return ok;
-}
-
 // ---------------------------------------------------------------------------------------------
 // TMA (cp.async.bulk.tensor), tile mode, 4-D, no multicast
 // ---------------------------------------------------------------------------------------------
@@ -215,6 +178,8 @@ __device__ __forceinline__ void bulk_load_1d(uint32_t dst_smem, const void* src,
       ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
       : "memory");
 }
+// Makes this thread's earlier ordinary writes to shared memory visible to the async proxy (TMA,
+// tcgen05.mma operand reads); follow it with a barrier before the reader is released.
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
@@ -342,6 +307,16 @@ __device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_
       "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]),
       "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]),
       "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+
+// Stores zeros to 32 columns of the warp's 32 lanes.
+__device__ __forceinline__ void tmem_st_zero_32x32b_x32(uint32_t taddr) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, "
+      "%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};"
+      ::"r"(taddr), "r"(0u)
       : "memory");
 }
 

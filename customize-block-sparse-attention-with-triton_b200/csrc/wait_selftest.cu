@@ -24,7 +24,7 @@ __global__ void __launch_bounds__(64, 1) wait_selftest_kernel(int32_t* status, i
     const bool ok = mbar_wait_warp(smem_u32(&bar), 0, flag);
     if (!ok && lane == 0) {
       abort_flag = 1;
-      if (status) atomicCAS(status, 0, 99);
+      report_status(status, 99);
     }
     if (lane == 0) report[0] = ok ? 1 : 0;
   } else {

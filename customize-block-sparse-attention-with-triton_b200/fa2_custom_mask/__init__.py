@@ -12,6 +12,7 @@ from .fa2_custom_mask import (  # noqa: F401
     flash_attention_custom_mask,
     reduce_dense_mask,
 )
+from . import sharding  # noqa: F401
 from .functional import (  # noqa: F401
     apply_head_wise_reorder,
     apply_inv_reorder,

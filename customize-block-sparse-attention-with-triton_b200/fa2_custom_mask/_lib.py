@@ -27,8 +27,7 @@ class BsaError(RuntimeError):
 
 class ListSizes(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int64) for n in (
-        "row_ptr", "col_idx", "col_ptr", "row_idx", "qpair_ptr", "qpair_ent",
-        "kpair_ptr", "kpair_ent", "groups", "meta")]
+        "row_ptr", "col_idx", "col_ptr", "row_idx", "groups", "meta")]
 
 
 _vp, _i, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
@@ -40,11 +39,15 @@ SIGNATURES = {
     "bsa_strerror": [_i],
     "bsa_mask_reduce": [_vp, _s4, _i, _i, _i, _vp, _vp, _vp],
     "bsa_tile_list_sizes": [_i, _i, _i, ctypes.POINTER(ListSizes)],
-    "bsa_tile_lists_build": [_vp, _s4, _i, _i, _i] + [_vp] * 10 + [_vp],
+    "bsa_tile_lists_build": [_vp, _s4, _i, _i, _i] + [_vp] * 6 + [_vp],
     "bsa_attn_fwd": [_vp, _s4, _vp, _s4, _vp, _s4, _vp, _s4, _vp, _vp, _vp, _vp, _i, _i, _f, _i,
                      _i, _i, _i, _i, _vp, _vp, _vp],
     "bsa_attn_fwd_block_mask": [_vp, _s4, _vp, _s4, _vp, _s4, _vp, _s4, _vp, _vp, _vp, _s4, _i, _i,
                                 _f, _i, _i, _i, _i, _i, _vp, _vp, _vp],
+    "bsa_attn_fwd_rows": [_vp, _s4, _vp, _s4, _vp, _s4, _vp, _s4, _vp, _vp, _vp, _vp, _i, _i, _f, _i,
+                          _i, _i, _i, _i, _i, _i, _vp, _vp, _vp],
+    "bsa_attn_fwd_block_mask_rows": [_vp, _s4, _vp, _s4, _vp, _s4, _vp, _s4, _vp, _vp, _vp, _s4, _i,
+                                     _i, _f, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp],
     "bsa_attn_bwd_delta": [_vp, _vp, _s4, _vp, _i, _i, _i, _i, _i, _vp],
     "bsa_attn_bwd_dkdv": [_vp, _vp, _vp, _vp, _s4, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i,
                           _i, _i, _i, _i, _vp, _vp, _vp],
@@ -56,6 +59,7 @@ SIGNATURES = {
     "bsa_inv_reorder_strided": [_vp, _s4, _vp, _s4, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "bsa_attn_fwd_block_mask_static": [_vp, _s4, _vp, _s4, _vp, _s4, _vp, _s4, _vp, _vp, _s4, _i,
                                        _i, _f, _i, _i, _i, _i, _i, _vp],
+    "bsa_static_warmup": [],
     "bsa_check_status": [_vp, _vp],
     "bsa_selftest_bounded_wait": [_vp, _vp, _vp],
 }

@@ -33,16 +33,12 @@ class TileLists:
     Bm: int
     Hm: int
     nb: int
-    qpair_ptr: Optional[torch.Tensor] = None
-    qpair_ent: Optional[torch.Tensor] = None
-    kpair_ptr: Optional[torch.Tensor] = None
-    kpair_ent: Optional[torch.Tensor] = None
     row_ptr: Optional[torch.Tensor] = None
     col_idx: Optional[torch.Tensor] = None
     col_ptr: Optional[torch.Tensor] = None
     row_idx: Optional[torch.Tensor] = None
     groups: Optional[torch.Tensor] = None
-    meta: Optional[torch.Tensor] = None  # int32[8]: nnz, G, qpair entries, kpair entries
+    meta: Optional[torch.Tensor] = None  # int32[8]: nnz, G, then zeros
 
     def list_strides(self, B: int, H: int):
         """(list_b_stride, list_h_stride) so that head (b,h) uses list b*sb + h*sh."""
@@ -112,13 +108,11 @@ def reduce_dense_mask(dense: torch.Tensor, return_partial: bool = False):
     return (out, partial) if return_partial else out
 
 
-def build_tile_lists(block_mask: torch.Tensor, want_q: bool = False, want_k: bool = False,
-                     want_csr: bool = True, want_groups: bool = False,
+def build_tile_lists(block_mask: torch.Tensor, want_csr: bool = True, want_groups: bool = False,
                      want_csc: bool = True) -> TileLists:
     """Block mask [..,nb,nb] -> device tile lists (worst-case sized, no host synchronisation).
     want_csr: row lists (forward and dQ kernels); want_csc: column lists (dK/dV kernel);
-    want_q / want_k: lists over pairs of adjacent query / key blocks (a data product, not used by
-    the kernels); want_groups: the reference's groups layout."""
+    want_groups: the reference's groups layout."""
     lib = _lib.load()
     m4 = _as_4d(_as_bytes(block_mask))
     if not m4.is_cuda:
@@ -128,7 +122,7 @@ def build_tile_lists(block_mask: torch.Tensor, want_q: bool = False, want_k: boo
         raise ValueError("block mask must be square in its last two dims")
     dev = m4.device
     # worst-case sizes, the same numbers bsa_tile_list_sizes reports
-    rows, pairs = Bm * Hm * nb, Bm * Hm * ((nb + 1) // 2)
+    rows = Bm * Hm * nb
 
     def buf(n):
         return torch.empty(n, dtype=torch.int32, device=dev)
@@ -136,10 +130,6 @@ def build_tile_lists(block_mask: torch.Tensor, want_q: bool = False, want_k: boo
     tl = TileLists(Bm=Bm, Hm=Hm, nb=nb, meta=buf(8))
     want_csr = want_csr or want_groups
     want_csc = want_csc or want_groups
-    if want_q:
-        tl.qpair_ptr, tl.qpair_ent = buf(pairs + 1), buf(pairs * nb)
-    if want_k:
-        tl.kpair_ptr, tl.kpair_ent = buf(pairs + 1), buf(pairs * nb)
     if want_csr:
         tl.row_ptr, tl.col_idx = buf(rows + 1), buf(rows * nb)
     if want_csc:
@@ -150,9 +140,7 @@ def build_tile_lists(block_mask: torch.Tensor, want_q: bool = False, want_k: boo
         _lib.check("bsa_tile_lists_build", lib.bsa_tile_lists_build(
             _lib.ptr(m4), _lib.strides4(m4), Bm, Hm, nb,
             _lib.ptr(tl.row_ptr), _lib.ptr(tl.col_idx), _lib.ptr(tl.col_ptr), _lib.ptr(tl.row_idx),
-            _lib.ptr(tl.qpair_ptr), _lib.ptr(tl.qpair_ent), _lib.ptr(tl.kpair_ptr),
-            _lib.ptr(tl.kpair_ent), _lib.ptr(tl.groups), _lib.ptr(tl.meta),
-            _lib.stream_ptr(dev)))
+            _lib.ptr(tl.groups), _lib.ptr(tl.meta), _lib.stream_ptr(dev)))
     return tl
 
 
@@ -163,7 +151,7 @@ def build_groups_from_block_mask(mask: torch.Tensor):
     synchronisation is the 8-byte read of (nnz, G) needed to size the returned tensors."""
     assert mask.dtype == torch.bool
     assert mask.dim() == 4
-    tl = build_tile_lists(mask, want_q=False, want_k=False, want_groups=True)
+    tl = build_tile_lists(mask, want_groups=True)
     nnz, G = (int(x) for x in tl.meta[:2].tolist())
     if G == 0:
         return None, None
@@ -208,75 +196,114 @@ def check_status(status: torch.Tensor):
     """Synchronises the current stream and raises if a kernel's bounded wait gave up."""
     lib = _lib.load()
     with _on_device(status.device):
-        try:
-            _lib.check("bsa_check_status", lib.bsa_check_status(
-                _lib.ptr(status), _lib.stream_ptr(status.device)))
-        except Exception:
-            # a kernel that gave up may have left its work counter part-way: start afresh
-            for key in [k for k in _work_counters if k[0] == status.device.index]:
-                del _work_counters[key]
-            raise
+        _lib.check("bsa_check_status", lib.bsa_check_status(
+            _lib.ptr(status), _lib.stream_ptr(status.device)))
 
 
-# One zeroed int32 word per (device, stream) for the persistent forward kernel's dynamic hand-out
-# of query blocks.  The kernel leaves the word at zero, and calls on one stream cannot overlap, so
-# the word is allocated once and never touched from the host again.
-_work_counters = {}
+class _StreamState:
+    """What the public op keeps per (device, stream): the zeroed work counter of the persistent
+    kernels (they leave it at zero, also after a bounded wait gave up), and a status word in
+    pinned host memory, which the device can write and the host can read without a
+    synchronisation.  The kernels only ever touch the status word when a wait gave up."""
 
-
-def _work_counter(device: torch.device, stream: int) -> Optional[torch.Tensor]:
-    key = (device.index, stream)
-    word = _work_counters.get(key)
-    if word is None:
-        if torch.cuda.is_current_stream_capturing():
-            return None  # no allocation inside a graph capture: fixed-stride hand-out instead
+    def __init__(self, device):
         # zeroed on the stream that will use it, so no cross-stream ordering is needed
-        word = torch.zeros(1, dtype=torch.int32, device=device)
-        _work_counters[key] = word
-    return word
+        self.counter = torch.zeros(1, dtype=torch.int32, device=device)
+        self.status = torch.zeros(1, dtype=torch.int32).pin_memory()
+
+    def raise_if_reported(self):
+        """Looks at the status word as it is now.  A report means that some earlier call on this
+        stream produced incomplete results; it surfaces at the first call after the kernel that
+        gave up has ended."""
+        code = int(self.status[0])
+        if code != 0:
+            self.status.zero_()
+            raise _lib.BsaError("flash_attention_custom_mask", -9,
+                                f"a bounded wait inside an earlier kernel on this stream gave up "
+                                f"(role {code}); its results are incomplete")
+
+
+_stream_states = {}
+
+
+def _stream_state(device: torch.device, stream: int) -> Optional[_StreamState]:
+    key = (device.index, stream)
+    st = _stream_states.get(key)
+    if st is None:
+        if torch.cuda.is_current_stream_capturing():
+            return None  # no allocation inside a graph capture: fixed-stride hand-out, no report
+        st = _StreamState(device)
+        _stream_states[key] = st
+    return st
+
+
+def _row_range(rows, nb):
+    if rows is None:
+        return 0, nb
+    r0, r1 = int(rows[0]), int(rows[1])
+    if not (0 <= r0 <= r1 <= nb):
+        raise ValueError(f"rows must satisfy 0 <= begin <= end <= {nb}, got {rows}")
+    return r0, r1
+
+
+def _fwd_outputs(q, out, want_rowmax):
+    B, H, N, D = q.shape
+    if out is None:
+        o = torch.empty((B, H, N, D), dtype=q.dtype, device=q.device)
+        lse2 = torch.empty((B, H, N), dtype=torch.float32, device=q.device)
+    else:
+        o, lse2 = out
+        if o.shape != q.shape or o.dtype != q.dtype or lse2.shape != (B, H, N) or \
+                lse2.dtype != torch.float32 or not lse2.is_contiguous():
+            raise ValueError("out must be (o like q, contiguous float32 lse2 [B,H,N])")
+    rowmax = torch.empty((B, H, N), dtype=torch.float32, device=q.device) if want_rowmax else None
+    return o, lse2, rowmax
 
 
 def attention_forward(q, k, v, lists: TileLists, sm_scale: float, want_rowmax: bool = False,
-                      status: Optional[torch.Tensor] = None):
+                      status: Optional[torch.Tensor] = None, rows=None, out=None):
     """Runs the forward kernel on prepared tile lists.  Returns (o, lse2, rowmax|None):
-    lse2 is the base-2 log-sum-exp of the logits scaled by sm_scale*log2(e)."""
+    lse2 is the base-2 log-sum-exp of the logits scaled by sm_scale*log2(e).
+    rows=(begin, end) restricts the call to that range of query-block rows of every head (the
+    other rows of the outputs are left untouched); out=(o, lse2) supplies the output tensors."""
     lib = _lib.load()
     B, H, N, D = q.shape
     q, k, v = _tma_ready(q), _tma_ready(k), _tma_ready(v)
-    o = torch.empty((B, H, N, D), dtype=q.dtype, device=q.device)
-    lse2 = torch.empty((B, H, N), dtype=torch.float32, device=q.device)
-    rowmax = torch.empty_like(lse2) if want_rowmax else None
+    o, lse2, rowmax = _fwd_outputs(q, out, want_rowmax)
     sb, sh = lists.list_strides(B, H)
+    r0, r1 = _row_range(rows, N // BLOCK)
     with _on_device(q.device):
         stream = _lib.stream_ptr(q.device)
-        counter = _work_counter(q.device, stream.value or 0)
-        _lib.check("bsa_attn_fwd", lib.bsa_attn_fwd(
+        state = _stream_state(q.device, stream.value or 0)
+        _lib.check("bsa_attn_fwd_rows", lib.bsa_attn_fwd_rows(
             _lib.ptr(q), _lib.strides4(q), _lib.ptr(k), _lib.strides4(k), _lib.ptr(v),
             _lib.strides4(v), _lib.ptr(o), _lib.strides4(o), _lib.ptr(lse2), _lib.ptr(rowmax),
             _lib.ptr(lists.row_ptr), _lib.ptr(lists.col_idx), sb, sh, float(sm_scale),
-            _lib.dtype_code(q.dtype), B, H, N, D, _lib.ptr(counter), _lib.ptr(status), stream))
+            _lib.dtype_code(q.dtype), B, H, N, D, r0, r1,
+            _lib.ptr(state.counter if state else None), _lib.ptr(status), stream))
     return o, lse2, rowmax
 
 
 def attention_forward_masked(q, k, v, block_mask: torch.Tensor, sm_scale: float,
-                             want_rowmax: bool = False, status: Optional[torch.Tensor] = None):
+                             want_rowmax: bool = False, status: Optional[torch.Tensor] = None,
+                             rows=None, out=None):
     """Forward straight from a block mask [..,nb,nb]: every CTA lists its own mask row, no tile
-    lists are built.  Returns (o, lse2, rowmax|None) like attention_forward."""
+    lists are built.  Returns (o, lse2, rowmax|None); rows and out as in attention_forward."""
     lib = _lib.load()
     B, H, N, D = q.shape
     m4 = _as_4d(_as_bytes(block_mask))
     q, k, v = _tma_ready(q), _tma_ready(k), _tma_ready(v)
-    o = torch.empty((B, H, N, D), dtype=q.dtype, device=q.device)
-    lse2 = torch.empty((B, H, N), dtype=torch.float32, device=q.device)
-    rowmax = torch.empty_like(lse2) if want_rowmax else None
+    o, lse2, rowmax = _fwd_outputs(q, out, want_rowmax)
+    r0, r1 = _row_range(rows, N // BLOCK)
     with _on_device(q.device):
         stream = _lib.stream_ptr(q.device)
-        counter = _work_counter(q.device, stream.value or 0)
-        _lib.check("bsa_attn_fwd_block_mask", lib.bsa_attn_fwd_block_mask(
+        state = _stream_state(q.device, stream.value or 0)
+        _lib.check("bsa_attn_fwd_block_mask_rows", lib.bsa_attn_fwd_block_mask_rows(
             _lib.ptr(q), _lib.strides4(q), _lib.ptr(k), _lib.strides4(k), _lib.ptr(v),
             _lib.strides4(v), _lib.ptr(o), _lib.strides4(o), _lib.ptr(lse2), _lib.ptr(rowmax),
             _lib.ptr(m4), _lib.strides4(m4), m4.shape[0], m4.shape[1], float(sm_scale),
-            _lib.dtype_code(q.dtype), B, H, N, D, _lib.ptr(counter), _lib.ptr(status), stream))
+            _lib.dtype_code(q.dtype), B, H, N, D, r0, r1,
+            _lib.ptr(state.counter if state else None), _lib.ptr(status), stream))
     return o, lse2, rowmax
 
 
@@ -296,7 +323,8 @@ def attention_backward(q, k, v, o, lse2, dout, lists: TileLists, sm_scale: float
     st = _lib.strides4(q)
     with _on_device(q.device):
         stream = _lib.stream_ptr(q.device)
-        counter = _work_counter(q.device, stream.value or 0)
+        state = _stream_state(q.device, stream.value or 0)
+        counter = state.counter if state else None
         _lib.check("bsa_attn_bwd_delta", lib.bsa_attn_bwd_delta(
             _lib.ptr(o), _lib.ptr(dout), st, _lib.ptr(delta), code, B, H, N, D, stream))
         _lib.check("bsa_attn_bwd_dkdv", lib.bsa_attn_bwd_dkdv(
@@ -310,6 +338,17 @@ def attention_backward(q, k, v, o, lse2, dout, lists: TileLists, sm_scale: float
             sb, sh, float(sm_scale), code, B, H, N, D, _lib.ptr(counter), _lib.ptr(status),
             stream))
     return dq, dk, dv
+
+
+def _op_status(device):
+    """The status word the public op hands to its kernels on the current stream of `device`, after
+    a look at what earlier calls left in it (no synchronisation)."""
+    with _on_device(device):
+        state = _stream_state(device, _lib.stream_ptr(device).value or 0)
+    if state is None:
+        return None
+    state.raise_if_reported()
+    return state.status
 
 
 class _attention(torch.autograd.Function):
@@ -332,8 +371,9 @@ class _attention(torch.autograd.Function):
         if not (q.dtype == k.dtype == v.dtype) or q.dtype not in (torch.float16, torch.bfloat16):
             raise TypeError("q, k, v must all be float16 or all bfloat16")
         block = _block_mask_for(mask, B, H, N, q.device)
+        status = _op_status(q.device)
         # the forward lists each mask row inside the kernel; only the backward needs lists as data
-        o, lse2, _ = attention_forward_masked(q, k, v, block, sm_scale)
+        o, lse2, _ = attention_forward_masked(q, k, v, block, sm_scale, status=status)
         if any(ctx.needs_input_grad[:3]):
             lists = build_tile_lists(block, want_csr=True, want_csc=True)
             ctx.save_for_backward(q, k, v, o, lse2, lists.row_ptr, lists.col_idx,
@@ -349,7 +389,8 @@ class _attention(torch.autograd.Function):
         q, k, v, o, lse2, rp, ci, cp, ri = ctx.saved_tensors
         Bm, Hm, nb = ctx.lists_shape
         lists = TileLists(Bm=Bm, Hm=Hm, nb=nb, row_ptr=rp, col_idx=ci, col_ptr=cp, row_idx=ri)
-        dq, dk, dv = attention_backward(q, k, v, o, lse2, do, lists, ctx.sm_scale)
+        dq, dk, dv = attention_backward(q, k, v, o, lse2, do, lists, ctx.sm_scale,
+                                        status=_op_status(q.device))
         return dq, dk, dv, None, None
 
 

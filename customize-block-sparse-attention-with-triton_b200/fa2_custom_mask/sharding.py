@@ -4,10 +4,15 @@ Every (batch, head) is independent (own q, k, v and mask slice), so the primary 
 rank a contiguous run of the flattened (b, h) index and nothing is exchanged on the data path.
 When there are fewer (b, h) units than ranks, the query-block rows of each head are split instead,
 balanced by listed-tile count, with that head's K and V replicated on every rank (forward only: a
-row split of the backward would need a dK/dV reduction).
+row split of the backward would need a dK/dV reduction).  The reference's forward grid is one
+program per listed (b, h, query block) row (fa2_custom_mask/fa2_custom_mask.py:69-70), so any
+subset of rows is a complete launch; the forward entry points take the row range as
+`rows=(begin, end)`.
 """
 from __future__ import annotations
 
+from bisect import bisect_right
+from itertools import accumulate
 from typing import List, Sequence, Tuple
 
 
@@ -22,21 +27,21 @@ def shard_heads(n_units: int, world_size: int, rank: int) -> Tuple[int, int]:
 
 def shard_rows_by_tiles(row_tiles: Sequence[int], world_size: int) -> List[Tuple[int, int]]:
     """Splits query-block rows 0..nb-1 into `world_size` contiguous [start, stop) ranges whose
-    listed-tile totals are as even as a contiguous split allows (greedy on the running total).
-    Boundaries are kept even so that a pair of query blocks never straddles two ranks."""
+    listed-tile totals are as even as a contiguous split allows: cut k is placed where the
+    running total is closest to k/world_size of the whole.  A range may be empty (more ranks than
+    rows, or all tiles in a few rows); its rank then has nothing to launch."""
+    if world_size <= 0:
+        raise ValueError("world_size must be positive")
     nb = len(row_tiles)
-    total = sum(row_tiles)
+    prefix = [0] + list(accumulate(int(t) for t in row_tiles))  # prefix[r] = tiles of rows < r
+    total = prefix[-1]
     bounds = [0]
-    acc = 0
-    r = 0
     for k in range(1, world_size):
         target = total * k / world_size
-        while r < nb and acc + row_tiles[r] / 2 <= target:
-            acc += row_tiles[r]
+        r = bisect_right(prefix, target) - 1          # prefix[r] <= target < prefix[r + 1]
+        if r < nb and prefix[r + 1] - target < target - prefix[r]:
             r += 1
-        cut = min(nb, r + (r % 2))
-        cut = max(cut, bounds[-1])
-        bounds.append(cut)
+        bounds.append(min(nb, max(r, bounds[-1])))
     bounds.append(nb)
     return [(bounds[i], bounds[i + 1]) for i in range(world_size)]
 

@@ -15,10 +15,7 @@
  * Vocabulary: a "block" is 64 consecutive tokens; nb = N/64 blocks per sequence; a "tile" is one
  * (query block m, key block n) pair that the block mask keeps.  The kernels walk row lists (per
  * query block its kept key blocks: forward, dQ) and column lists (per key block the query blocks
- * that keep it: dK/dV).  bsa_tile_lists_build can also emit lists over PAIRS of adjacent blocks:
- * the "pair list" of pair p holds, ascending, every block index j of the other axis that is kept
- * for block 2p or 2p+1, encoded as
- *     entry = (j << 2) | flags,   flags bit0: block 2p keeps j,  bit1: block 2p+1 keeps j.
+ * that keep it: dK/dV).
  */
 #ifndef BSATTN_H_
 #define BSATTN_H_
@@ -30,11 +27,12 @@
 extern "C" {
 #endif
 
-#define BSA_VERSION 100
+#define BSA_VERSION 200
 
 typedef enum bsa_status {
   BSA_OK = 0,
-  BSA_ERR_BAD_SHAPE = -1,      /* N not a multiple of 64, D != 64, non-positive sizes            */
+  BSA_ERR_BAD_SHAPE = -1,      /* N not a multiple of 64, D != 64, non-positive sizes, bad row range,
+                                  negative sm_scale                                               */
   BSA_ERR_BAD_DTYPE = -2,      /* dtype is neither BSA_F16 nor BSA_BF16                           */
   BSA_ERR_BAD_STRIDE = -3,     /* innermost stride != 1, or an outer stride not 16-byte aligned   */
   BSA_ERR_BAD_POINTER = -4,    /* null or misaligned pointer                                      */
@@ -74,10 +72,6 @@ typedef struct bsa_list_sizes {
   int64_t col_idx;    /* worst case B*H*nb*nb              */
   int64_t col_ptr;    /* B*H*nb + 1                        */
   int64_t row_idx;    /* worst case B*H*nb*nb              */
-  int64_t qpair_ptr;  /* B*H*ceil(nb/2) + 1                */
-  int64_t qpair_ent;  /* worst case B*H*ceil(nb/2)*nb      */
-  int64_t kpair_ptr;  /* B*H*ceil(nb/2) + 1                */
-  int64_t kpair_ent;  /* worst case B*H*ceil(nb/2)*nb      */
   int64_t groups;     /* worst case 5*B*H*nb               */
   int64_t meta;       /* 8                                 */
 } bsa_list_sizes;
@@ -92,22 +86,21 @@ int bsa_tile_list_sizes(int B, int H, int nb, bsa_list_sizes* out);
  *                     (forward and dQ kernels).
  *   col_ptr/row_idx : CSR of the transposed mask (per key block, query blocks ascending;
  *                     dK/dV kernel).
- *   qpair_ptr/qpair_ent : pair lists over query-block pairs (not read by any kernel here).
- *   kpair_ptr/kpair_ent : pair lists over key-block pairs (likewise).
  *   groups     : rows (b,h,m,start,len) of the non-empty rows only, in row order.
- *   meta       : int32[8] = {nnz, G, qpair entries, kpair entries, 0,0,0,0}.
+ *   meta       : int32[8] = {nnz, G, 0,0,0,0,0,0}.
  * Any (ptr,idx) pair, and groups, may be NULL to skip that product; meta is required.
  */
 int bsa_tile_lists_build(const uint8_t* block, const int64_t block_strides[4], int B, int H, int nb,
                          int32_t* row_ptr, int32_t* col_idx, int32_t* col_ptr, int32_t* row_idx,
-                         int32_t* qpair_ptr, int32_t* qpair_ent, int32_t* kpair_ptr,
-                         int32_t* kpair_ent, int32_t* groups, int32_t* meta, void* stream);
+                         int32_t* groups, int32_t* meta, void* stream);
 
 /*
  * Forward attention over the listed tiles; replaces the _attn_fwd launch
  * (fa2_custom_mask/fa2_custom_mask.py:77-87, kernel fa2_custom_mask/fa2_fwd.py:108-206).
  *   q,k,v,o : [B,H,N,64] fp16/bf16, element strides *_strides[4]; last stride 1, others multiples
  *             of 8 elements, base 16-byte aligned.
+ *   sm_scale: the factor on Q K^T; must not be negative (the kernel takes row maxima before
+ *             scaling).
  *   lse2    : out fp32 [B,H,N] contiguous: log2-sum-exp2 of the scaled logits
  *             (natural-log LSE = lse2 * ln 2); -inf for rows of query blocks with no listed tile.
  *   rowmax  : optional out fp32 [B,H,N] (may be NULL): running row maximum of the scaled logits in
@@ -122,9 +115,10 @@ int bsa_tile_lists_build(const uint8_t* block, const int64_t block_strides[4], i
  *             evens out rows of unequal length; without one every CTA walks a fixed stride of
  *             query blocks.  The word must hold 0 when the kernel starts and holds 0 again when it
  *             ends, so one zeroed word serves any number of calls that cannot overlap on the GPU
- *             (calls on one stream); calls that may overlap need a word each.  After a kernel that
- *             reported through `status`, zero the word again before reuse.
- *   status  : optional int32 device word (may be NULL); a non-zero value after the stream drains
+ *             (calls on one stream); calls that may overlap need a word each.  A CTA whose bounded
+ *             wait gave up still draws its remaining tickets, so the word returns to 0 then too.
+ *   status  : optional int32 word (may be NULL) in device memory or in pinned host memory that the
+ *             device can reach; a non-zero value after the stream drains
  *             means a bounded wait inside the kernel gave up (see bsa_check_status).
  */
 int bsa_attn_fwd(const void* q, const int64_t q_strides[4], const void* k,
@@ -149,6 +143,31 @@ int bsa_attn_fwd_block_mask(const void* q, const int64_t q_strides[4], const voi
                             const uint8_t* block, const int64_t block_strides[4], int Bm, int Hm,
                             float sm_scale, int dtype, int B, int H, int N, int D,
                             int32_t* work_counter, int32_t* status, void* stream);
+
+/*
+ * The two forward entry points restricted to the query-block rows [row_begin, row_end) of every
+ * (batch, head): rows of o, lse2 and rowmax outside the range are not touched.  The reference
+ * launches one program per listed (batch, head, query block) row
+ * (fa2_custom_mask/fa2_custom_mask.py:69-70), so any subset of its grid is a valid launch; this is
+ * the same freedom, used to split the rows of a head across GPUs when there are fewer (batch, head)
+ * units than GPUs (every GPU then holds all of that head's K and V).  An empty range returns
+ * BSA_OK without launching.  bsa_attn_fwd / bsa_attn_fwd_block_mask are these with the range
+ * [0, N/64).
+ */
+int bsa_attn_fwd_rows(const void* q, const int64_t q_strides[4], const void* k,
+                      const int64_t k_strides[4], const void* v, const int64_t v_strides[4], void* o,
+                      const int64_t o_strides[4], float* lse2, float* rowmax,
+                      const int32_t* row_ptr, const int32_t* col_idx, int list_b_stride,
+                      int list_h_stride, float sm_scale, int dtype, int B, int H, int N, int D,
+                      int row_begin, int row_end, int32_t* work_counter, int32_t* status,
+                      void* stream);
+int bsa_attn_fwd_block_mask_rows(const void* q, const int64_t q_strides[4], const void* k,
+                                 const int64_t k_strides[4], const void* v,
+                                 const int64_t v_strides[4], void* o, const int64_t o_strides[4],
+                                 float* lse2, float* rowmax, const uint8_t* block,
+                                 const int64_t block_strides[4], int Bm, int Hm, float sm_scale,
+                                 int dtype, int B, int H, int N, int D, int row_begin, int row_end,
+                                 int32_t* work_counter, int32_t* status, void* stream);
 
 /*
  * delta[b,h,i] = sum_d o[b,h,i,d] * do[b,h,i,d] in fp32; replaces _attn_bwd_preprocess
@@ -190,7 +209,8 @@ int bsa_attn_bwd_dq(const void* q, const void* k, const void* v, const void* dou
  * grid axes are laid out in the order (p0,p1,p2).
  *   in/out : [B,heads,T=F*Hh*W,D] with element strides `strides` (shared by in and out, as in the
  *            reference); elem_bytes is 1, 2, 4 or 8.
- *   orders : device int32 [heads,3].
+ *   orders : device int32 [heads,3].  A row that is not a permutation of (0,1,2) leaves that
+ *            head's rows of `out` unwritten (checked on the device, no error is reported).
  */
 int bsa_reorder(const void* in, void* out, const int64_t strides[4], const int32_t* orders, int B,
                 int heads, int T, int D, int F, int Hh, int W, int elem_bytes, void* stream);
@@ -228,12 +248,19 @@ int bsa_inv_reorder_strided(const void* in, const int64_t in_strides[4], void* o
  * image instead (BSA_STATIC_SCRATCH_INTS 32-bit words, held by every GPU that loads the library
  * until the process exits); the result equals bsa_tile_lists_build followed by bsa_attn_fwd.
  *   block : bytes, logical [Bm,Hm,nb,nb] with element strides block_strides[4]; Bm is 1 or B, Hm is
- *           1 or H.  All other arguments as in bsa_attn_fwd (rowmax and the status word are not
- *           offered here).
+ *           1 or H.  All other arguments as in bsa_attn_fwd.  rowmax, the work counter and the
+ *           status word are not offered here: the query blocks are handed out at a fixed stride
+ *           (a few percent slower than the counter on masks with rows of unequal length), and a
+ *           bounded wait that gave up is not reported.
  * Limit: 8 + Bm*Hm*nb + 1 + Bm*Hm*nb*nb <= BSA_STATIC_SCRATCH_INTS, else BSA_ERR_TOO_LARGE
  * (one shared mask up to N = 92,000; eight per-head masks up to N = 32,000).
- * The first call on each device looks up the array's device address; make that call outside any
- * stream capture.  The call makes no cudaMalloc/cudaFree and calls no allocating library routine.
+ * The first call on each device looks up the array's device address.  With CUDA's lazy module
+ * loading that is also the moment the driver loads the library's kernels onto the device and
+ * reserves the array's 8 MiB there, so make that first call (or call bsa_static_warmup) early:
+ * before the process hands the rest of the device memory to its own pool, and outside any stream
+ * capture.  After that, a call makes no cudaMalloc/cudaFree and calls no allocating library
+ * routine.  The looked-up address is remembered per device for the life of the process: a
+ * cudaDeviceReset invalidates it.
  * All calls on a device share the one array: two calls whose GPU work may overlap (different
  * streams, or different host threads) race on it and must be serialised by the caller.
  */
@@ -244,6 +271,12 @@ int bsa_attn_fwd_block_mask_static(const void* q, const int64_t q_strides[4], co
                                    float* lse2, const uint8_t* block,
                                    const int64_t block_strides[4], int Bm, int Hm, float sm_scale,
                                    int dtype, int B, int H, int N, int D, void* stream);
+
+/*
+ * Does only the first-call set-up of bsa_attn_fwd_block_mask_static on the current device (module
+ * load, address look-up) and enqueues nothing.  No reference counterpart.
+ */
+int bsa_static_warmup(void);
 
 /*
  * Synchronises `stream`, reads the device status word and returns BSA_OK, BSA_ERR_DEVICE_TIMEOUT

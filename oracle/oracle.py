@@ -94,11 +94,9 @@ def build_groups(mask) -> tuple:
 
 def tile_lists(mask) -> dict:
     """All list products of the library's tile-list builder, from a [B,H,nb,nb] block mask:
-    CSR (row_ptr, col_idx), transposed CSR (col_ptr, row_idx), and the pair lists whose entries
-    are (index << 2) | flags with flag bit0/bit1 = first/second block of the pair keeps it."""
+    CSR (row_ptr, col_idx), transposed CSR (col_ptr, row_idx), and the reference's groups."""
     m = np.asarray(mask).astype(bool)
     B, H, nb, _ = m.shape
-    npair = (nb + 1) // 2
     flat = m.reshape(B * H, nb, nb)
 
     def csr(mat):  # mat [BH, major, minor]
@@ -108,28 +106,13 @@ def tile_lists(mask) -> dict:
         idx = np.nonzero(mat.reshape(-1, mat.shape[-1]))[1].astype(np.int32)
         return ptr, idx
 
-    def pairs(mat):  # mat [BH, major, minor] -> pair lists over major
-        pad = np.zeros((mat.shape[0], 2 * npair, mat.shape[2]), dtype=np.int32)
-        pad[:, :nb] = mat
-        flags = pad[:, 0::2] | (pad[:, 1::2] << 1)  # [BH, npair, minor]
-        keep = flags != 0
-        counts = keep.sum(-1).reshape(-1)
-        ptr = np.zeros(counts.size + 1, dtype=np.int32)
-        np.cumsum(counts, out=ptr[1:])
-        rows, minor = np.nonzero(keep.reshape(-1, keep.shape[-1]))
-        ent = (minor.astype(np.int32) << 2) | flags.reshape(-1, flags.shape[-1])[rows, minor]
-        return ptr, ent.astype(np.int32)
-
     row_ptr, col_idx = csr(flat)
     col_ptr, row_idx = csr(flat.transpose(0, 2, 1))
-    qpair_ptr, qpair_ent = pairs(flat)
-    kpair_ptr, kpair_ent = pairs(flat.transpose(0, 2, 1))
     groups, n_list = build_groups(m)
     return dict(row_ptr=row_ptr, col_idx=col_idx, col_ptr=col_ptr, row_idx=row_idx,
-                qpair_ptr=qpair_ptr, qpair_ent=qpair_ent, kpair_ptr=kpair_ptr, kpair_ent=kpair_ent,
                 groups=groups, n_list=n_list,
-                meta=np.asarray([col_idx.size, 0 if groups is None else groups.shape[0],
-                                 qpair_ent.size, kpair_ent.size], dtype=np.int32))
+                meta=np.asarray([col_idx.size, 0 if groups is None else groups.shape[0]],
+                                dtype=np.int32))
 
 
 # --------------------------------------------------------------------------------------------

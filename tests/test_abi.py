@@ -26,7 +26,7 @@ def test_python_binding_covers_the_header(lib):
 
 
 def test_version_and_strerror(lib):
-    assert lib.bsa_version() == 100
+    assert lib.bsa_version() == 200
     assert lib.bsa_strerror(0) == b"ok"
     for code in range(-9, 0):
         assert lib.bsa_strerror(code) not in (b"", b"unknown status")
@@ -38,8 +38,8 @@ def test_list_sizes(lib):
     s = _lib.ListSizes()
     assert lib.bsa_tile_list_sizes(2, 3, 7, ctypes.byref(s)) == 0
     assert (s.row_ptr, s.col_idx) == (2 * 3 * 7 + 1, 2 * 3 * 7 * 7)
-    assert (s.qpair_ptr, s.qpair_ent) == (2 * 3 * 4 + 1, 2 * 3 * 4 * 7)
-    assert (s.kpair_ptr, s.kpair_ent, s.groups, s.meta) == (25, 168, 5 * 42, 8)
+    assert (s.col_ptr, s.row_idx) == (2 * 3 * 7 + 1, 2 * 3 * 7 * 7)
+    assert (s.groups, s.meta) == (5 * 42, 8)
     assert lib.bsa_tile_list_sizes(0, 1, 1, ctypes.byref(s)) == -1
 
 

@@ -92,6 +92,45 @@ def test_baseline_config5_shape_one_head(lib):
     assert (vc.grad[0, 0].float() - dv_ref).abs().max().item() <= G_TOL
 
 
+def test_baseline_config5_shape_two_by_two_heads(lib):
+    """B=2, H=2 of BASELINE config 5 (N=16384, block-causal, p=0.25, a different mask per head),
+    with q, k, v and dO stored as [B,N,H,D] and viewed as [B,H,N,D]: forward and gradients of
+    every (batch, head) against the fp32 arithmetic evaluated on the GPU in chunks."""
+    from fa2_custom_mask import flash_attention_custom_mask
+    B, H, N = 2, 2, 16384
+    g = torch.Generator(device="cuda").manual_seed(56)
+    q, k, v, do = (torch.randn(B, N, H, 64, device="cuda", generator=g).to(torch.bfloat16)
+                   .transpose(1, 2) for _ in range(4))
+    assert not q.is_contiguous()
+    mask = oracle.make_block_mask(B, H, N // 64, 0.25, seed=56, causal=True).cuda()
+    qc, kc, vc = (t.clone(memory_format=torch.preserve_format).requires_grad_(True)
+                  for t in (q, k, v))
+    o = flash_attention_custom_mask(qc, kc, vc, mask, 0.125)
+    o.backward(do)
+    for b in range(B):
+        for h in range(H):
+            qf, kf, vf, dof = (t[b, h].float() for t in (q, k, v, do))
+            dk_ref = torch.zeros_like(kf)
+            dv_ref = torch.zeros_like(vf)
+            worst_o = worst_dq = 0.0
+            for r0 in range(0, N, 2048):
+                r1 = r0 + 2048
+                dense = mask[b, h, r0 // 64:r1 // 64].repeat_interleave(64, 0).repeat_interleave(64, 1)
+                s = (qf[r0:r1] @ kf.T) * 0.125
+                p = torch.softmax(s.masked_fill(~dense, float("-inf")), -1)
+                oc = p @ vf
+                worst_o = max(worst_o, (o[b, h, r0:r1].float() - oc).abs().max().item())
+                dp = dof[r0:r1] @ vf.T
+                ds = p * (dp - (oc * dof[r0:r1]).sum(-1, keepdim=True))
+                worst_dq = max(worst_dq,
+                               (qc.grad[b, h, r0:r1].float() - 0.125 * ds @ kf).abs().max().item())
+                dk_ref += 0.125 * ds.T @ qf[r0:r1]
+                dv_ref += p.T @ dof[r0:r1]
+            assert worst_o <= 2e-2 and worst_dq <= G_TOL, (b, h, worst_o, worst_dq)
+            assert (kc.grad[b, h].float() - dk_ref).abs().max().item() <= G_TOL
+            assert (vc.grad[b, h].float() - dv_ref).abs().max().item() <= G_TOL
+
+
 @pytest.mark.parametrize("D", [16, 32])
 def test_small_head_dimensions_are_padded(lib, D):
     """The reference accepts D in {16, 32, 64, 128, 256} (fa2_custom_mask.py:58); 16 and 32 run on

@@ -11,27 +11,23 @@ pytestmark = pytest.mark.gpu
 
 def _lists_to_numpy(tl):
     meta = tl.meta.cpu().numpy()
-    nnz, G, nq, nk = (int(x) for x in meta[:4])
-    out = dict(meta=meta[:4])
+    nnz, G = (int(x) for x in meta[:2])
+    assert not meta[2:].any()
+    out = dict(meta=meta[:2])
     out["row_ptr"] = tl.row_ptr.cpu().numpy()
     out["col_ptr"] = tl.col_ptr.cpu().numpy()
-    out["qpair_ptr"] = tl.qpair_ptr.cpu().numpy()
-    out["kpair_ptr"] = tl.kpair_ptr.cpu().numpy()
     out["col_idx"] = tl.col_idx.cpu().numpy()[:nnz]
     out["row_idx"] = tl.row_idx.cpu().numpy()[:nnz]
-    out["qpair_ent"] = tl.qpair_ent.cpu().numpy()[:nq]
-    out["kpair_ent"] = tl.kpair_ent.cpu().numpy()[:nk]
     out["groups"] = tl.groups.cpu().numpy()[:5 * G].reshape(G, 5)
     return out
 
 
 def _check_lists(mask_cpu, lib):
     from fa2_custom_mask import build_tile_lists
-    tl = build_tile_lists(mask_cpu.cuda(), want_q=True, want_k=True, want_groups=True)
+    tl = build_tile_lists(mask_cpu.cuda(), want_groups=True)
     got = _lists_to_numpy(tl)
     ref = oracle.tile_lists(mask_cpu.numpy())
-    for key in ("meta", "row_ptr", "col_idx", "col_ptr", "row_idx", "qpair_ptr", "qpair_ent",
-                "kpair_ptr", "kpair_ent"):
+    for key in ("meta", "row_ptr", "col_idx", "col_ptr", "row_idx"):
         np.testing.assert_array_equal(got[key], ref[key], err_msg=key)
     if ref["groups"] is None:
         assert got["groups"].shape[0] == 0
@@ -73,11 +69,12 @@ def test_lists_on_broadcast_and_strided_masks(lib):
     np.testing.assert_array_equal(tl.row_ptr.cpu().numpy(), ref["row_ptr"])
     np.testing.assert_array_equal(tl.col_idx.cpu().numpy()[:ref["col_idx"].size], ref["col_idx"])
     sliced = oracle.make_block_mask(1, 2, 20, 0.4, seed=2).cuda()[:, :, 3:15, 5:17]  # non-contiguous
-    tl = build_tile_lists(sliced, want_csr=True, want_csc=True, want_k=True)
+    tl = build_tile_lists(sliced, want_csr=True, want_csc=True)
     ref = oracle.tile_lists(sliced.cpu().numpy())
     np.testing.assert_array_equal(tl.col_ptr.cpu().numpy(), ref["col_ptr"])
     np.testing.assert_array_equal(tl.row_idx.cpu().numpy()[:ref["row_idx"].size], ref["row_idx"])
-    np.testing.assert_array_equal(tl.kpair_ent.cpu().numpy()[:ref["kpair_ent"].size], ref["kpair_ent"])
+    np.testing.assert_array_equal(tl.row_ptr.cpu().numpy(), ref["row_ptr"])
+    np.testing.assert_array_equal(tl.col_idx.cpu().numpy()[:ref["col_idx"].size], ref["col_idx"])
 
 
 @pytest.mark.parametrize("B,H,N,p", [(1, 1, 64, 1.0), (2, 2, 320, 0.4), (1, 1, 1024, 0.1),

@@ -66,9 +66,19 @@ def test_shard_heads_partitions_exactly():
         spans = shard_rows_by_tiles(tiles, ws)
         assert spans[0][0] == 0 and spans[-1][1] == 274
         assert all(spans[i][1] == spans[i + 1][0] for i in range(ws - 1))
-        assert all(a % 2 == 0 for a, _ in spans)
         loads = [sum(tiles[a:b]) for a, b in spans]
-        assert max(loads) <= 1.25 * sum(tiles) / ws
+        assert max(loads) <= 1.05 * sum(tiles) / ws
+    # uneven rows: every row is counted once, for the rank that gets it
+    assert [sum([1, 9, 1, 1, 1, 1, 1, 1][a:b]) for a, b in
+            shard_rows_by_tiles([1, 9, 1, 1, 1, 1, 1, 1], 2)] == [10, 6]
+    loads = [sum(range(1, 17)[a:b]) for a, b in shard_rows_by_tiles(list(range(1, 17)), 4)]
+    assert loads == [36, 30, 39, 31] and sum(loads) == 136
+    # all tiles in one row, or more ranks than rows: empty ranges, still a partition
+    for tiles_, ws in (([10, 0, 0, 0], 4), ([3, 3], 5), ([0, 0, 0], 2), ([], 3)):
+        spans = shard_rows_by_tiles(tiles_, ws)
+        assert len(spans) == ws and spans[0][0] == 0 and spans[-1][1] == len(tiles_)
+        assert all(a <= b for a, b in spans)
+        assert all(spans[i][1] == spans[i + 1][0] for i in range(ws - 1))
     assert plan(1, 32, 8, 3)[0] == "heads"
     assert plan(1, 1, 8, 3, tiles)[0] == "rows"
 
@@ -109,3 +119,31 @@ def _rank_main(rank, world, port, B, H, nb):
 
 def test_head_sharding_two_ranks_gloo():
     mp.spawn(_rank_main, args=(2, _free_port(), 1, 3, 2), nprocs=2, join=True)
+
+
+def _rank_rows(rank, world, port, nb):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from fa2_custom_mask.sharding import plan
+        # one head, fewer (b, h) units than ranks: every rank holds all of K and V and computes
+        # its share of the query-block rows, balanced by listed tiles
+        q, k, v = oracle.make_qkv(1, 1, nb * 64, 64, seed=4)
+        mask = oracle.make_block_mask(1, 1, nb, 0.4, seed=4, causal=True)
+        kind, (r0, r1) = plan(1, 1, world, rank, mask[0, 0].sum(-1).tolist())
+        assert kind == "rows"
+        o_mine, _ = oracle.attn_forward(q[:, :, 64 * r0:64 * r1], k, v, mask[:, :, r0:r1], 0.125)
+        pieces = [None] * world
+        dist.all_gather_object(pieces, (r0, r1, o_mine))
+        if rank == 0:
+            full, _ = oracle.attn_forward(q, k, v, mask, 0.125)
+            spans = sorted((a, b) for a, b, _ in pieces)
+            assert spans[0][0] == 0 and spans[-1][1] == nb
+            got = torch.cat([p[2] for p in sorted(pieces, key=lambda p: p[0])], dim=2)
+            assert torch.allclose(got, full, atol=1e-6)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_row_sharding_two_ranks_gloo():
+    mp.spawn(_rank_rows, args=(2, _free_port(), 6), nprocs=2, join=True)

@@ -38,27 +38,14 @@ def test_tile_lists_consistent_with_groups(golden):
         np.testing.assert_array_equal(ref_groups[:, 3], tl["row_ptr"][rows])
         np.testing.assert_array_equal(ref_groups[:, 4], lens[rows])
         np.testing.assert_array_equal(ref_groups[:, 2], rows % nb)
-        # pair lists decode back to the mask, and so does the transposed CSR
-        rebuilt = np.zeros((B * H, nb, nb), dtype=bool)
-        npair = (nb + 1) // 2
-        for u in range(B * H * npair):
-            for e in tl["qpair_ent"][tl["qpair_ptr"][u]:tl["qpair_ptr"][u + 1]]:
-                n, f = e >> 2, e & 3
-                bh, p = divmod(u, npair)
-                if f & 1:
-                    rebuilt[bh, 2 * p, n] = True
-                if f & 2:
-                    rebuilt[bh, 2 * p + 1, n] = True
-        np.testing.assert_array_equal(rebuilt.reshape(mask.shape), mask)
+        # both CSR forms decode back to the mask
+        rebuilt = np.zeros((B * H * nb, nb), dtype=bool)
         rebuilt_t = np.zeros((B * H, nb, nb), dtype=bool)
-        for u in range(B * H * npair):
-            for e in tl["kpair_ent"][tl["kpair_ptr"][u]:tl["kpair_ptr"][u + 1]]:
-                m, f = e >> 2, e & 3
-                bh, p = divmod(u, npair)
-                if f & 1:
-                    rebuilt_t[bh, m, 2 * p] = True
-                if f & 2:
-                    rebuilt_t[bh, m, 2 * p + 1] = True
+        for r in range(B * H * nb):
+            rebuilt[r, tl["col_idx"][tl["row_ptr"][r]:tl["row_ptr"][r + 1]]] = True
+            bh, n = divmod(r, nb)
+            rebuilt_t[bh, tl["row_idx"][tl["col_ptr"][r]:tl["col_ptr"][r + 1]], n] = True
+        np.testing.assert_array_equal(rebuilt.reshape(mask.shape), mask)
         np.testing.assert_array_equal(rebuilt_t.reshape(mask.shape), mask)
 
 
