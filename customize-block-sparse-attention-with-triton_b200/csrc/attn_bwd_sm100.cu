@@ -194,7 +194,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
 
   if (warp == 8) {
     // =========================== TMA producer ===========================
-    const bool leader = elect_one();
     bool ok = true;
     bool terminal = p.ticket == nullptr;  // drew a ticket past the end (or draws none)
     int gs = 0, ni = 0;
@@ -230,37 +229,38 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
       // the block's own operands: the previous item's S/dP instructions must be complete
       if (ni >= 1) ok = mbar_wait_warp(smem_u32(&sm->stat_free), (ni - 1) & 1, abort_flag);
       if (!ok) break;
-      if (leader) {
+      // One lane per copy: a single thread can start a tile load only every couple of hundred
+      // cycles, which up to eight copies in a row would turn into the kernel's bound.
+      {
         const uint32_t bar = smem_u32(&sm->stat_full);
-        mbar_expect_tx(bar, 4 * kBwdTile);
-        tma_load_4d(smem_u32(sm->stat0[0]), &tm_stat0, bar, 0, it.blk * 64, it.h, it.b);
-        tma_load_4d(smem_u32(sm->stat0[1]), &tm_stat0, bar, 0, it.blk * 64, it.h, it.b);
-        tma_load_4d(smem_u32(sm->stat1[0]), &tm_stat1, bar, 0, it.blk * 64, it.h, it.b);
-        tma_load_4d(smem_u32(sm->stat1[1]), &tm_stat1, bar, 0, it.blk * 64, it.h, it.b);
+        if (lane == 0) mbar_expect_tx(bar, 4 * kBwdTile);
+        __syncwarp();
+        if (lane < 2)
+          tma_load_4d(smem_u32(sm->stat0[lane]), &tm_stat0, bar, 0, it.blk * 64, it.h, it.b);
+        else if (lane < 4)
+          tma_load_4d(smem_u32(sm->stat1[lane - 2]), &tm_stat1, bar, 0, it.blk * 64, it.h, it.b);
       }
       for (int j = 0; j < n_super; ++j, ++gs) {
         const int s = gs % kBwdStages;
         const int nt = min(2, it.n_tiles - 2 * j);
-        const int n0 = __ldg(it.ents + 2 * j);
-        const int n1 = nt == 2 ? __ldg(it.ents + 2 * j + 1) : 0;
+        const int tl = (lane >> 1) & 1;  // lanes 0, 1, 4, 5 serve tile a, lanes 2, 3, 6, 7 tile b
+        const int nj = tl < nt ? __ldg(it.ents + 2 * j + tl) : 0;
         ok = mbar_wait_warp(smem_u32(&sm->in_empty[s]), ((gs / kBwdStages) & 1) ^ 1, abort_flag);
         if (!ok) break;
-        if (leader) {
-          const uint32_t bar = smem_u32(&sm->in_full[s]);
-          mbar_expect_tx(bar, nt * (2 * kBwdTile + (kDKDV ? 512u : 0u)));
-          tma_load_4d(smem_u32(sm->str0[s][0]), &tm_str0, bar, 0, n0 * 64, it.h, it.b);
-          tma_load_4d(smem_u32(sm->str1[s][0]), &tm_str1, bar, 0, n0 * 64, it.h, it.b);
-          if constexpr (kDKDV) {
-            bulk_load_1d(smem_u32(sm->lse[s][0]), p.lse2 + it.vec_base + n0 * 64, 256, bar);
-            bulk_load_1d(smem_u32(sm->delta[s][0]), p.delta + it.vec_base + n0 * 64, 256, bar);
-          }
-          if (nt == 2) {
-            tma_load_4d(smem_u32(sm->str0[s][1]), &tm_str0, bar, 0, n1 * 64, it.h, it.b);
-            tma_load_4d(smem_u32(sm->str1[s][1]), &tm_str1, bar, 0, n1 * 64, it.h, it.b);
-            if constexpr (kDKDV) {
-              bulk_load_1d(smem_u32(sm->lse[s][1]), p.lse2 + it.vec_base + n1 * 64, 256, bar);
-              bulk_load_1d(smem_u32(sm->delta[s][1]), p.delta + it.vec_base + n1 * 64, 256, bar);
-            }
+        const uint32_t bar = smem_u32(&sm->in_full[s]);
+        if (lane == 0) mbar_expect_tx(bar, nt * (2 * kBwdTile + (kDKDV ? 512u : 0u)));
+        __syncwarp();
+        if (tl < nt) {
+          if (lane < 4) {
+            if (lane & 1)
+              tma_load_4d(smem_u32(sm->str1[s][tl]), &tm_str1, bar, 0, nj * 64, it.h, it.b);
+            else
+              tma_load_4d(smem_u32(sm->str0[s][tl]), &tm_str0, bar, 0, nj * 64, it.h, it.b);
+          } else if (kDKDV && lane < 8) {
+            if (lane & 1)
+              bulk_load_1d(smem_u32(sm->delta[s][tl]), p.delta + it.vec_base + nj * 64, 256, bar);
+            else
+              bulk_load_1d(smem_u32(sm->lse[s][tl]), p.lse2 + it.vec_base + nj * 64, 256, bar);
           }
         }
       }

@@ -15,27 +15,31 @@
 // 64..127 (and zeros to the others): eight M=128, N=128, K=16 MMAs per superstep, none of whose
 // 128 x 128 outputs is thrown away.
 //
-// Roles (15 warps); every role walks the same item sequence, so set-up of item i+1 and write-out
+// Roles (16 warps); every role walks the same item sequence, so set-up of item i+1 and write-out
 // of item i-1 overlap the arithmetic of item i:
 //   warp 8      : producer — draws the item, lists its key blocks (from the mask row, or copies the
-//                 CSR row), TMA-loads Q and only the listed K/V tiles: K into a 2-deep ring of
-//                 superstages (4 tiles, held until S is complete; loaded one superstep ahead of
-//                 V), V into a 3-deep one (held until P V is complete)
+//                 CSR row), TMA-loads Q and the listed K tiles into a 2-deep ring of superstages
+//                 (4 tiles, held until S is complete), one lane per tile
+//   warp 15     : V producer — TMA-loads the listed V tiles into a 3-deep ring (held until P V is
+//                 complete), one lane per tile.  Only listed tiles are ever loaded.
 //   warp 9      : S issuer and TMEM owner
-//   warp 10     : P V issuer — O[T] += P_t V_t for the tiles t of the superstep, T the softmax team
-//                 of the superstep.  P is read from TMEM, V is an MN-major shared-memory operand.
-//                 The lanes that do not own tile t hold zeros in t's P columns, so row r of an
-//                 accumulator only sums products of tiles a, c and row r+64 only of tiles b, d.
+//   warp 10     : P V issuer — O[T] += P_t V_t for the tiles t of the superstep: tiles a, b into the
+//                 accumulator of softmax team 0, tiles c, d into that of team 1.  P is read from
+//                 TMEM, V is an MN-major shared-memory operand.  The lanes that do not own tile t
+//                 hold zeros in t's P columns, so row r of an accumulator only sums products of
+//                 the tile owned by lanes 0..63 and row r+64 only of the other one.
 //   warps 0..7  : online softmax in two teams of four warps (team = warp / 4, TMEM lane quarter =
-//                 warp % 4).  Supersteps alternate between the teams; each team has its own
+//                 warp % 4).  Every warp works on every superstep: team 0 on tiles a, b (columns
+//                 0..63 of the slot), team 1 on tiles c, d (columns 64..127); each team has its own
 //                 accumulator and (m, l) per lane.  Three S slots (128 TMEM columns) rotate over
 //                 the supersteps; a slot is held from the S MMAs until the P V MMAs that read the
-//                 probabilities, which overwrite the logits in place, are complete.  A warp takes
-//                 the maximum of its lanes' logits (64 columns at a time), moves the lane's
-//                 reference maximum if need be (rescaling its accumulator rows), then exponentiates:
-//                 first the tile still in registers from the maximum pass, then the other one,
-//                 loaded a second time.  Lanes 0..63 put P_c, P_a into columns 64..127 and zeros
-//                 into 0..63; lanes 64..127 put P_b, P_d into columns 0..63 and zeros into 64..127.
+//                 probabilities, which overwrite the logits in place, are complete, so while one
+//                 slot is with the softmax warps the next already holds its logits and the
+//                 previous one is being multiplied with V.  A warp loads its tile's 64 logits,
+//                 takes the row maximum, moves the lane's reference maximum if need be (rescaling
+//                 its accumulator rows), exponentiates, and stores P (16-bit, 32 columns) over one
+//                 half of the tile's columns and zeros over the other half, where the other 64
+//                 lanes' P goes: tile t's P ends up in columns [32 t, +32) of the slot.
 //   warps 11..14: write-out — merge the four partial results (m, l, O) of every query row (teams x
 //                 lanes r / r+64), normalise, store O, LSE and the row maximum.
 // TMEM (512 columns): S/P slots 3 x 128, accumulators 2 x 64.
@@ -43,15 +47,14 @@
 // Numerics follow the reference's loop (fa2_custom_mask/fa2_fwd.py:150-196): logits scaled by
 // sm_scale*log2(e), exp2 domain, fp32 row sums of the fp32 probabilities, P rounded to the input
 // dtype before P V.  The running maximum is only advanced when it grew by more than 8 (a factor
-// 256), which leaves O = acc / l unchanged because both use the same reference maximum.  The
-// partial results are merged in the order (even supersteps, odd supersteps) of the item, whichever
-// team computed them, so results do not depend on which CTA computes an item.
+// 256), which leaves O = acc / l unchanged because both use the same reference maximum.  Which
+// partial result a tile goes into depends on its position in the row's list alone, so results do
+// not depend on which CTA computes an item.
 //
 // Every wait is bounded; a wait that gives up raises a CTA-wide flag, every role then falls
 // through its loops without touching barriers' data again, and TMEM is always released.  Every
 // barrier is waited on only by warps that see each of its phases, or that know the barrier to be
-// at most one phase behind (a parity wait cannot tell a phase from the one two before it): the
-// barriers of the S slots come in sets of six, the least common multiple of slots and teams.
+// at most one phase behind (a parity wait cannot tell a phase from the one two before it).
 #include <math.h>
 #include <string.h>
 
@@ -63,9 +66,9 @@ namespace bsa {
 constexpr int kKStages = 2;     // K superstages (4 tiles) in flight: held from load to S complete
 constexpr int kVStages = 3;     // V superstages (4 tiles) in flight: held from load to P V complete
 constexpr int kSlots = 3;       // S/P slots (128 TMEM columns): held from S issue to P V complete
-constexpr int kSets = 6;        // barrier sets of the slots: lcm(kSlots, 2 teams)
-constexpr int kFwdThreads = 480;
+constexpr int kFwdThreads = 512;
 constexpr int kSoftmaxWarps = 8, kProducerWarp = 8, kSWarp = 9, kPvWarp = 10;  // warps 11..14 write out
+constexpr int kVProducerWarp = 15;  // = the last warp
 constexpr uint32_t kTileBytes = 64 * 64 * 2;       // one Q, K or V tile
 constexpr uint32_t kFwdTmemCols = 512;
 // TMEM columns: slot r at 128 r; accumulator of softmax team T at 384 + 64 T.
@@ -94,9 +97,9 @@ struct FwdSmem {
   uint64_t k_empty[kKStages];                 // S of the superstep complete
   uint64_t v_full[kVStages];
   uint64_t v_empty[kVStages];                 // P V of the superstep complete
-  uint64_t s_full[kSets];                     // S of the superstep complete
-  uint64_t p_full[kSets];                     // the team's four warps stored P of the superstep
-  uint64_t pv_done[kSets];                    // P V of the superstep complete: slot free, O current
+  uint64_t s_full[kSlots];                    // S of the superstep complete
+  uint64_t p_full[kSlots][2];                 // by team: its four warps stored P of the superstep
+  uint64_t pv_done[kSlots];                   // P V of the superstep complete: slot free, O current
   uint64_t o_full[2];                         // last P V of the item done
   uint64_t stats_full[2];                     // softmax warps published (m, l) of the item
   uint64_t o_free[2];                         // write-out holds accumulators/stats/header in registers
@@ -154,17 +157,6 @@ __device__ __forceinline__ void exp_chunk(const uint32_t* sr, float c, float neg
   float a0, a1;
   unpack_f32x2(l01, a0, a1);
   l += a0 + a1;
-}
-
-// exp2 of the 64 logits of one tile held in sr; the probabilities go to 32 TMEM columns at p_addr.
-template <bool kBf16>
-__device__ __forceinline__ void exp_tile(const uint32_t* sr, float c, float neg_m, uint32_t p_addr,
-                                         float& l) {
-  uint32_t pk[16];
-  exp_chunk<kBf16>(sr, c, neg_m, pk, l);
-  tmem_st_32x32b_x16(p_addr, pk);
-  exp_chunk<kBf16>(sr + 32, c, neg_m, pk, l);
-  tmem_st_32x32b_x16(p_addr + 16, pk);
 }
 
 __device__ __forceinline__ float max3(float a, float b, float c) {
@@ -308,9 +300,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_init(smem_u32(&sm->v_full[s]), 1);
       mbar_init(smem_u32(&sm->v_empty[s]), 1);
     }
-    for (int s = 0; s < kSets; ++s) {
+    for (int s = 0; s < kSlots; ++s) {
       mbar_init(smem_u32(&sm->s_full[s]), 1);
-      mbar_init(smem_u32(&sm->p_full[s]), kSoftmaxWarps / 2);  // the four warps of one team
+      mbar_init(smem_u32(&sm->p_full[s][0]), kSoftmaxWarps / 2);
+      mbar_init(smem_u32(&sm->p_full[s][1]), kSoftmaxWarps / 2);
       mbar_init(smem_u32(&sm->pv_done[s]), 1);
     }
     mbar_init(smem_u32(&sm->order_full), 1);
@@ -343,14 +336,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
   if (warp == kProducerWarp) {
     // =========================== producer ===========================
-    const bool leader = elect_one();
     bool ok = true;
     bool terminal = p.ticket == nullptr;  // drew a ticket past the end (or draws none)
     int gs = 0;  // supersteps issued so far by this CTA (ring position)
     int qi = 0;  // non-empty items so far (Q buffer position)
-    for (int i = 0, w = blockIdx.x; ok; ++i) {
-      const int par = i & 1;
-      if (i > 0) {
+    int w = blockIdx.x;
+
+    // Draws item j (the first one is the CTA's own), lists its key blocks into the list buffer of
+    // j's parity and publishes them.  Returns the tile count, or -1 when there is no further item
+    // (published as well) or a wait gave up (ok = false).
+    auto set_up = [&](int j, FwdItem& it) -> int {
+      const int par = j & 1;
+      if (j > 0) {
         // next item: the following ticket when items are handed out dynamically, else a fixed stride
         if (p.ticket != nullptr) {
           int t = 0;
@@ -363,8 +360,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           t = __shfl_sync(0xffffffffu, t, 0);
           terminal = t >= n2;
           if (sorted && t < n2) {
-            if (i == 1) ok = mbar_wait_warp(smem_u32(&sm->order_full), 0, abort_flag);
-            if (!ok) break;
+            if (j == 1) ok = mbar_wait_warp(smem_u32(&sm->order_full), 0, abort_flag);
+            if (!ok) return -1;
             t = *const_cast<volatile int*>(&sm->order[t]);
           }
           w = stride + t;
@@ -372,18 +369,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           w += stride;
         }
       }
-      // the list buffer (and the tile count) of item i-2 must have been read by everyone
-      if (i >= 2)
-        ok = mbar_wait_warp_idle(smem_u32(&sm->o_free[par]), ((i - 2) >> 1) & 1, abort_flag, 128);
-      if (!ok) break;
+      // the list buffer (and the tile count) of item j-2 must have been read by everyone
+      if (j >= 2)
+        ok = mbar_wait_warp_idle(smem_u32(&sm->o_free[par]), ((j - 2) >> 1) & 1, abort_flag, 128);
+      if (!ok) return -1;
       if (w >= p.items) {
         if (lane == 0) {
           sm->item[par] = -1;
           mbar_arrive(smem_u32(&sm->list_full[par]));
         }
-        break;
+        return -1;
       }
-      const FwdItem it = fwd_item(w, p);
+      it = fwd_item(w, p);
       uint16_t* cols = sm->cols[par];
       int n_tiles = 0;
       if (p.block != nullptr) {
@@ -393,16 +390,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           // four independent loads per lane before the ballots
           bool keep[4];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int c = c0 + 32 * j + lane;
-            keep[j] = c < p.nb && mrow[c * p.ms3] != 0;
+          for (int jj = 0; jj < 4; ++jj) {
+            const int c = c0 + 32 * jj + lane;
+            keep[jj] = c < p.nb && mrow[c * p.ms3] != 0;
           }
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const unsigned bal = __ballot_sync(0xffffffffu, keep[j]);
-            if (keep[j])
+          for (int jj = 0; jj < 4; ++jj) {
+            const unsigned bal = __ballot_sync(0xffffffffu, keep[jj]);
+            if (keep[jj])
               cols[n_tiles + __popc(bal & ((1u << lane) - 1u))] =
-                  static_cast<uint16_t>(c0 + 32 * j + lane);
+                  static_cast<uint16_t>(c0 + 32 * jj + lane);
             n_tiles += __popc(bal);
           }
         }
@@ -411,8 +408,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             static_cast<int64_t>(it.b * p.list_b_stride + it.h * p.list_h_stride) * p.nb + it.mb;
         const int beg = __ldg(p.row_ptr + li);
         n_tiles = __ldg(p.row_ptr + li + 1) - beg;
-        for (int j = lane; j < n_tiles; j += 32)
-          cols[j] = static_cast<uint16_t>(__ldg(p.col_idx + beg + j));
+        for (int jj = lane; jj < n_tiles; jj += 32)
+          cols[jj] = static_cast<uint16_t>(__ldg(p.col_idx + beg + jj));
       }
       __syncwarp();
       if (lane == 0) {
@@ -420,49 +417,60 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         sm->item[par] = w;
         mbar_arrive(smem_u32(&sm->list_full[par]));  // release: count and list are visible
       }
+      return n_tiles;
+    };
+
+    // The set-up of item i+1 (a global atomic, the mask row, the list) runs while the last two K
+    // superstages of item i are still to be issued, i.e. at a moment when this warp would
+    // otherwise wait for a free K stage: its latencies stay off the tensor pipe's critical path.
+    // The other roles see the next item's header early as well.
+    FwdItem it, it_next;
+    int n_tiles = set_up(0, it);
+    for (int i = 0; ok && n_tiles >= 0; ++i) {
+      const uint16_t* cols = sm->cols[i & 1];
       const int n_super = (n_tiles + 3) >> 2;
-      if (n_super == 0) continue;
-      const int qpar = qi & 1;
-      if (qi >= 2) ok = mbar_wait_warp(smem_u32(&sm->q_free[qpar]), ((qi - 2) >> 1) & 1, abort_flag);
+      int n_next = -2;  // -2: item i+1 not set up yet
+      if (n_super > 0) {
+        const int qpar = qi & 1;
+        if (qi >= 2) ok = mbar_wait_warp(smem_u32(&sm->q_free[qpar]), ((qi - 2) >> 1) & 1, abort_flag);
+        if (!ok) break;
+        if (lane == 0) {
+          const uint32_t bar = smem_u32(&sm->q_full[qpar]);
+          mbar_expect_tx(bar, kTileBytes);
+          tma_load_4d(smem_u32(sm->qz[1 + 2 * qpar]), &tm_q, bar, 0, it.mb * 64, it.h, it.b);
+        }
+        ++qi;
+      }
+      // One lane per tile issues its load: a single thread can start a tile load only every couple
+      // of hundred cycles, which four loads in a row would turn into the kernel's bound.
+      for (int u = 0; u < n_super; ++u) {
+        if (n_next == -2 && u >= n_super - 2) {
+          // only if nothing in the set-up would have to wait now (the list buffer is free, the
+          // hand-out order is there): the K tiles below must not be held back by it
+          const int j = i + 1;
+          bool ready = j < 2 || mbar_try_wait(smem_u32(&sm->o_free[j & 1]), ((j - 2) >> 1) & 1);
+          if (j == 1 && sorted) ready = ready && mbar_try_wait(smem_u32(&sm->order_full), 0);
+          if (__all_sync(0xffffffffu, ready)) {
+            n_next = set_up(j, it_next);
+            if (!ok) break;
+          }
+        }
+        const int g = gs + u, ks = g % kKStages;
+        const int nt = min(4, n_tiles - 4 * u);
+        ok = mbar_wait_warp(smem_u32(&sm->k_empty[ks]), ((g / kKStages) & 1) ^ 1, abort_flag);
+        if (!ok) break;
+        const uint32_t bar = smem_u32(&sm->k_full[ks]);
+        if (lane == 0) mbar_expect_tx(bar, kTileBytes * nt);
+        __syncwarp();
+        if (lane < nt)  // shared-memory order a, c, b, d
+          tma_load_4d(smem_u32(sm->k[ks][((lane & 1) << 1) | (lane >> 1)]), &tm_k, bar, 0,
+                      static_cast<int>(cols[4 * u + lane]) * 64, it.h, it.b);
+      }
       if (!ok) break;
-      if (leader) {
-        const uint32_t bar = smem_u32(&sm->q_full[qpar]);
-        mbar_expect_tx(bar, kTileBytes);
-        tma_load_4d(smem_u32(sm->qz[1 + 2 * qpar]), &tm_q, bar, 0, it.mb * 64, it.h, it.b);
-      }
-      ++qi;
-      // K runs one superstep ahead of V: a K stage is free as soon as its S is complete, a V stage
-      // only when the superstep's P V is, and the wait for the latter must not hold back the K
-      // tiles that the next S needs.
-      for (int u = 0; u <= n_super && ok; ++u) {
-        if (u < n_super) {
-          const int g = gs + u, ks = g % kKStages;
-          const int nt = min(4, n_tiles - 4 * u);
-          ok = mbar_wait_warp(smem_u32(&sm->k_empty[ks]), ((g / kKStages) & 1) ^ 1, abort_flag);
-          if (!ok) break;
-          if (leader) {
-            const uint32_t bar = smem_u32(&sm->k_full[ks]);
-            mbar_expect_tx(bar, kTileBytes * nt);
-            for (int t = 0; t < nt; ++t)  // shared-memory order a, c, b, d
-              tma_load_4d(smem_u32(sm->k[ks][((t & 1) << 1) | (t >> 1)]), &tm_k, bar, 0,
-                          static_cast<int>(cols[4 * u + t]) * 64, it.h, it.b);
-          }
-        }
-        if (u > 0) {
-          const int g = gs + u - 1, vs = g % kVStages;
-          const int nt = min(4, n_tiles - 4 * (u - 1));
-          ok = mbar_wait_warp(smem_u32(&sm->v_empty[vs]), ((g / kVStages) & 1) ^ 1, abort_flag);
-          if (!ok) break;
-          if (leader) {
-            const uint32_t bar = smem_u32(&sm->v_full[vs]);
-            mbar_expect_tx(bar, kTileBytes * nt);
-            for (int t = 0; t < nt; ++t)
-              tma_load_4d(smem_u32(sm->v[vs][t]), &tm_v, bar, 0,
-                          static_cast<int>(cols[4 * (u - 1) + t]) * 64, it.h, it.b);
-          }
-        }
-      }
       gs += n_super;
+      if (n_next == -2) n_next = set_up(i + 1, it_next);
+      n_tiles = n_next;
+      it = it_next;
     }
     if (!ok) fwd_give_up(sm, p.status, kFailProducer);
     if (!terminal && lane == 0) {
@@ -474,6 +482,37 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if (t == p.items - 1) atomicExch(p.ticket, 0);
       } while (t < n2);
     }
+  } else if (warp == kVProducerWarp) {
+    // =========================== V producer ===========================
+    // Loads the V tiles of the listed key blocks, one lane per tile, from the list the producer
+    // published; a warp of its own, so that waiting for a free V stage (P V complete) never holds
+    // back the K tiles of a later superstep.
+    bool ok = true;
+    int gs = 0;
+    for (int i = 0; ok; ++i) {
+      const int par = i & 1;
+      ok = mbar_wait_warp(smem_u32(&sm->list_full[par]), (i >> 1) & 1, abort_flag);
+      if (!ok) break;
+      const int w = *const_cast<volatile int*>(&sm->item[par]);
+      if (w < 0) break;  // no more work
+      const FwdItem it = fwd_item(w, p);
+      const int n_tiles = *const_cast<volatile int*>(&sm->ntiles[par]);
+      const int n_super = (n_tiles + 3) >> 2;
+      const uint16_t* cols = sm->cols[par];
+      for (int u = 0; u < n_super; ++u, ++gs) {
+        const int vs = gs % kVStages;
+        const int nt = min(4, n_tiles - 4 * u);
+        ok = mbar_wait_warp(smem_u32(&sm->v_empty[vs]), ((gs / kVStages) & 1) ^ 1, abort_flag);
+        if (!ok) break;
+        const uint32_t bar = smem_u32(&sm->v_full[vs]);
+        if (lane == 0) mbar_expect_tx(bar, kTileBytes * nt);
+        __syncwarp();
+        if (lane < nt)
+          tma_load_4d(smem_u32(sm->v[vs][lane]), &tm_v, bar, 0,
+                      static_cast<int>(cols[4 * u + lane]) * 64, it.h, it.b);
+      }
+    }
+    if (!ok) fwd_give_up(sm, p.status, kFailProducer);
   } else if (warp == kSWarp) {
     // =========================== S issuer ===========================
     constexpr uint32_t idesc_n128 = umma_idesc(kBf16, 0, 0, 128, 128);
@@ -499,14 +538,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const uint64_t desc_bot = desc_qz + static_cast<uint64_t>(2 * qpar) * kTileDesc;
       const uint64_t desc_top = desc_bot + kTileDesc;
       for (int u = 0; u < n_super; ++u, ++gs) {
-        const int ks = gs % kKStages, slot = gs % kSlots, set = gs % kSets;
+        const int ks = gs % kKStages, slot = gs % kSlots;
         const int nt = min(4, n_tiles - 4 * u);
         ok = mbar_wait_warp(smem_u32(&sm->k_full[ks]), (gs / kKStages) & 1, abort_flag);
         if (!ok) break;
         // the slot's previous user, three supersteps ago, must have had its P V completed
         if (gs >= kSlots)
-          ok = mbar_wait_warp(smem_u32(&sm->pv_done[(gs - kSlots) % kSets]),
-                              ((gs - kSlots) / kSets) & 1, abort_flag);
+          ok = mbar_wait_warp(smem_u32(&sm->pv_done[slot]), ((gs - kSlots) / kSlots) & 1,
+                              abort_flag);
         if (!ok) break;
         tc_fence_after();
         if (leader) {
@@ -521,7 +560,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk) umma_ss(d, desc_bot + 2 * kk, desc_bd + 2 * kk, id_bd, 1);
           }
-          tc_commit(smem_u32(&sm->s_full[set]));
+          tc_commit(smem_u32(&sm->s_full[slot]));
           tc_commit(smem_u32(&sm->k_empty[ks]));
           if (u == n_super - 1) tc_commit(smem_u32(&sm->q_free[qpar]));  // Q buffer reusable
         }
@@ -553,30 +592,34 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         continue;
       }
       for (int u = 0; u < n_super; ++u, ++gs) {
-        const int vs = gs % kVStages, slot = gs % kSlots, set = gs % kSets;
-        const int team = gs & 1;
+        const int vs = gs % kVStages, slot = gs % kSlots;
         const int nt = min(4, n_tiles - 4 * u);
         ok = mbar_wait_warp(smem_u32(&sm->v_full[vs]), (gs / kVStages) & 1, abort_flag);
         if (!ok) break;
-        ok = mbar_wait_warp(smem_u32(&sm->p_full[set]), (gs / kSets) & 1, abort_flag);
-        if (!ok) break;
-        tc_fence_after();
-        if (leader) {
-          // A team's first superstep of an item (u = 0 or 1) starts its accumulator afresh.  Keys
-          // [16 kk, +16) of tile t sit 8 kk columns into the tile's P columns: a at 96, b at 0, c at
-          // 64, d at 32; the lanes that do not own the tile hold zeros there.
-          const uint32_t o_acc = tmem + kTmemO + 64 * team;
-          const uint32_t p_slot = tmem + 128 * slot;
-          for (int t = 0; t < nt; ++t) {
-            const uint32_t p_cols = p_slot + ((t & 1) ? 0u : 64u) + ((t >> 1) == (t & 1) ? 32u : 0u);
-            const uint64_t desc_v = desc_v0 + static_cast<uint64_t>((vs * 4 + t) * (kTileBytes >> 4));
+        // Tiles a, b go to the accumulator of team 0 as soon as that team has stored their P, tiles
+        // c, d to that of team 1; the first product of an item into an accumulator starts it
+        // afresh.  Keys [16 kk, +16) of tile t sit at column 32 t + 8 kk of the slot; the lanes
+        // that do not own the tile hold zeros there.
+        const uint32_t p_slot = tmem + 128 * slot;
+        for (int team = 0; team < 2 && ok; ++team) {
+          ok = mbar_wait_warp(smem_u32(&sm->p_full[slot][team]), (gs / kSlots) & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          if (leader) {
+            const uint32_t o_acc = tmem + kTmemO + 64 * team;
+            for (int t = 2 * team; t < min(nt, 2 * team + 2); ++t) {
+              const uint64_t desc_v = desc_v0 + static_cast<uint64_t>((vs * 4 + t) * (kTileBytes >> 4));
 #pragma unroll
-            for (int kk = 0; kk < 4; ++kk)
-              umma_ts(o_acc, p_cols + 8 * kk, desc_v + 128 * kk, idesc_pv,
-                      (u > 1) || (t > 0) || (kk > 0));
+              for (int kk = 0; kk < 4; ++kk)
+                umma_ts(o_acc, p_slot + 32 * t + 8 * kk, desc_v + 128 * kk, idesc_pv,
+                        (u > 0) || (t & 1) || (kk > 0));
+            }
           }
+        }
+        if (!ok) break;
+        if (leader) {
           tc_commit(smem_u32(&sm->v_empty[vs]));
-          tc_commit(smem_u32(&sm->pv_done[set]));
+          tc_commit(smem_u32(&sm->pv_done[slot]));
           if (u == n_super - 1) tc_commit(smem_u32(&sm->o_full[par]));
         }
       }
@@ -584,17 +627,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     if (!ok) fwd_give_up(sm, p.status, kFailMma);
   } else if (warp < kSoftmaxWarps) {
     // =========================== softmax ===========================
-    const int team = warp >> 2;       // supersteps alternate between the two teams of four warps
+    const int team = warp >> 2;       // team 0 takes tiles a, b of every superstep, team 1 tiles c, d
     const int quarter = warp & 3;     // TMEM lane quarter this warp may touch
     const int half = quarter >> 1;    // lanes 0..63 own tiles a, c of a superstep, 64..127 b, d
+    const int t_mine = 2 * team + half, t_other = 2 * team + (half ^ 1);
     const int lane_row = quarter * 32 + lane;  // TMEM lane
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
     const uint32_t o_addr = tmem + lane_base + kTmemO + 64 * team;
-    // Columns of a slot.  "Kept" tile: the one whose logits stay in registers after the maximum
-    // pass (c for lanes 0..63, b for lanes 64..127); its columns also take this half's P.  The
-    // other tile (a or d) is loaded a second time for its exponentials; its columns take zeros.
-    const uint32_t col_keep = half ? 0u : 64u;
-    const uint32_t col_re = col_keep ^ 64u;
+    // columns of a slot: the team's logits at [64 team, +64); this warp's P over the first or the
+    // second half of them, zeros over the other half (where the other lanes' P goes)
+    const uint32_t col_s = 64u * team;
+    const uint32_t col_p = col_s + 32u * half, col_z = col_s + 32u * (half ^ 1);
     const float c = p.scale_log2;
     bool ok = true;
     int g0 = 0;  // supersteps of all earlier items of this CTA
@@ -607,32 +650,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const int n_super = (n_tiles + 3) >> 2;
       float m_ref = -INFINITY, m_true = -INFINITY, l = 0.f;
 
-      for (int u = team ^ (g0 & 1); u < n_super; u += 2) {
+      for (int u = 0; u < n_super; ++u) {
         const int g = g0 + u;
-        const int set = g % kSets;
-        const uint32_t s_addr = tmem + lane_base + 128 * (g % kSlots);
+        const int slot = g % kSlots;
+        const uint32_t s_addr = tmem + lane_base + 128 * slot;
         const int nt = min(4, n_tiles - 4 * u);
-        const bool keep = half ? nt >= 2 : nt >= 3;
-        const bool re = half ? nt >= 4 : nt >= 1;
-        ok = mbar_wait_warp(smem_u32(&sm->s_full[set]), (g / kSets) & 1, abort_flag);
+        ok = mbar_wait_warp(smem_u32(&sm->s_full[slot]), (g / kSlots) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
-        if (keep || re) {
+        if (t_mine < nt) {
           uint32_t sr[64];
-          float mx = -INFINITY;
-          if (re) {
-            tmem_ld_32x32b_x32(s_addr + col_re, sr);
-            tmem_ld_32x32b_x32(s_addr + col_re + 32, sr + 32);
-            tc_wait_ld();
-            mx = fmaxf(max_chunk(sr), max_chunk(sr + 32));
-          }
-          if (keep) {
-            tmem_ld_32x32b_x32(s_addr + col_keep, sr);
-            tmem_ld_32x32b_x32(s_addr + col_keep + 32, sr + 32);
-            tc_wait_ld();
-            mx = max3(mx, max_chunk(sr), max_chunk(sr + 32));
-          }
-          const float zmax = mx * c;
+          tmem_ld_32x32b_x32(s_addr + col_s, sr);
+          tmem_ld_32x32b_x32(s_addr + col_s + 32, sr + 32);
+          tc_wait_ld();
+          const float zmax = fmaxf(max_chunk(sr), max_chunk(sr + 32)) * c;
           m_true = fmaxf(m_true, zmax);
           float alpha = 1.f;
           bool rescale = false;
@@ -645,8 +676,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             rescale = true;
           }
           if (__any_sync(0xffffffffu, rescale)) {
-            // this warp's O rows must hold the team's previous product (two supersteps ago) first
-            ok = mbar_wait_warp(smem_u32(&sm->pv_done[(g - 2) % kSets]), ((g - 2) / kSets) & 1,
+            // this warp's O rows must hold the team's previous product (the superstep before) first
+            ok = mbar_wait_warp(smem_u32(&sm->pv_done[(g - 1) % kSlots]), ((g - 1) / kSlots) & 1,
                                 abort_flag);
             if (!ok) break;
             tc_fence_after();
@@ -661,26 +692,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
               tmem_st_32x32b_x16(o_addr + 16 * part, orow);
             }
           }
-          const float neg_m = -m_ref;
-          if (keep) {
-            exp_tile<kBf16>(sr, c, neg_m, s_addr + col_keep, l);
-            if (re) {
-              tmem_ld_32x32b_x32(s_addr + col_re, sr);
-              tmem_ld_32x32b_x32(s_addr + col_re + 32, sr + 32);
-              tc_wait_ld();
-              exp_tile<kBf16>(sr, c, neg_m, s_addr + col_keep + 32, l);
-            }
-          } else {
-            exp_tile<kBf16>(sr, c, neg_m, s_addr + col_keep + 32, l);
-          }
+          uint32_t pk[16];
+          exp_chunk<kBf16>(sr, c, -m_ref, pk, l);
+          tmem_st_32x32b_x16(s_addr + col_p, pk);
+          exp_chunk<kBf16>(sr + 32, c, -m_ref, pk, l);
+          tmem_st_32x32b_x16(s_addr + col_p + 16, pk);
         }
-        // the other half's P columns: zeros in these lanes (the logits there are used up)
-        tmem_st_zero_32x32b_x32(s_addr + col_re);
-        tmem_st_zero_32x32b_x32(s_addr + col_re + 32);
+        // the other lanes' tile of this team reads these lanes too: zeros (the logits are used up)
+        if (t_other < nt) tmem_st_zero_32x32b_x32(s_addr + col_z);
         tc_wait_st();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&sm->p_full[set]));
+        if (lane == 0) mbar_arrive(smem_u32(&sm->p_full[slot][team]));
       }
       if (!ok) break;
 
@@ -697,7 +720,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     if (!ok) fwd_give_up(sm, p.status, kFailSoftmax);
   } else {
     // =========================== write-out ===========================
-    // Merges the four partial results of every query row (even / odd supersteps x lanes r / r+64).
+    // Merges the four partial results of every query row (teams 0 / 1 x lanes r / r+64).
     // A warp reads both accumulators of its own lanes from TMEM; lanes 64..127 hand their weighted
     // rows to lanes 0..63 through shared memory, 32 columns at a time.  All named barriers of an
     // iteration are always executed, also after a give-up, and the last one carries the give-up
@@ -709,7 +732,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const int r_blk = (quarter & 1) * 32 + lane;  // row of the query block
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
     bool ok = true;
-    int g0 = 0;
     for (int i = 0;; ++i) {
       const int par = i & 1;
       ok = mbar_wait_warp_idle(smem_u32(&sm->list_full[par]), (i >> 1) & 1, abort_flag, 256);
@@ -717,41 +739,40 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (w < 0) break;  // no more work: the same for all four warps
       const FwdItem it = fwd_item(w, p);
       const int n_tiles = ok ? *const_cast<volatile int*>(&sm->ntiles[par]) : 0;
-      const int n_super = (n_tiles + 3) >> 2;
-      // the team that took the item's even supersteps comes first in every sum
-      const int t_even = g0 & 1, t_odd = t_even ^ 1;
-      g0 += n_super;
-      if (ok) ok = mbar_wait_warp_idle(smem_u32(&sm->stats_full[par]), (i >> 1) & 1, abort_flag, 256);
-      if (ok) ok = mbar_wait_warp(smem_u32(&sm->o_full[par]), (i >> 1) & 1, abort_flag);
+      if (ok) ok = mbar_wait_warp_idle(smem_u32(&sm->stats_full[par]), (i >> 1) & 1, abort_flag, 128);
+      // The weights of the four partial results need the statistics only, which the softmax warps
+      // publish before the item's last P V is complete: work them out before waiting for that, so
+      // that the accumulators are given back (o_free) as soon as they have been read.
       float acc[64];
-      float m_all = -INFINITY, l_all = 0.f, mt = -INFINITY;
+      float m_all = -INFINITY, l_all = 0.f, mt = -INFINITY, w0 = 0.f, w1 = 0.f;
       if (ok) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const int tm = (j & 1) ? t_odd : t_even;
-          m_all = fmaxf(m_all, sm->mref[par][tm][r_blk + 64 * (j >> 1)]);
-          mt = fmaxf(mt, sm->mtrue[par][tm][r_blk + 64 * (j >> 1)]);
+          m_all = fmaxf(m_all, sm->mref[par][j & 1][r_blk + 64 * (j >> 1)]);
+          mt = fmaxf(mt, sm->mtrue[par][j & 1][r_blk + 64 * (j >> 1)]);
         }
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const int tm = (j & 1) ? t_odd : t_even;
-          const float mi = sm->mref[par][tm][r_blk + 64 * (j >> 1)];
+          const float mi = sm->mref[par][j & 1][r_blk + 64 * (j >> 1)];
           if (mi != -INFINITY)
-            l_all += ex2_approx(mi - m_all) * sm->lsum[par][tm][r_blk + 64 * (j >> 1)];
+            l_all += ex2_approx(mi - m_all) * sm->lsum[par][j & 1][r_blk + 64 * (j >> 1)];
         }
         const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
-        const float m0 = sm->mref[par][t_even][lane_row], m1 = sm->mref[par][t_odd][lane_row];
-        const float w0 = m0 == -INFINITY ? 0.f : ex2_approx(m0 - m_all) * inv;
-        const float w1 = m1 == -INFINITY ? 0.f : ex2_approx(m1 - m_all) * inv;
+        const float m0 = sm->mref[par][0][lane_row], m1 = sm->mref[par][1][lane_row];
+        w0 = m0 == -INFINITY ? 0.f : ex2_approx(m0 - m_all) * inv;
+        w1 = m1 == -INFINITY ? 0.f : ex2_approx(m1 - m_all) * inv;
+      }
+      if (ok) ok = mbar_wait_warp(smem_u32(&sm->o_full[par]), (i >> 1) & 1, abort_flag);
+      if (ok) {
         if (n_tiles > 0) {  // warp-uniform
-          // a team's accumulator holds this item's sums only if the team had a superstep in it
-          const bool live1 = n_super > 1;
+          // team 1's accumulator holds this item's sums only if the item has a tile c
+          const bool live1 = n_tiles > 2;
           tc_fence_after();
 #pragma unroll
           for (int part = 0; part < 4; ++part) {
             uint32_t a0[16], a1[16];
-            tmem_ld_32x32b_x16(tmem + lane_base + kTmemO + 64 * t_even + 16 * part, a0);
-            tmem_ld_32x32b_x16(tmem + lane_base + kTmemO + 64 * t_odd + 16 * part, a1);
+            tmem_ld_32x32b_x16(tmem + lane_base + kTmemO + 16 * part, a0);
+            tmem_ld_32x32b_x16(tmem + lane_base + kTmemO + 64 + 16 * part, a1);
             tc_wait_ld();
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
