@@ -598,12 +598,63 @@ def run_ours(args, rank, world, local_rank):
     print(json.dumps(line))
 
 
+PROFILE_CASES = ("fwd_headline", "fwd_dense", "fwd_bwd_causal", "mask_reduce", "tile_lists", "delta",
+                 "reorder")
+
+
+def run_profile_case(name, iters):
+    """One small case of one kernel family, launched `iters` times and nothing else: the command a
+    profiler capture is pointed at (a few hundred MB on the device at most, a handful of
+    launches).  Prints nothing that is a benchmark value."""
+    from fa2_custom_mask import (_lib, apply_head_wise_reorder, attention_backward,
+                                 attention_forward, attention_forward_masked, build_tile_lists,
+                                 reduce_dense_mask)
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    if name in ("fwd_headline", "fwd_dense"):
+        (q, k, v), m = device_problem(dev, 1, 1, N_CTX, DENSITY if name == "fwd_headline" else 1.0,
+                                      torch.float16, seed=3)
+        fn = lambda: attention_forward_masked(q, k, v, m, SM_SCALE)
+    elif name == "fwd_bwd_causal":
+        # BASELINE.json config 5 with 2 x 4 of its 2 x 16 heads
+        (q, k, v, do), m = device_problem(dev, 2, 4, 16384, 0.25, torch.bfloat16, seed=5, causal=True, n=4)
+        lists = build_tile_lists(m)
+        o, lse2, _ = attention_forward(q, k, v, lists, SM_SCALE)
+        fn = lambda: (attention_forward(q, k, v, lists, SM_SCALE),
+                      attention_backward(q, k, v, o, lse2, do, lists, SM_SCALE))
+    elif name == "mask_reduce":
+        dense = synth_block_mask(1, 1, N_CTX // 64, DENSITY, seed=1).to(dev)
+        dense = dense.repeat_interleave(64, dim=-2).repeat_interleave(64, dim=-1)   # 307 MB > L2
+        fn = lambda: reduce_dense_mask(dense)
+    elif name == "tile_lists":
+        m = synth_block_mask(1, 32, 500, DENSITY, seed=1).to(dev)                   # config 4 mask
+        fn = lambda: build_tile_lists(m, want_csr=True, want_csc=True)
+    elif name == "delta":
+        o, do = (torch.randn(2, 16, 16384, HEAD_DIM, device=dev).to(torch.bfloat16) for _ in range(2))
+        delta = torch.empty((2, 16, 16384), dtype=torch.float32, device=dev)
+        lib = _lib.load()
+        fn = lambda: lib.bsa_attn_bwd_delta(_lib.ptr(o), _lib.ptr(do), _lib.strides4(o), _lib.ptr(delta),
+                                            _lib.dtype_code(o.dtype), 2, 16, 16384, HEAD_DIM,
+                                            _lib.stream_ptr(dev))
+    else:
+        x = torch.randn(2, 48, 13 * 30 * 45, HEAD_DIM, device=dev, dtype=torch.float16)  # 216 MB > L2
+        orders = torch.tensor([[0, 1, 2], [0, 2, 1], [1, 0, 2], [1, 2, 0], [2, 0, 1], [2, 1, 0]],
+                              device=dev, dtype=torch.int32)[torch.arange(48, device=dev) % 6]
+        fn = lambda: apply_head_wise_reorder(x, orders, 13, 30, 45)
+    for _ in range(iters):
+        fn()
+    torch.cuda.synchronize(dev)
+    print(f"profile case {name}: {iters} iterations done")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--profile-case", default=None, choices=PROFILE_CASES,
+                    help="launch one small case --steps times and exit (for profiler captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
@@ -617,6 +668,9 @@ def main():
     import __graft_entry__
     if rank == 0:
         __graft_entry__.build()
+    if args.profile_case:
+        run_profile_case(args.profile_case, args.steps)
+        return
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))

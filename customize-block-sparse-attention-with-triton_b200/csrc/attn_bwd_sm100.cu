@@ -39,6 +39,7 @@ constexpr int kBwdStages = 4;
 constexpr int kBwdThreads = 352;
 constexpr uint32_t kBwdTile = 64 * 64 * 2;
 constexpr uint32_t kBwdTmemCols = 512;
+constexpr int kListIndex = BSA_LIST_PARTIAL_FLAG - 1;  // a list entry without its flag
 // TMEM columns: X0 = S (or S^T), X1 = dP (or dP^T), 128 each (tile a in columns 0..63 of lanes
 // 0..63, tile b in columns 64..127 of lanes 64..127); P and dS as 16-bit pairs, 32 columns per
 // tile; two fp32 accumulators.
@@ -67,6 +68,8 @@ struct BwdSmem {
 struct BwdParams {
   const int32_t* list_ptr;  // dK/dV: column lists (col_ptr/row_idx); dQ: row lists (row_ptr/col_idx)
   const int32_t* list_idx;
+  const uint8_t* dense;     // optional element-level mask for the tiles whose list entry is flagged
+  int64_t ds0, ds1, ds2;
   const float* lse2;
   const float* delta;
   void* out0;  // dV (dK/dV kernel only)
@@ -143,7 +146,9 @@ __device__ __forceinline__ BwdItem bwd_item(int w, const BwdParams& p) {
 // the other roles through shared memory; every role walks the same sequence and counts
 // supersteps (gs) and non-empty items (ni) the same way, so barrier phases follow from the counts.
 
-template <bool kBf16, bool kDKDV>
+// kElementMask: the instantiation that applies a dense mask inside the tiles whose list entries
+// are flagged; the plain one carries none of that code.
+template <bool kBf16, bool kDKDV, bool kElementMask>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
                 const __grid_constant__ CUtensorMap tm_stat1,
@@ -244,7 +249,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
         const int s = gs % kBwdStages;
         const int nt = min(2, it.n_tiles - 2 * j);
         const int tl = (lane >> 1) & 1;  // lanes 0, 1, 4, 5 serve tile a, lanes 2, 3, 6, 7 tile b
-        const int nj = tl < nt ? __ldg(it.ents + 2 * j + tl) : 0;
+        const int nj = tl < nt ? (__ldg(it.ents + 2 * j + tl) & kListIndex) : 0;
         ok = mbar_wait_warp(smem_u32(&sm->in_empty[s]), ((gs / kBwdStages) & 1) ^ 1, abort_flag);
         if (!ok) break;
         const uint32_t bar = smem_u32(&sm->in_full[s]);
@@ -417,13 +422,48 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
       }
       float my_lse = 0.f, my_delta = 0.f;
       if constexpr (!kDKDV) {
+        // (a row whose elements are all masked has LSE = -inf; every logit it meets is -inf too,
+        // and against a finite stand-in it exponentiates to 0 instead of NaN)
         my_lse = __ldg(p.lse2 + it.vec_base + row);
+        if constexpr (kElementMask) my_lse = fmaxf(my_lse, -3.0e38f);
         my_delta = __ldg(p.delta + it.vec_base + row);
       }
+      // element-level mask: where this lane's mask bytes of a tile start (dQ: its query row, 32
+      // consecutive keys; dK/dV: its key column, 32 consecutive query rows)
+      const uint8_t* mask_at = nullptr;
+      if constexpr (kElementMask)
+        mask_at = p.dense + it.b * p.ds0 + it.h * p.ds1 +
+                  (kDKDV ? static_cast<int64_t>(row) : static_cast<int64_t>(row) * p.ds2);
       for (int j = 0; ok && j < n_super; ++j, ++gs) {
         const int s = gs % kBwdStages;
         const int nt = min(2, it.n_tiles - 2 * j);
         const bool active = t_mine < nt;  // warp-uniform
+        // A tile with masked elements inside: fetch this lane's 32 mask bytes while S is on its way
+        uint32_t mw[8];
+        bool partial = false;
+        if (kElementMask && active) {
+          const int e = __ldg(it.ents + 2 * j + t_mine);
+          partial = (e & BSA_LIST_PARTIAL_FLAG) != 0;  // warp-uniform
+          if (partial) {
+            const int64_t other = static_cast<int64_t>((e & kListIndex) * 64 + 32 * ch);
+            if constexpr (kDKDV) {
+              const uint8_t* mp = mask_at + other * p.ds2;
+#pragma unroll
+              for (int q4 = 0; q4 < 8; ++q4) {
+                uint32_t w4 = 0;
+#pragma unroll
+                for (int bb = 0; bb < 4; ++bb)
+                  w4 |= static_cast<uint32_t>(__ldg(mp + (4 * q4 + bb) * p.ds2)) << (8 * bb);
+                mw[q4] = w4;
+              }
+            } else {
+              const uint4* mp = reinterpret_cast<const uint4*>(mask_at + other);
+              const uint4 a = __ldg(mp), b2 = __ldg(mp + 1);
+              mw[0] = a.x; mw[1] = a.y; mw[2] = a.z; mw[3] = a.w;
+              mw[4] = b2.x; mw[5] = b2.y; mw[6] = b2.z; mw[7] = b2.w;
+            }
+          }
+        }
         if constexpr (kDKDV) {
           // the LSE2/delta vectors of this stage arrive through the async proxy
           ok = mbar_wait_warp(smem_u32(&sm->in_full[s]), (gs / kBwdStages) & 1, abort_flag);
@@ -442,6 +482,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&sm->x_free));
+        if (partial) {
+          // masked elements: logit -inf, so P = 0 and with it dS = 0
+#pragma unroll
+          for (int q4 = 0; q4 < 8; ++q4) {
+            const uint32_t nz = __vcmpne4(mw[q4], 0u);
+#pragma unroll
+            for (int bb = 0; bb < 4; ++bb) {
+              const uint32_t keep = __byte_perm(nz, 0u, 0x1111u * bb);
+              xs[4 * q4 + bb] = (xs[4 * q4 + bb] & keep) | (0xff800000u & ~keep);
+            }
+          }
+        }
         uint32_t pk_p[16], pk_ds[16];
         if (active) {
           const float4* lse4 = reinterpret_cast<const float4*>(&sm->lse[s][t_mine][32 * ch]);
@@ -451,7 +503,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
             float l[4], d[4];
             if constexpr (kDKDV) {
               const float4 lv = lse4[i / 4], dv = del4[i / 4];
+              // (-inf = a query row with every element masked: see my_lse above)
               l[0] = lv.x; l[1] = lv.y; l[2] = lv.z; l[3] = lv.w;
+              if constexpr (kElementMask) {
+#pragma unroll
+                for (int t = 0; t < 4; ++t) l[t] = fmaxf(l[t], -3.0e38f);
+              }
               d[0] = dv.x; d[1] = dv.y; d[2] = dv.z; d[3] = dv.w;
             } else {
               l[0] = l[1] = l[2] = l[3] = my_lse;
@@ -562,8 +619,17 @@ static int launch_bwd(const void* q, const void* k, const void* v, const void* d
                       const int64_t strides[4], const float* lse2, const float* delta, void* out0,
                       void* out1, const int32_t* list_ptr, const int32_t* list_idx,
                       int list_b_stride, int list_h_stride, float sm_scale, int dtype, int B, int H,
-                      int N, int D, int32_t* ticket, int32_t* status, void* stream) {
+                      int N, int D, const uint8_t* dense, const int64_t* dense_strides,
+                      int32_t* ticket, int32_t* status, void* stream) {
   if (B <= 0 || H <= 0 || N <= 0 || (N % kBlock) != 0 || D != kHeadDim) return BSA_ERR_BAD_SHAPE;
+  if (dense != nullptr) {
+    if (!dense_strides || !is_aligned(dense, 16)) return BSA_ERR_BAD_POINTER;
+    if (dense_strides[3] != 1 || dense_strides[2] <= 0 || (dense_strides[2] % 16) != 0 ||
+        dense_strides[0] < 0 || dense_strides[1] < 0 || (dense_strides[0] % 16) != 0 ||
+        (dense_strides[1] % 16) != 0)
+      return BSA_ERR_BAD_STRIDE;
+    if (!(sm_scale > 0.f)) return BSA_ERR_BAD_SHAPE;
+  }
   if (dtype != BSA_F16 && dtype != BSA_BF16) return BSA_ERR_BAD_DTYPE;
   if (!lse2 || !delta || !list_ptr || !list_idx || !is_aligned(lse2, 16) || !is_aligned(delta, 16))
     return BSA_ERR_BAD_POINTER;
@@ -589,6 +655,10 @@ static int launch_bwd(const void* q, const void* k, const void* v, const void* d
   BwdParams prm;
   prm.list_ptr = list_ptr;
   prm.list_idx = list_idx;
+  prm.dense = dense;
+  prm.ds0 = dense ? dense_strides[0] : 0;
+  prm.ds1 = dense ? dense_strides[1] : 0;
+  prm.ds2 = dense ? dense_strides[2] : 0;
   prm.lse2 = lse2;
   prm.delta = delta;
   prm.out0 = out0;
@@ -609,7 +679,10 @@ static int launch_bwd(const void* q, const void* k, const void* v, const void* d
   prm.ticket = ticket;
 
   const size_t smem_bytes = sizeof(BwdSmem) + 1024;
-  auto kern = dtype == BSA_BF16 ? attn_bwd_kernel<true, kDKDV> : attn_bwd_kernel<false, kDKDV>;
+  auto kern = dense != nullptr ? (dtype == BSA_BF16 ? attn_bwd_kernel<true, kDKDV, true>
+                                                    : attn_bwd_kernel<false, kDKDV, true>)
+                               : (dtype == BSA_BF16 ? attn_bwd_kernel<true, kDKDV, false>
+                                                    : attn_bwd_kernel<false, kDKDV, false>);
   if ((rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes)) != BSA_OK)
     return rc;
   int sms = 0;
@@ -627,19 +700,21 @@ extern "C" int bsa_attn_bwd_dkdv(const void* q, const void* k, const void* v, co
                                  void* dk, void* dv, const int32_t* col_ptr,
                                  const int32_t* row_idx, int list_b_stride, int list_h_stride,
                                  float sm_scale, int dtype, int B, int H, int N, int D,
+                                 const uint8_t* dense, const int64_t dense_strides[4],
                                  int32_t* work_counter, int32_t* status, void* stream) {
   return bsa::launch_bwd<true>(q, k, v, dout, strides, lse2, delta, dv, dk, col_ptr, row_idx,
-                               list_b_stride, list_h_stride, sm_scale, dtype, B, H, N, D,
-                               work_counter, status, stream);
+                               list_b_stride, list_h_stride, sm_scale, dtype, B, H, N, D, dense,
+                               dense_strides, work_counter, status, stream);
 }
 
 extern "C" int bsa_attn_bwd_dq(const void* q, const void* k, const void* v, const void* dout,
                                const int64_t strides[4], const float* lse2, const float* delta,
                                void* dq, const int32_t* row_ptr, const int32_t* col_idx,
                                int list_b_stride, int list_h_stride, float sm_scale, int dtype,
-                               int B, int H, int N, int D, int32_t* work_counter, int32_t* status,
-                               void* stream) {
+                               int B, int H, int N, int D, const uint8_t* dense,
+                               const int64_t dense_strides[4], int32_t* work_counter,
+                               int32_t* status, void* stream) {
   return bsa::launch_bwd<false>(q, k, v, dout, strides, lse2, delta, nullptr, dq, row_ptr,
                                 col_idx, list_b_stride, list_h_stride, sm_scale, dtype, B, H, N,
-                                D, work_counter, status, stream);
+                                D, dense, dense_strides, work_counter, status, stream);
 }

@@ -76,13 +76,15 @@ constexpr uint32_t kTmemO = 384;
 constexpr float kRescaleThreshold = 8.0f;
 constexpr int kFwdMaxTiles = 2048;  // key blocks per row that a CTA can list (N <= 131072)
 constexpr int kMaxSorted = 320;     // items beyond the first round that a CTA can put in order
+constexpr uint16_t kColPartial = 0x8000;  // list entry in shared memory: the tile has masked elements
+constexpr uint16_t kColIndex = 0x7fff;
 
 struct FwdSmem {
   uint8_t qz[5][kTileBytes];                  // Z, Q (even items), Z, Q (odd items), Z
   uint8_t k[kKStages][4][kTileBytes];         // tiles in the order a, c, b, d
   uint8_t v[kVStages][4][kTileBytes];         // tiles in the order a, b, c, d
   float xfer[32][65];                         // write-out: lanes 64..127 hand over, [col][row]
-  uint16_t cols[2][kFwdMaxTiles];             // by item parity: the item's key-block list
+  uint16_t cols[2][kFwdMaxTiles];             // by item parity: the item's key-block list (| kColPartial)
   alignas(16) int cnt[kMaxSorted];            // sort keys (tile count, item) of the items beyond the first round
   int order[kMaxSorted];                      // those items, longest first
   int ntiles[2];
@@ -113,6 +115,8 @@ struct FwdParams {
   const int32_t* col_idx;
   const uint8_t* block;     // mask mode (block != nullptr): the producer lists the mask row
   int64_t ms0, ms1, ms2, ms3;
+  const uint8_t* dense;     // optional element-level mask for the tiles marked partial
+  int64_t ds0, ds1, ds2;
   void* o;
   int64_t o_sb, o_sh, o_sn;
   float* lse2;
@@ -265,7 +269,9 @@ __device__ __forceinline__ void fwd_build_order(FwdSmem* sm, const FwdParams& p,
   if (tid == 0) mbar_arrive(smem_u32(&sm->order_full));
 }
 
-template <bool kBf16>
+// kElementMask: the instantiation that applies a dense mask inside the tiles marked partial; the
+// plain one carries none of that code.
+template <bool kBf16, bool kElementMask>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const FwdParams p) {
@@ -388,18 +394,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const uint8_t* mrow = fwd_mask_row(it, p);
         for (int c0 = 0; c0 < p.nb; c0 += 128) {
           // four independent loads per lane before the ballots
-          bool keep[4];
+          int byte[4];
 #pragma unroll
           for (int jj = 0; jj < 4; ++jj) {
             const int c = c0 + 32 * jj + lane;
-            keep[jj] = c < p.nb && mrow[c * p.ms3] != 0;
+            byte[jj] = c < p.nb ? mrow[c * p.ms3] : 0;
           }
 #pragma unroll
           for (int jj = 0; jj < 4; ++jj) {
-            const unsigned bal = __ballot_sync(0xffffffffu, keep[jj]);
-            if (keep[jj])
-              cols[n_tiles + __popc(bal & ((1u << lane) - 1u))] =
-                  static_cast<uint16_t>(c0 + 32 * jj + lane);
+            const unsigned bal = __ballot_sync(0xffffffffu, byte[jj] != 0);
+            if (byte[jj] != 0)
+              cols[n_tiles + __popc(bal & ((1u << lane) - 1u))] = static_cast<uint16_t>(
+                  (c0 + 32 * jj + lane) | (kElementMask && byte[jj] == 2 ? kColPartial : 0));
             n_tiles += __popc(bal);
           }
         }
@@ -408,8 +414,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             static_cast<int64_t>(it.b * p.list_b_stride + it.h * p.list_h_stride) * p.nb + it.mb;
         const int beg = __ldg(p.row_ptr + li);
         n_tiles = __ldg(p.row_ptr + li + 1) - beg;
-        for (int jj = lane; jj < n_tiles; jj += 32)
-          cols[jj] = static_cast<uint16_t>(__ldg(p.col_idx + beg + jj));
+        for (int jj = lane; jj < n_tiles; jj += 32) {
+          const int e = __ldg(p.col_idx + beg + jj);
+          cols[jj] = static_cast<uint16_t>(
+              (e & kColIndex) | (kElementMask && (e & BSA_LIST_PARTIAL_FLAG) ? kColPartial : 0));
+        }
       }
       __syncwarp();
       if (lane == 0) {
@@ -464,7 +473,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         __syncwarp();
         if (lane < nt)  // shared-memory order a, c, b, d
           tma_load_4d(smem_u32(sm->k[ks][((lane & 1) << 1) | (lane >> 1)]), &tm_k, bar, 0,
-                      static_cast<int>(cols[4 * u + lane]) * 64, it.h, it.b);
+                      static_cast<int>(cols[4 * u + lane] & kColIndex) * 64, it.h, it.b);
       }
       if (!ok) break;
       gs += n_super;
@@ -509,7 +518,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         __syncwarp();
         if (lane < nt)
           tma_load_4d(smem_u32(sm->v[vs][lane]), &tm_v, bar, 0,
-                      static_cast<int>(cols[4 * u + lane]) * 64, it.h, it.b);
+                      static_cast<int>(cols[4 * u + lane] & kColIndex) * 64, it.h, it.b);
       }
     }
     if (!ok) fwd_give_up(sm, p.status, kFailProducer);
@@ -645,16 +654,35 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const int par = i & 1;
       ok = mbar_wait_warp(smem_u32(&sm->list_full[par]), (i >> 1) & 1, abort_flag);
       if (!ok) break;
-      if (*const_cast<volatile int*>(&sm->item[par]) < 0) break;  // no more work
+      const int w_item = *const_cast<volatile int*>(&sm->item[par]);
+      if (w_item < 0) break;  // no more work
       const int n_tiles = *const_cast<volatile int*>(&sm->ntiles[par]);
       const int n_super = (n_tiles + 3) >> 2;
+      const uint16_t* cols = sm->cols[par];
       float m_ref = -INFINITY, m_true = -INFINITY, l = 0.f;
+      // this lane's row of the element-level mask, if there is one
+      const uint8_t* mask_row = nullptr;
+      if constexpr (kElementMask) {
+        const FwdItem it = fwd_item(w_item, p);
+        mask_row = p.dense + it.b * p.ds0 + it.h * p.ds1 +
+                   static_cast<int64_t>(it.mb * 64 + (quarter & 1) * 32 + lane) * p.ds2;
+      }
 
       for (int u = 0; u < n_super; ++u) {
         const int g = g0 + u;
         const int slot = g % kSlots;
         const uint32_t s_addr = tmem + lane_base + 128 * slot;
         const int nt = min(4, n_tiles - 4 * u);
+        // A tile with masked elements inside: fetch this row's 64 mask bytes while S is on its way
+        uint16_t entry = 0;
+        if constexpr (kElementMask) entry = t_mine < nt ? cols[4 * u + t_mine] : 0;
+        const bool partial = kElementMask && (entry & kColPartial) != 0;  // warp-uniform
+        uint4 mw[4];
+        if (partial) {
+          const uint4* mp = reinterpret_cast<const uint4*>(mask_row + (entry & kColIndex) * 64);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) mw[j] = __ldg(mp + j);
+        }
         ok = mbar_wait_warp(smem_u32(&sm->s_full[slot]), (g / kSlots) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
@@ -663,6 +691,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           tmem_ld_32x32b_x32(s_addr + col_s, sr);
           tmem_ld_32x32b_x32(s_addr + col_s + 32, sr + 32);
           tc_wait_ld();
+          if (partial) {
+            // masked elements become -inf: they take no part in the maximum and exponentiate to 0
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint32_t w4[4] = {mw[j].x, mw[j].y, mw[j].z, mw[j].w};
+#pragma unroll
+              for (int q4 = 0; q4 < 4; ++q4) {
+                const uint32_t nz = __vcmpne4(w4[q4], 0u);  // 0xff in every byte that keeps its element
+#pragma unroll
+                for (int bb = 0; bb < 4; ++bb) {
+                  const uint32_t keep = __byte_perm(nz, 0u, 0x1111u * bb);
+                  const int i = 16 * j + 4 * q4 + bb;
+                  sr[i] = (sr[i] & keep) | (0xff800000u & ~keep);
+                }
+              }
+            }
+          }
           const float zmax = fmaxf(max_chunk(sr), max_chunk(sr + 32)) * c;
           m_true = fmaxf(m_true, zmax);
           float alpha = 1.f;
@@ -692,10 +737,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
               tmem_st_32x32b_x16(o_addr + 16 * part, orow);
             }
           }
+          // (a row with nothing kept so far has m_ref = -inf: its logits are all -inf, and with a
+          // zero in place of the maximum they exponentiate to 0 instead of NaN)
+          const float neg_m = (kElementMask && m_ref == -INFINITY) ? 0.f : -m_ref;
           uint32_t pk[16];
-          exp_chunk<kBf16>(sr, c, -m_ref, pk, l);
+          exp_chunk<kBf16>(sr, c, neg_m, pk, l);
           tmem_st_32x32b_x16(s_addr + col_p, pk);
-          exp_chunk<kBf16>(sr + 32, c, -m_ref, pk, l);
+          exp_chunk<kBf16>(sr + 32, c, neg_m, pk, l);
           tmem_st_32x32b_x16(s_addr + col_p + 16, pk);
         }
         // the other lanes' tile of this team reads these lanes too: zeros (the logits are used up)
@@ -884,11 +932,21 @@ static int launch_fwd(const void* q, const int64_t q_strides[4], const void* k,
                       const int32_t* row_ptr, const int32_t* col_idx, const uint8_t* block,
                       const int64_t* block_strides, int list_b_stride, int list_h_stride,
                       float sm_scale, int dtype, int B, int H, int N, int D, int row_begin,
-                      int row_end, int32_t* status, int32_t* ticket, void* stream) {
+                      int row_end, const uint8_t* dense, const int64_t* dense_strides,
+                      int32_t* status, int32_t* ticket, void* stream) {
   if (B <= 0 || H <= 0 || N <= 0 || (N % kBlock) != 0 || D != kHeadDim) return BSA_ERR_BAD_SHAPE;
   if (!(sm_scale >= 0.f)) return BSA_ERR_BAD_SHAPE;  // the row maximum is taken before scaling
   if (dtype != BSA_F16 && dtype != BSA_BF16) return BSA_ERR_BAD_DTYPE;
   if (!lse2 || (block == nullptr && (!row_ptr || !col_idx))) return BSA_ERR_BAD_POINTER;
+  if (dense != nullptr) {
+    // rows of 64 mask bytes are read as four 16-byte words; -inf times a zero scale would be NaN
+    if (!dense_strides || !is_aligned(dense, 16)) return BSA_ERR_BAD_POINTER;
+    if (dense_strides[3] != 1 || dense_strides[2] <= 0 || (dense_strides[2] % 16) != 0 ||
+        dense_strides[0] < 0 || dense_strides[1] < 0 || (dense_strides[0] % 16) != 0 ||
+        (dense_strides[1] % 16) != 0)
+      return BSA_ERR_BAD_STRIDE;
+    if (!(sm_scale > 0.f)) return BSA_ERR_BAD_SHAPE;
+  }
   int rc;
   if ((rc = check_qkv_operand(q, q_strides)) != BSA_OK) return rc;
   if ((rc = check_qkv_operand(k, k_strides)) != BSA_OK) return rc;
@@ -916,6 +974,10 @@ static int launch_fwd(const void* q, const int64_t q_strides[4], const void* k,
   prm.ms1 = block ? block_strides[1] : 0;
   prm.ms2 = block ? block_strides[2] : 0;
   prm.ms3 = block ? block_strides[3] : 0;
+  prm.dense = dense;
+  prm.ds0 = dense ? dense_strides[0] : 0;
+  prm.ds1 = dense ? dense_strides[1] : 0;
+  prm.ds2 = dense ? dense_strides[2] : 0;
   prm.o = o;
   prm.o_sb = o_strides[0];
   prm.o_sh = o_strides[1];
@@ -938,7 +1000,9 @@ static int launch_fwd(const void* q, const int64_t q_strides[4], const void* k,
   if ((rc = sm_count(&sms)) != BSA_OK) return rc;
 
   const size_t smem_bytes = sizeof(FwdSmem) + 1024;
-  auto kern = dtype == BSA_BF16 ? attn_fwd_kernel<true> : attn_fwd_kernel<false>;
+  auto kern = dense != nullptr
+                  ? (dtype == BSA_BF16 ? attn_fwd_kernel<true, true> : attn_fwd_kernel<false, true>)
+                  : (dtype == BSA_BF16 ? attn_fwd_kernel<true, false> : attn_fwd_kernel<false, false>);
   if ((rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes)) != BSA_OK)
     return rc;
   const dim3 grid(static_cast<unsigned>(prm.items < sms ? prm.items : sms));  // one CTA per SM
@@ -955,12 +1019,14 @@ extern "C" int bsa_attn_fwd_rows(const void* q, const int64_t q_strides[4], cons
                                  float* lse2, float* rowmax, const int32_t* row_ptr,
                                  const int32_t* col_idx, int list_b_stride, int list_h_stride,
                                  float sm_scale, int dtype, int B, int H, int N, int D,
-                                 int row_begin, int row_end, int32_t* work_counter,
+                                 int row_begin, int row_end, const uint8_t* dense,
+                                 const int64_t dense_strides[4], int32_t* work_counter,
                                  int32_t* status, void* stream) {
   if (!row_ptr || !col_idx) return BSA_ERR_BAD_POINTER;
   return bsa::launch_fwd(q, q_strides, k, k_strides, v, v_strides, o, o_strides, lse2, rowmax,
                          row_ptr, col_idx, nullptr, nullptr, list_b_stride, list_h_stride, sm_scale,
-                         dtype, B, H, N, D, row_begin, row_end, status, work_counter, stream);
+                         dtype, B, H, N, D, row_begin, row_end, dense, dense_strides, status,
+                         work_counter, stream);
 }
 
 extern "C" int bsa_attn_fwd(const void* q, const int64_t q_strides[4], const void* k,
@@ -971,7 +1037,7 @@ extern "C" int bsa_attn_fwd(const void* q, const int64_t q_strides[4], const voi
                             int D, int32_t* work_counter, int32_t* status, void* stream) {
   return bsa_attn_fwd_rows(q, q_strides, k, k_strides, v, v_strides, o, o_strides, lse2, rowmax,
                            row_ptr, col_idx, list_b_stride, list_h_stride, sm_scale, dtype, B, H,
-                           N, D, 0, N / bsa::kBlock, work_counter, status, stream);
+                           N, D, 0, N / bsa::kBlock, nullptr, nullptr, work_counter, status, stream);
 }
 
 extern "C" int bsa_attn_fwd_block_mask_rows(
@@ -979,15 +1045,16 @@ extern "C" int bsa_attn_fwd_block_mask_rows(
     const void* v, const int64_t v_strides[4], void* o, const int64_t o_strides[4], float* lse2,
     float* rowmax, const uint8_t* block, const int64_t block_strides[4], int Bm, int Hm,
     float sm_scale, int dtype, int B, int H, int N, int D, int row_begin, int row_end,
-    int32_t* work_counter, int32_t* status, void* stream) {
+    const uint8_t* dense, const int64_t dense_strides[4], int32_t* work_counter, int32_t* status,
+    void* stream) {
   if (!block || !block_strides) return BSA_ERR_BAD_POINTER;
   if ((Bm != 1 && Bm != B) || (Hm != 1 && Hm != H)) return BSA_ERR_BAD_SHAPE;
   for (int i = 0; i < 4; ++i)
     if (block_strides[i] < 0) return BSA_ERR_BAD_STRIDE;
   return bsa::launch_fwd(q, q_strides, k, k_strides, v, v_strides, o, o_strides, lse2, rowmax,
                          nullptr, nullptr, block, block_strides, Bm > 1 ? 1 : 0, Hm > 1 ? 1 : 0,
-                         sm_scale, dtype, B, H, N, D, row_begin, row_end, status, work_counter,
-                         stream);
+                         sm_scale, dtype, B, H, N, D, row_begin, row_end, dense, dense_strides,
+                         status, work_counter, stream);
 }
 
 extern "C" int bsa_attn_fwd_block_mask(const void* q, const int64_t q_strides[4], const void* k,
@@ -1000,6 +1067,6 @@ extern "C" int bsa_attn_fwd_block_mask(const void* q, const int64_t q_strides[4]
                                        void* stream) {
   return bsa_attn_fwd_block_mask_rows(q, q_strides, k, k_strides, v, v_strides, o, o_strides, lse2,
                                       rowmax, block, block_strides, Bm, Hm, sm_scale, dtype, B, H,
-                                      N, D, 0, N > 0 ? N / bsa::kBlock : 0, work_counter, status,
-                                      stream);
+                                      N, D, 0, N > 0 ? N / bsa::kBlock : 0, nullptr, nullptr,
+                                      work_counter, status, stream);
 }

@@ -24,7 +24,7 @@ __device__ __forceinline__ uint32_t zero_byte_bits(uint32_t x) {
 
 __global__ void __launch_bounds__(kReduceThreads)
 mask_reduce_kernel(const uint8_t* __restrict__ dense, int64_t sb, int64_t sh, int64_t sr, int H,
-                   int N, int nb, uint8_t* __restrict__ block, int32_t* partial) {
+                   int N, int nb, uint8_t* __restrict__ block, int32_t* partial, int mark_partial) {
   __shared__ uint32_t s_any[4][16];
   __shared__ uint32_t s_zero[4][16];
   const int bh = blockIdx.z;
@@ -63,7 +63,10 @@ mask_reduce_kernel(const uint8_t* __restrict__ dense, int64_t sb, int64_t sh, in
     const bool any = (s_any[0][t] | s_any[1][t] | s_any[2][t] | s_any[3][t]) != 0;
     const bool has_zero = (s_zero[0][t] | s_zero[1][t] | s_zero[2][t] | s_zero[3][t]) != 0;
     const bool in_range = cb < nb;
-    if (in_range) block[(static_cast<int64_t>(bh) * nb + rb) * nb + cb] = any ? 1 : 0;
+    // 0 = no element kept, 1 = kept; with mark_partial a kept tile that also has masked elements is 2
+    if (in_range)
+      block[(static_cast<int64_t>(bh) * nb + rb) * nb + cb] =
+          any ? ((mark_partial && has_zero) ? 2 : 1) : 0;
     if (partial) {
       const unsigned m = __ballot_sync(0x0000ffffu, in_range && any && has_zero);
       if (t == 0 && m) atomicAdd(partial, __popc(m));
@@ -92,8 +95,13 @@ struct ListArgs {
 
 constexpr int kListThreads = 256;
 
-__device__ __forceinline__ bool list_kept(const ListArgs& a, const uint8_t* head, int row, int col) {
-  return head[row * a.s2 + col * a.s3] != 0;
+// Mask byte of tile (row, col): 0 = not kept, 1 = kept, 2 = kept with masked elements inside (a
+// dense mask reduced with mark_partial).  A list entry of such a tile carries kPartialFlag.
+__device__ __forceinline__ int list_byte(const ListArgs& a, const uint8_t* head, int row, int col) {
+  return head[row * a.s2 + col * a.s3];
+}
+__device__ __forceinline__ int list_entry(int index, int byte) {
+  return byte == 2 ? (index | BSA_LIST_PARTIAL_FLAG) : index;
 }
 
 // Lists along the mask's rows: one warp per major unit, lanes sweep the minor axis 32 at a time.
@@ -110,10 +118,11 @@ __device__ __forceinline__ void lists_along_rows(const ListArgs& a) {
   if constexpr (kFill) out = a.ent[0] + a.ptr[0][unit];
   for (int c0 = 0; c0 < a.nb; c0 += 32) {
     const int c = c0 + lane;
-    const bool f = c < a.nb && list_kept(a, head, major, c);
+    const int byte = c < a.nb ? list_byte(a, head, major, c) : 0;
+    const bool f = byte != 0;
     const unsigned m = __ballot_sync(0xffffffffu, f);
     if constexpr (kFill) {
-      if (f) out[count + __popc(m & ((1u << lane) - 1u))] = c;
+      if (f) out[count + __popc(m & ((1u << lane) - 1u))] = list_entry(c, byte);
     }
     count += __popc(m);
   }
@@ -141,7 +150,7 @@ __device__ __forceinline__ void lists_along_cols(const ListArgs& a) {
   const int r1 = min(a.nb, r0 + chunk);
   int count = 0;
   if (valid)
-    for (int r = r0; r < r1; ++r) count += list_kept(a, head, r, major) ? 1 : 0;
+    for (int r = r0; r < r1; ++r) count += list_byte(a, head, r, major) != 0 ? 1 : 0;
   s_cnt[warp][lane] = count;
   __syncthreads();
   const int64_t unit = static_cast<int64_t>(bh) * a.nb + major;
@@ -158,8 +167,10 @@ __device__ __forceinline__ void lists_along_cols(const ListArgs& a) {
       for (int w = 0; w < warp; ++w) before += s_cnt[w][lane];
       int32_t* out = a.ent[1] + a.ptr[1][unit] + before;
       int k = 0;
-      for (int r = r0; r < r1; ++r)
-        if (list_kept(a, head, r, major)) out[k++] = r;
+      for (int r = r0; r < r1; ++r) {
+        const int byte = list_byte(a, head, r, major);
+        if (byte != 0) out[k++] = list_entry(r, byte);
+      }
     }
   }
 }
@@ -334,9 +345,10 @@ __global__ void __launch_bounds__(kScanThreads) lists_rows_small_kernel(const Li
     int count = 0;
     for (int c0 = 0; c0 < a.nb; c0 += 32) {
       const int c = c0 + lane;
-      const bool f = c < a.nb && row[c] != 0;
+      const int byte = c < a.nb ? row[c] : 0;
+      const bool f = byte != 0;
       const unsigned mk = __ballot_sync(0xffffffffu, f);
-      if (f) out[count + __popc(mk & ((1u << lane) - 1u))] = c;
+      if (f) out[count + __popc(mk & ((1u << lane) - 1u))] = list_entry(c, byte);
       count += __popc(mk);
     }
   }
@@ -345,7 +357,8 @@ __global__ void __launch_bounds__(kScanThreads) lists_rows_small_kernel(const Li
 }  // namespace bsa
 
 extern "C" int bsa_mask_reduce(const uint8_t* dense, const int64_t s[4], int B, int H, int N,
-                               uint8_t* block, int32_t* partial_tiles, void* stream) {
+                               uint8_t* block, int32_t* partial_tiles, int mark_partial,
+                               void* stream) {
   using namespace bsa;
   if (B <= 0 || H <= 0 || N <= 0 || (N % kBlock) != 0) return BSA_ERR_BAD_SHAPE;
   if (!dense || !block || !is_aligned(dense, 16)) return BSA_ERR_BAD_POINTER;
@@ -359,7 +372,7 @@ extern "C" int bsa_mask_reduce(const uint8_t* dense, const int64_t s[4], int B, 
     return BSA_ERR_CUDA;
   const dim3 grid((N + kReduceCols - 1) / kReduceCols, nb, B * H);
   mask_reduce_kernel<<<grid, kReduceThreads, 0, st>>>(dense, s[0], s[1], s[2], H, N, nb, block,
-                                                      partial_tiles);
+                                                      partial_tiles, mark_partial);
   return cudaGetLastError() == cudaSuccess ? BSA_OK : BSA_ERR_CUDA;
 }
 

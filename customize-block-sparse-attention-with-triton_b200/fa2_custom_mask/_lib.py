@@ -37,7 +37,7 @@ _s4 = ctypes.POINTER(ctypes.c_int64)
 SIGNATURES = {
     "bsa_version": [],
     "bsa_strerror": [_i],
-    "bsa_mask_reduce": [_vp, _s4, _i, _i, _i, _vp, _vp, _vp],
+    "bsa_mask_reduce": [_vp, _s4, _i, _i, _i, _vp, _vp, _i, _vp],
     "bsa_tile_list_sizes": [_i, _i, _i, ctypes.POINTER(ListSizes)],
     "bsa_tile_lists_build": [_vp, _s4, _i, _i, _i] + [_vp] * 6 + [_vp],
     "bsa_attn_fwd": [_vp, _s4, _vp, _s4, _vp, _s4, _vp, _s4, _vp, _vp, _vp, _vp, _i, _i, _f, _i,
@@ -45,14 +45,14 @@ SIGNATURES = {
     "bsa_attn_fwd_block_mask": [_vp, _s4, _vp, _s4, _vp, _s4, _vp, _s4, _vp, _vp, _vp, _s4, _i, _i,
                                 _f, _i, _i, _i, _i, _i, _vp, _vp, _vp],
     "bsa_attn_fwd_rows": [_vp, _s4, _vp, _s4, _vp, _s4, _vp, _s4, _vp, _vp, _vp, _vp, _i, _i, _f, _i,
-                          _i, _i, _i, _i, _i, _i, _vp, _vp, _vp],
+                          _i, _i, _i, _i, _i, _i, _vp, _s4, _vp, _vp, _vp],
     "bsa_attn_fwd_block_mask_rows": [_vp, _s4, _vp, _s4, _vp, _s4, _vp, _s4, _vp, _vp, _vp, _s4, _i,
-                                     _i, _f, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp],
+                                     _i, _f, _i, _i, _i, _i, _i, _i, _i, _vp, _s4, _vp, _vp, _vp],
     "bsa_attn_bwd_delta": [_vp, _vp, _s4, _vp, _i, _i, _i, _i, _i, _vp],
     "bsa_attn_bwd_dkdv": [_vp, _vp, _vp, _vp, _s4, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i,
-                          _i, _i, _i, _i, _vp, _vp, _vp],
+                          _i, _i, _i, _i, _vp, _s4, _vp, _vp, _vp],
     "bsa_attn_bwd_dq": [_vp, _vp, _vp, _vp, _s4, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i,
-                        _i, _i, _i, _i, _vp, _vp, _vp],
+                        _i, _i, _i, _i, _vp, _s4, _vp, _vp, _vp],
     "bsa_reorder": [_vp, _vp, _s4, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "bsa_inv_reorder": [_vp, _vp, _s4, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "bsa_reorder_strided": [_vp, _s4, _vp, _s4, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],

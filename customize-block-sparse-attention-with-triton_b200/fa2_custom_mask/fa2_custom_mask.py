@@ -7,8 +7,10 @@ fa2_custom_mask/fa2_custom_mask.py, with every device step done by libbsattn (sm
 Differences from the reference that a caller can observe (all are supersets):
   * `mask` may be the reference's block mask [B,H,N/64,N/64] (leading dims may be 1 or absent to
     share one mask across batch/heads) or a dense boolean mask whose last two dims are [N,N]; a
-    dense mask is reduced to blocks on the GPU (a block is kept when any element is kept, and a
-    kept block is attended in full, as in the reference kernel);
+    dense mask is reduced to blocks on the GPU (a block is listed when any of its elements is
+    kept) and applied element by element inside the blocks that are only partly kept, in forward
+    and backward: the result is the reference's naive masked softmax (kernel-test.py:37-40) for
+    ANY boolean mask, at the cost of the listed blocks only;
   * `mask=None` attends every block (the reference raises);
   * rows of query blocks with no kept block get O = 0 (the reference leaves them unwritten);
   * the backward is correct for any block mask and works for bf16 (the reference's is not);
@@ -81,12 +83,9 @@ def _as_4d(mask: torch.Tensor) -> torch.Tensor:
     return mask
 
 
-def reduce_dense_mask(dense: torch.Tensor, return_partial: bool = False):
-    """Dense boolean mask [..., N, N] -> block mask [..., N/64, N/64] (bool) on the GPU.
-
-    With return_partial=True also returns a one-element int32 device tensor counting the tiles
-    that are neither fully kept nor fully masked (reading it synchronises; the op never does)."""
-    lib = _lib.load()
+def _dense_ready(dense: torch.Tensor) -> torch.Tensor:
+    """A dense mask as bytes [Bm,Hm,N,N] that the kernels can read: unit inner stride, 16-byte
+    aligned base and outer strides (a copy is made otherwise)."""
     d4 = _as_4d(_as_bytes(dense))
     Bm, Hm, N, N2 = d4.shape
     if N != N2 or N % BLOCK:
@@ -95,16 +94,30 @@ def reduce_dense_mask(dense: torch.Tensor, return_partial: bool = False):
         raise ValueError("mask must be a CUDA tensor")
     ok = (d4.stride(3) == 1 and d4.stride(2) % 16 == 0 and d4.data_ptr() % 16 == 0
           and all(d4.stride(i) % 16 == 0 for i in (0, 1)))
-    if not ok:
-        d4 = d4.contiguous()
+    return d4 if ok else d4.contiguous()
+
+
+def reduce_dense_mask(dense: torch.Tensor, return_partial: bool = False,
+                      mark_partial: bool = False):
+    """Dense boolean mask [..., N, N] -> block mask [..., N/64, N/64] on the GPU.
+
+    By default the result is bool (a block is kept when any of its elements is).  With
+    mark_partial=True it is uint8: 0 = nothing kept, 1 = kept, 2 = kept but with masked elements
+    inside; the kernels apply the dense mask inside the blocks marked 2.
+    With return_partial=True also returns a one-element int32 device tensor counting the tiles
+    that are neither fully kept nor fully masked (reading it synchronises; the op never does)."""
+    lib = _lib.load()
+    d4 = _dense_ready(dense)
+    Bm, Hm, N, _ = d4.shape
     nb = N // BLOCK
     block = torch.empty((Bm, Hm, nb, nb), dtype=torch.uint8, device=d4.device)
     partial = torch.empty(1, dtype=torch.int32, device=d4.device) if return_partial else None
     with _on_device(d4.device):
         _lib.check("bsa_mask_reduce", lib.bsa_mask_reduce(
             _lib.ptr(d4), _lib.strides4(d4), Bm, Hm, N, _lib.ptr(block), _lib.ptr(partial),
-            _lib.stream_ptr(d4.device)))
-    out = block.view(torch.bool).reshape(*dense.shape[:-2], nb, nb)
+            1 if mark_partial else 0, _lib.stream_ptr(d4.device)))
+    out = block if mark_partial else block.view(torch.bool)
+    out = out.reshape(*dense.shape[:-2], nb, nb)
     return (out, partial) if return_partial else out
 
 
@@ -168,23 +181,41 @@ def _tma_ready(t: torch.Tensor) -> torch.Tensor:
 
 
 def _block_mask_for(mask, B, H, N, device):
-    """The op's `mask` argument as a block mask [..,nb,nb] on `device`."""
+    """The op's `mask` argument as (block mask [..,nb,nb], dense mask bytes [Bm,Hm,N,N] or None) on
+    `device`.  With a dense mask the block mask marks the partly kept blocks with 2."""
     nb = N // BLOCK
     if mask is None:
         mask = torch.ones((1, 1, nb, nb), dtype=torch.bool, device=device)
     if mask.device != device:
         raise ValueError("mask must live on the same device as q")
+    dense = None
     if mask.shape[-1] == nb and mask.shape[-2] == nb:
         block = mask
     elif mask.shape[-1] == N and mask.shape[-2] == N:
-        block = reduce_dense_mask(mask)
+        dense = _dense_ready(mask)
+        block = reduce_dense_mask(dense, mark_partial=True)
     else:
         raise ValueError(
             f"mask must be a block mask [..,{nb},{nb}] or a dense mask [..,{N},{N}], got {tuple(mask.shape)}")
     m4 = _as_4d(block)
     if m4.shape[0] not in (1, B) or m4.shape[1] not in (1, H):
         raise ValueError(f"mask leading dims {tuple(m4.shape[:2])} do not broadcast to ({B},{H})")
-    return block
+    return block, dense
+
+
+def _dense_args(dense, B, H):
+    """(pointer, strides) of an optional dense mask [Bm,Hm,N,N], broadcast axes with stride 0."""
+    if dense is None:
+        return None, None
+    d4 = _dense_ready(dense)
+    if d4.shape[0] not in (1, B) or d4.shape[1] not in (1, H):
+        raise ValueError(f"dense mask leading dims {tuple(d4.shape[:2])} do not broadcast to ({B},{H})")
+    st = list(d4.stride())
+    if d4.shape[0] == 1:
+        st[0] = 0
+    if d4.shape[1] == 1:
+        st[1] = 0
+    return d4, (ctypes.c_int64 * 4)(*st)
 
 
 def new_status_word(device) -> torch.Tensor:
@@ -261,17 +292,20 @@ def _fwd_outputs(q, out, want_rowmax):
 
 
 def attention_forward(q, k, v, lists: TileLists, sm_scale: float, want_rowmax: bool = False,
-                      status: Optional[torch.Tensor] = None, rows=None, out=None):
+                      status: Optional[torch.Tensor] = None, rows=None, out=None, dense=None):
     """Runs the forward kernel on prepared tile lists.  Returns (o, lse2, rowmax|None):
     lse2 is the base-2 log-sum-exp of the logits scaled by sm_scale*log2(e).
     rows=(begin, end) restricts the call to that range of query-block rows of every head (the
-    other rows of the outputs are left untouched); out=(o, lse2) supplies the output tensors."""
+    other rows of the outputs are left untouched); out=(o, lse2) supplies the output tensors;
+    dense = the element-level mask [..,N,N] the lists' block mask was reduced from with
+    mark_partial (applied inside the blocks marked 2)."""
     lib = _lib.load()
     B, H, N, D = q.shape
     q, k, v = _tma_ready(q), _tma_ready(k), _tma_ready(v)
     o, lse2, rowmax = _fwd_outputs(q, out, want_rowmax)
     sb, sh = lists.list_strides(B, H)
     r0, r1 = _row_range(rows, N // BLOCK)
+    d4, dst = _dense_args(dense, B, H)
     with _on_device(q.device):
         stream = _lib.stream_ptr(q.device)
         state = _stream_state(q.device, stream.value or 0)
@@ -279,22 +313,24 @@ def attention_forward(q, k, v, lists: TileLists, sm_scale: float, want_rowmax: b
             _lib.ptr(q), _lib.strides4(q), _lib.ptr(k), _lib.strides4(k), _lib.ptr(v),
             _lib.strides4(v), _lib.ptr(o), _lib.strides4(o), _lib.ptr(lse2), _lib.ptr(rowmax),
             _lib.ptr(lists.row_ptr), _lib.ptr(lists.col_idx), sb, sh, float(sm_scale),
-            _lib.dtype_code(q.dtype), B, H, N, D, r0, r1,
+            _lib.dtype_code(q.dtype), B, H, N, D, r0, r1, _lib.ptr(d4), dst,
             _lib.ptr(state.counter if state else None), _lib.ptr(status), stream))
     return o, lse2, rowmax
 
 
 def attention_forward_masked(q, k, v, block_mask: torch.Tensor, sm_scale: float,
                              want_rowmax: bool = False, status: Optional[torch.Tensor] = None,
-                             rows=None, out=None):
+                             rows=None, out=None, dense=None):
     """Forward straight from a block mask [..,nb,nb]: every CTA lists its own mask row, no tile
-    lists are built.  Returns (o, lse2, rowmax|None); rows and out as in attention_forward."""
+    lists are built.  Returns (o, lse2, rowmax|None); rows, out and dense as in
+    attention_forward."""
     lib = _lib.load()
     B, H, N, D = q.shape
     m4 = _as_4d(_as_bytes(block_mask))
     q, k, v = _tma_ready(q), _tma_ready(k), _tma_ready(v)
     o, lse2, rowmax = _fwd_outputs(q, out, want_rowmax)
     r0, r1 = _row_range(rows, N // BLOCK)
+    d4, dst = _dense_args(dense, B, H)
     with _on_device(q.device):
         stream = _lib.stream_ptr(q.device)
         state = _stream_state(q.device, stream.value or 0)
@@ -302,14 +338,15 @@ def attention_forward_masked(q, k, v, block_mask: torch.Tensor, sm_scale: float,
             _lib.ptr(q), _lib.strides4(q), _lib.ptr(k), _lib.strides4(k), _lib.ptr(v),
             _lib.strides4(v), _lib.ptr(o), _lib.strides4(o), _lib.ptr(lse2), _lib.ptr(rowmax),
             _lib.ptr(m4), _lib.strides4(m4), m4.shape[0], m4.shape[1], float(sm_scale),
-            _lib.dtype_code(q.dtype), B, H, N, D, r0, r1,
+            _lib.dtype_code(q.dtype), B, H, N, D, r0, r1, _lib.ptr(d4), dst,
             _lib.ptr(state.counter if state else None), _lib.ptr(status), stream))
     return o, lse2, rowmax
 
 
 def attention_backward(q, k, v, o, lse2, dout, lists: TileLists, sm_scale: float,
-                       status: Optional[torch.Tensor] = None):
-    """delta, then dK/dV over the column lists and dQ over the row lists."""
+                       status: Optional[torch.Tensor] = None, dense=None):
+    """delta, then dK/dV over the column lists and dQ over the row lists.  dense: the element-level
+    mask the forward was given, if any."""
     lib = _lib.load()
     B, H, N, D = q.shape
     # the three kernels take one stride set for q, k, v, o, dO and the gradients
@@ -321,6 +358,7 @@ def attention_backward(q, k, v, o, lse2, dout, lists: TileLists, sm_scale: float
     sb, sh = lists.list_strides(B, H)
     code = _lib.dtype_code(q.dtype)
     st = _lib.strides4(q)
+    d4, dst = _dense_args(dense, B, H)
     with _on_device(q.device):
         stream = _lib.stream_ptr(q.device)
         state = _stream_state(q.device, stream.value or 0)
@@ -330,13 +368,13 @@ def attention_backward(q, k, v, o, lse2, dout, lists: TileLists, sm_scale: float
         _lib.check("bsa_attn_bwd_dkdv", lib.bsa_attn_bwd_dkdv(
             _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(dout), st, _lib.ptr(lse2),
             _lib.ptr(delta), _lib.ptr(dk), _lib.ptr(dv), _lib.ptr(lists.col_ptr),
-            _lib.ptr(lists.row_idx), sb, sh, float(sm_scale), code, B, H, N, D,
+            _lib.ptr(lists.row_idx), sb, sh, float(sm_scale), code, B, H, N, D, _lib.ptr(d4), dst,
             _lib.ptr(counter), _lib.ptr(status), stream))
         _lib.check("bsa_attn_bwd_dq", lib.bsa_attn_bwd_dq(
             _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(dout), st, _lib.ptr(lse2),
             _lib.ptr(delta), _lib.ptr(dq), _lib.ptr(lists.row_ptr), _lib.ptr(lists.col_idx),
-            sb, sh, float(sm_scale), code, B, H, N, D, _lib.ptr(counter), _lib.ptr(status),
-            stream))
+            sb, sh, float(sm_scale), code, B, H, N, D, _lib.ptr(d4), dst, _lib.ptr(counter),
+            _lib.ptr(status), stream))
     return dq, dk, dv
 
 
@@ -370,15 +408,16 @@ class _attention(torch.autograd.Function):
             raise RuntimeError("flash_attention_custom_mask needs CUDA tensors; there is no CPU path")
         if not (q.dtype == k.dtype == v.dtype) or q.dtype not in (torch.float16, torch.bfloat16):
             raise TypeError("q, k, v must all be float16 or all bfloat16")
-        block = _block_mask_for(mask, B, H, N, q.device)
+        block, dense = _block_mask_for(mask, B, H, N, q.device)
         status = _op_status(q.device)
         # the forward lists each mask row inside the kernel; only the backward needs lists as data
-        o, lse2, _ = attention_forward_masked(q, k, v, block, sm_scale, status=status)
+        o, lse2, _ = attention_forward_masked(q, k, v, block, sm_scale, status=status, dense=dense)
         if any(ctx.needs_input_grad[:3]):
             lists = build_tile_lists(block, want_csr=True, want_csc=True)
             ctx.save_for_backward(q, k, v, o, lse2, lists.row_ptr, lists.col_idx,
                                   lists.col_ptr, lists.row_idx)
             ctx.lists_shape = (lists.Bm, lists.Hm, lists.nb)
+            ctx.dense = dense  # the caller's mask (or an aligned copy of it): not to be changed before backward
         ctx.sm_scale = sm_scale
         ctx.HEAD_DIM = D
         ctx.USE_MASK = mask is not None
@@ -390,7 +429,7 @@ class _attention(torch.autograd.Function):
         Bm, Hm, nb = ctx.lists_shape
         lists = TileLists(Bm=Bm, Hm=Hm, nb=nb, row_ptr=rp, col_idx=ci, col_ptr=cp, row_idx=ri)
         dq, dk, dv = attention_backward(q, k, v, o, lse2, do, lists, ctx.sm_scale,
-                                        status=_op_status(q.device))
+                                        status=_op_status(q.device), dense=ctx.dense)
         return dq, dk, dv, None, None
 
 

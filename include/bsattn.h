@@ -29,6 +29,10 @@ extern "C" {
 
 #define BSA_VERSION 200
 
+/* Tile-list entries (col_idx, row_idx) are block indices; an entry of a tile that is kept but has
+ * masked elements inside (mask byte 2, see bsa_mask_reduce) also carries this flag. */
+#define BSA_LIST_PARTIAL_FLAG (1 << 30)
+
 typedef enum bsa_status {
   BSA_OK = 0,
   BSA_ERR_BAD_SHAPE = -1,      /* N not a multiple of 64, D != 64, non-positive sizes, bad row range,
@@ -59,12 +63,17 @@ const char* bsa_strerror(int status);
  *   dense    : bytes (0 = masked, non-zero = kept), logical shape [B,H,N,N], element strides
  *              dense_strides[4] (0 allowed for broadcast over b/h); last stride must be 1, the
  *              row stride and base address multiples of 16.
- *   block    : out, contiguous [B,H,nb,nb] bytes (0/1).
+ *   block    : out, contiguous [B,H,nb,nb] bytes: 0 = no element kept, 1 = kept.  With
+ *              mark_partial != 0 a tile that is kept but also has masked elements gets 2, which
+ *              the list builder and the forward/backward kernels understand: given the dense
+ *              mask as well, they apply it element by element inside those tiles (the in-tile
+ *              mask the reference sketches in fa2_custom_mask/fa2_fwd.py:57-75 and its naive
+ *              check applies, kernel-test.py:37-40).
  *   partial_tiles : optional out (may be NULL), one int32 that the call first zeroes and then
  *              increments once per tile that is neither all-kept nor all-masked.
  */
 int bsa_mask_reduce(const uint8_t* dense, const int64_t dense_strides[4], int B, int H, int N,
-                    uint8_t* block, int32_t* partial_tiles, void* stream);
+                    uint8_t* block, int32_t* partial_tiles, int mark_partial, void* stream);
 
 /* Number of int32 elements the caller must provide for each output of bsa_tile_lists_build. */
 typedef struct bsa_list_sizes {
@@ -81,7 +90,9 @@ int bsa_tile_list_sizes(int B, int H, int nb, bsa_list_sizes* out);
  * Block mask -> tile lists, all built on the device with no host synchronisation.
  * Replaces build_groups_from_block_mask (fa2_custom_mask/fa2_custom_mask.py:15-38), whose
  * outputs are reproduced bit-exactly:  n_list == col_idx[0:nnz]  and  groups == groups[0:G].
- *   block      : bytes, logical [B,H,nb,nb], element strides block_strides[4] (0 = broadcast).
+ *   block      : bytes (0, 1 or 2, see bsa_mask_reduce), logical [B,H,nb,nb], element strides
+ *                block_strides[4] (0 = broadcast).  Entries of tiles with byte 2 carry
+ *                BSA_LIST_PARTIAL_FLAG; a mask of zeros and ones gives the reference's lists.
  *   row_ptr/col_idx : CSR over rows r=(b*H+h)*nb+m, empty rows kept, columns ascending
  *                     (forward and dQ kernels).
  *   col_ptr/row_idx : CSR of the transposed mask (per key block, query blocks ascending;
@@ -145,21 +156,29 @@ int bsa_attn_fwd_block_mask(const void* q, const int64_t q_strides[4], const voi
                             int32_t* work_counter, int32_t* status, void* stream);
 
 /*
- * The two forward entry points restricted to the query-block rows [row_begin, row_end) of every
- * (batch, head): rows of o, lse2 and rowmax outside the range are not touched.  The reference
- * launches one program per listed (batch, head, query block) row
- * (fa2_custom_mask/fa2_custom_mask.py:69-70), so any subset of its grid is a valid launch; this is
- * the same freedom, used to split the rows of a head across GPUs when there are fewer (batch, head)
- * units than GPUs (every GPU then holds all of that head's K and V).  An empty range returns
- * BSA_OK without launching.  bsa_attn_fwd / bsa_attn_fwd_block_mask are these with the range
- * [0, N/64).
+ * The two forward entry points in their general form.
+ *   row_begin, row_end : only the query-block rows [row_begin, row_end) of every (batch, head) are
+ *           computed; rows of o, lse2 and rowmax outside the range are not touched.  The reference
+ *           launches one program per listed (batch, head, query block) row
+ *           (fa2_custom_mask/fa2_custom_mask.py:69-70), so any subset of its grid is a valid
+ *           launch; this is the same freedom, used to split the rows of a head across GPUs when
+ *           there are fewer (batch, head) units than GPUs (every GPU then holds all of that
+ *           head's K and V).  An empty range returns BSA_OK without launching.
+ *   dense, dense_strides : optional (may be NULL) element-level mask, bytes, logical [B,H,N,N]
+ *           with element strides dense_strides[4] (0 for a broadcast axis; last stride 1, base and
+ *           the other strides multiples of 16).  Tiles marked 2 in `block` (flagged in the lists)
+ *           then keep only the elements whose byte is non-zero; rows without any kept element
+ *           get o = 0 and lse2 = -inf.  Without it every listed tile is attended in full, as in
+ *           the reference kernel.
+ * bsa_attn_fwd / bsa_attn_fwd_block_mask are these with the range [0, N/64) and no dense mask.
  */
 int bsa_attn_fwd_rows(const void* q, const int64_t q_strides[4], const void* k,
                       const int64_t k_strides[4], const void* v, const int64_t v_strides[4], void* o,
                       const int64_t o_strides[4], float* lse2, float* rowmax,
                       const int32_t* row_ptr, const int32_t* col_idx, int list_b_stride,
                       int list_h_stride, float sm_scale, int dtype, int B, int H, int N, int D,
-                      int row_begin, int row_end, int32_t* work_counter, int32_t* status,
+                      int row_begin, int row_end, const uint8_t* dense,
+                      const int64_t dense_strides[4], int32_t* work_counter, int32_t* status,
                       void* stream);
 int bsa_attn_fwd_block_mask_rows(const void* q, const int64_t q_strides[4], const void* k,
                                  const int64_t k_strides[4], const void* v,
@@ -167,6 +186,7 @@ int bsa_attn_fwd_block_mask_rows(const void* q, const int64_t q_strides[4], cons
                                  float* lse2, float* rowmax, const uint8_t* block,
                                  const int64_t block_strides[4], int Bm, int Hm, float sm_scale,
                                  int dtype, int B, int H, int N, int D, int row_begin, int row_end,
+                                 const uint8_t* dense, const int64_t dense_strides[4],
                                  int32_t* work_counter, int32_t* status, void* stream);
 
 /*
@@ -185,12 +205,15 @@ int bsa_attn_bwd_delta(const void* o, const void* dout, const int64_t o_strides[
  * block the query blocks that list it), addressed like the row lists of bsa_attn_fwd.  Key blocks
  * that no query block lists get dk = dv = 0.  work_counter: as in bsa_attn_fwd (both backward
  * kernels are persistent too; the same zeroed word can serve all calls of one stream).
+ * dense, dense_strides: the optional element-level mask of bsa_attn_fwd_rows (NULL = none), applied
+ * inside the tiles whose list entries carry BSA_LIST_PARTIAL_FLAG; pass what the forward was given.
  */
 int bsa_attn_bwd_dkdv(const void* q, const void* k, const void* v, const void* dout,
                       const int64_t strides[4], const float* lse2, const float* delta, void* dk,
                       void* dv, const int32_t* col_ptr, const int32_t* row_idx,
                       int list_b_stride, int list_h_stride, float sm_scale, int dtype, int B, int H,
-                      int N, int D, int32_t* work_counter, int32_t* status, void* stream);
+                      int N, int D, const uint8_t* dense, const int64_t dense_strides[4],
+                      int32_t* work_counter, int32_t* status, void* stream);
 
 /*
  * dQ over the row lists (row_ptr/col_idx, as in bsa_attn_fwd); replaces _attn_bwd_dq
@@ -200,7 +223,8 @@ int bsa_attn_bwd_dq(const void* q, const void* k, const void* v, const void* dou
                     const int64_t strides[4], const float* lse2, const float* delta, void* dq,
                     const int32_t* row_ptr, const int32_t* col_idx, int list_b_stride,
                     int list_h_stride, float sm_scale, int dtype, int B, int H, int N, int D,
-                    int32_t* work_counter, int32_t* status, void* stream);
+                    const uint8_t* dense, const int64_t dense_strides[4], int32_t* work_counter,
+                    int32_t* status, void* stream);
 
 /*
  * Head-wise token reorder; replaces reorder_kernel (fa2_custom_mask/permute.py:5-58, launched from

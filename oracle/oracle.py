@@ -118,13 +118,15 @@ def tile_lists(mask) -> dict:
 # --------------------------------------------------------------------------------------------
 # attention, naive form (kernel-test.py:37-40) — the numeric oracle at every size
 # --------------------------------------------------------------------------------------------
-def attn_forward(q, k, v, block_mask, sm_scale):
-    """fp32 masked softmax attention exactly as kernel-test.py:37-40 computes it.
+def attn_forward_dense(q, k, v, dense_mask, sm_scale):
+    """fp32 masked softmax attention exactly as kernel-test.py:37-40 computes it, for an
+    element-level boolean mask [.., N, N] (the reference's naive path masks per element; its kernel
+    only knows whole blocks, fa2_custom_mask/fa2_fwd.py:57-75 shows the in-tile mask it intended).
     Returns (O, LSE) with LSE = logsumexp of the scaled, masked logits (natural log).
-    Rows of query blocks without any kept block give O = 0 and LSE = -inf (the reference's naive
-    path gives NaN there; its kernel leaves those rows unwritten)."""
+    Rows without any kept element give O = 0 and LSE = -inf (the reference's naive path gives NaN
+    there; its kernel leaves rows of empty query blocks unwritten)."""
     qf, kf, vf = q.float(), k.float(), v.float()
-    dense = expand_block_mask(block_mask.to(torch.bool))
+    dense = dense_mask.to(torch.bool)
     s = torch.matmul(qf, kf.transpose(-2, -1)) * sm_scale
     s = s.masked_fill(~dense, float("-inf"))
     lse = torch.logsumexp(s, dim=-1)
@@ -134,12 +136,17 @@ def attn_forward(q, k, v, block_mask, sm_scale):
     return o, lse
 
 
-def attn_forward_backward(q, k, v, block_mask, sm_scale, dout):
+def attn_forward(q, k, v, block_mask, sm_scale):
+    """attn_forward_dense for a 64x64 block mask [.., nb, nb] (expanded as kernel-test.py:18)."""
+    return attn_forward_dense(q, k, v, expand_block_mask(block_mask.to(torch.bool)), sm_scale)
+
+
+def attn_forward_backward_dense(q, k, v, dense_mask, sm_scale, dout):
     """O, LSE and (dQ, dK, dV) by torch autograd through the fp32 naive form above."""
     qf = q.detach().float().requires_grad_(True)
     kf = k.detach().float().requires_grad_(True)
     vf = v.detach().float().requires_grad_(True)
-    dense = expand_block_mask(block_mask.to(torch.bool))
+    dense = dense_mask.to(torch.bool)
     s = torch.matmul(qf, kf.transpose(-2, -1)) * sm_scale
     s = s.masked_fill(~dense, float("-inf"))
     lse = torch.logsumexp(s, dim=-1)
@@ -148,6 +155,12 @@ def attn_forward_backward(q, k, v, block_mask, sm_scale, dout):
     o = torch.matmul(p, vf)
     o.backward(dout.float())
     return o.detach(), lse.detach(), qf.grad, kf.grad, vf.grad
+
+
+def attn_forward_backward(q, k, v, block_mask, sm_scale, dout):
+    """attn_forward_backward_dense for a 64x64 block mask."""
+    return attn_forward_backward_dense(q, k, v, expand_block_mask(block_mask.to(torch.bool)),
+                                       sm_scale, dout)
 
 
 def naive_cpu_forward(q, k, v, dense_mask, sm_scale):

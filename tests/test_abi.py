@@ -58,7 +58,7 @@ def test_shape_and_dtype_checks_come_before_any_cuda_call(lib):
     # misaligned base pointer
     args3 = [ctypes.c_void_p(0x1004)] + args[1:]
     assert lib.bsa_attn_fwd(*args3, 0, 1, 1, 64, 64, None, None, None) == -4
-    assert lib.bsa_mask_reduce(fake, s4, 1, 1, 100, fake, None, None) == -1
+    assert lib.bsa_mask_reduce(fake, s4, 1, 1, 100, fake, None, 0, None) == -1
     assert lib.bsa_reorder(fake, fake, s4, fake, 1, 1, 10, 8, 2, 2, 2, 2, None) == -1  # F*H*W != T
     assert lib.bsa_reorder(fake, fake, s4, fake, 1, 1, 8, 8, 2, 2, 2, 3, None) == -2   # elem size
     assert lib.bsa_selftest_bounded_wait(None, None, None) == -4
