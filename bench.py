@@ -480,7 +480,9 @@ def run_ours(args, rank, world, local_rank):
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
     (q, k, v, mask), tiles = make_inputs(seed=2 + rank, device=dev)
-    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    # 1 GiB: the untimed flush also keeps the GPU busy for a few hundred microseconds, so that the
+    # host has enqueued the timed call before the device gets to it (no host gap inside the events)
+    flush = torch.empty(1024 * 1024 * 1024, dtype=torch.uint8, device=dev)
     status = new_status_word(dev)
     out_buf = (torch.empty_like(q), torch.empty(1, 1, N_CTX, dtype=torch.float32, device=dev))
 
@@ -515,11 +517,30 @@ def run_ours(args, rank, world, local_rank):
     kern_ms = step_ms
 
     # ---- end to end: public op, pinned host inputs, D2H of the output ----
-    (hq, hk, hv, hmask), _ = make_inputs(seed=2 + rank, pinned=True)
+    # q, k, v and the mask of a step lie in ONE pinned staging buffer and cross PCIe in one copy;
+    # the op is called on views of its device copy
+    (hq, hk, hv, hmask), _ = make_inputs(seed=2 + rank)
+    parts = [hq.view(torch.uint8).reshape(-1), hk.view(torch.uint8).reshape(-1),
+             hv.view(torch.uint8).reshape(-1), hmask.view(torch.uint8).reshape(-1)]
+    offs = [0]
+    for t in parts:
+        offs.append((offs[-1] + t.numel() + 255) // 256 * 256)
+    staging = torch.empty(offs[-1], dtype=torch.uint8).pin_memory()
+    for t, o0 in zip(parts, offs):
+        staging[o0:o0 + t.numel()].copy_(t)
+    d_staging = torch.empty_like(staging, device=dev)
+    shp = hq.shape
+
+    def dview(i, dtype, shape):
+        n = parts[i].numel()
+        return d_staging[offs[i]:offs[i] + n].view(dtype).reshape(shape)
+
+    dq, dk, dv = (dview(i, torch.float16, shp) for i in range(3))
+    dm = dview(3, torch.bool, hmask.shape)
     h_out = torch.empty_like(hq).pin_memory()
 
     def e2e_step():
-        dq, dk, dv, dm = (t.to(dev, non_blocking=True) for t in (hq, hk, hv, hmask))
+        d_staging.copy_(staging, non_blocking=True)
         with torch.no_grad():
             o = flash_attention_custom_mask(dq, dk, dv, dm, SM_SCALE)
         h_out.copy_(o, non_blocking=True)
@@ -554,7 +575,7 @@ def run_ours(args, rank, world, local_rank):
     value = total_tiles * FLOP_PER_TILE * args.steps / (step_ms * 1e-3) / 1e12
     # per-GPU kernel figure: this rank's tiles over its own mean kernel time (max over ranks)
     achieved = (total_tiles / world) * FLOP_PER_TILE * args.steps / (kern_ms * 1e-3) / 1e12
-    h2d = sum(t.numel() * t.element_size() for t in (hq, hk, hv, hmask))
+    h2d = staging.numel()
     d2h = h_out.numel() * h_out.element_size()
     line = {
         "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world,
@@ -563,7 +584,7 @@ def run_ours(args, rank, world, local_rank):
         "data": "synthetic", "config": CONFIG,
         "path": {"step": "forward kernel with in-kernel tile listing from the block mask",
                  "tiles_per_gpu": total_tiles / world, "sharding": "one head per GPU",
-                 "l2": "flushed between steps (256 MiB write, untimed)"},
+                 "l2": "flushed between steps (1 GiB write, untimed)"},
         "fwd_kernel_ms": kern_ms / args.steps,
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s",
                      "frac": achieved / peak_tf, "traffic": FWD_KERNEL_DRAM_BYTES,
