@@ -392,13 +392,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (p.block != nullptr) {
         // mask mode: ordered compaction of the kept blocks of mask row (b, h, mb)
         const uint8_t* mrow = fwd_mask_row(it, p);
+        // 128 columns per pass, four independent loads per lane; the next pass's loads are issued
+        // before this pass's ballots, so a row costs one round trip to L2 rather than one per pass
+        int byte[4], next[4];
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+          const int c = 32 * jj + lane;
+          next[jj] = c < p.nb ? mrow[c * p.ms3] : 0;
+        }
         for (int c0 = 0; c0 < p.nb; c0 += 128) {
-          // four independent loads per lane before the ballots
-          int byte[4];
 #pragma unroll
           for (int jj = 0; jj < 4; ++jj) {
-            const int c = c0 + 32 * jj + lane;
-            byte[jj] = c < p.nb ? mrow[c * p.ms3] : 0;
+            byte[jj] = next[jj];
+            const int c = c0 + 128 + 32 * jj + lane;
+            next[jj] = c < p.nb ? mrow[c * p.ms3] : 0;
           }
 #pragma unroll
           for (int jj = 0; jj < 4; ++jj) {
@@ -660,6 +667,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const int n_super = (n_tiles + 3) >> 2;
       const uint16_t* cols = sm->cols[par];
       float m_ref = -INFINITY, m_true = -INFINITY, l = 0.f;
+      bool next_ready = false;  // the S barrier of the coming superstep has been seen complete
       // this lane's row of the element-level mask, if there is one
       const uint8_t* mask_row = nullptr;
       if constexpr (kElementMask) {
@@ -683,14 +691,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
           for (int j = 0; j < 4; ++j) mw[j] = __ldg(mp + j);
         }
-        ok = mbar_wait_warp(smem_u32(&sm->s_full[slot]), (g / kSlots) & 1, abort_flag);
-        if (!ok) break;
+        if (!next_ready) {
+          ok = mbar_wait_warp(smem_u32(&sm->s_full[slot]), (g / kSlots) & 1, abort_flag);
+          if (!ok) break;
+        }
         tc_fence_after();
         if (t_mine < nt) {
           uint32_t sr[64];
           tmem_ld_32x32b_x32(s_addr + col_s, sr);
           tmem_ld_32x32b_x32(s_addr + col_s + 32, sr + 32);
           tc_wait_ld();
+          // the other lanes' tile of this team reads these lanes too: zeros (the logits are in
+          // registers now); stored first, so that it drains under the arithmetic
+          if (t_other < nt) tmem_st_zero_32x32b_x32(s_addr + col_z);
           if (partial) {
             // masked elements become -inf: they take no part in the maximum and exponentiate to 0
 #pragma unroll
@@ -745,13 +758,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           tmem_st_32x32b_x16(s_addr + col_p, pk);
           exp_chunk<kBf16>(sr + 32, c, neg_m, pk, l);
           tmem_st_32x32b_x16(s_addr + col_p + 16, pk);
+        } else if (t_other < nt) {
+          tmem_st_zero_32x32b_x32(s_addr + col_z);
         }
-        // the other lanes' tile of this team reads these lanes too: zeros (the logits are used up)
-        if (t_other < nt) tmem_st_zero_32x32b_x32(s_addr + col_z);
+        // Look at the next superstep's S barrier now: the round trip to it runs under the drain of
+        // the stores, and if S is there (it normally is: three slots) the wait at the top of the
+        // loop is skipped.
+        bool polled = false;
+        if (u + 1 < n_super)
+          polled = mbar_try_wait(smem_u32(&sm->s_full[(g + 1) % kSlots]), ((g + 1) / kSlots) & 1);
         tc_wait_st();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&sm->p_full[slot][team]));
+        next_ready = __all_sync(0xffffffffu, polled);
       }
       if (!ok) break;
 
