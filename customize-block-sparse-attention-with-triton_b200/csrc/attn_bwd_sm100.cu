@@ -22,10 +22,11 @@
 //
 // Persistent: one CTA per SM starts with block blockIdx.x and draws further blocks from an
 // optional work counter (or walks a fixed stride); long lists first when the mask is causal.
-// Roles: warps 0..7 compute (lane quarter = warp % 4, column half = warp / 4), warp 8 TMA
-// producer, warp 9 issues the S/dP MMAs and owns TMEM, warp 10 issues the accumulating MMAs (two
-// issuers, so neither waits behind the other's barrier round trips; both run warp-wide with one
-// elected lane issuing).  S/dP are released as soon as the compute warps hold them in registers;
+// Roles: warps 0..15 compute (lane quarter = warp % 4, 16 of a tile's 64 columns = warp / 4: four
+// warps per SM sub-partition, so that one warp's TMEM loads, stores and barrier round trips hide
+// behind the others' arithmetic), warp 16 TMA producer, warp 17 issues the S/dP MMAs and owns
+// TMEM, warp 18 issues the accumulating MMAs (two issuers, so neither waits behind the other's
+// barrier round trips; both run warp-wide with one elected lane issuing).  S/dP are released as soon as the compute warps hold them in registers;
 // P^T/dS^T live in their own TMEM buffers until the accumulating MMAs that read them are complete.
 // Every wait is bounded and every barrier is waited on by warps that see each of its phases.
 #include <math.h>
@@ -36,7 +37,10 @@
 namespace bsa {
 
 constexpr int kBwdStages = 4;
-constexpr int kBwdThreads = 352;
+constexpr int kCW = 16;                    // compute warps: 4 lane quarters x (kCW / 4) column parts
+constexpr int kChunk = 64 / (kCW / 4);     // columns of a tile per compute warp
+constexpr int kProdWarp = kCW, kXWarp = kCW + 1, kAccWarp = kCW + 2;
+constexpr int kBwdThreads = 32 * (kCW + 3);
 constexpr uint32_t kBwdTile = 64 * 64 * 2;
 constexpr uint32_t kBwdTmemCols = 512;
 constexpr int kListIndex = BSA_LIST_PARTIAL_FLAG - 1;  // a list entry without its flag
@@ -89,13 +93,13 @@ __device__ __forceinline__ void bwd_give_up(BwdSmem* sm, int32_t* status, int co
   report_status(status, code);
 }
 
-// Stores 32 columns of one output row: (own[i] + other[i]) * scale as 16-bit.
+// Stores kChunk columns of one output row: (own[i] + other[i]) * scale as 16-bit.
 template <bool kBf16>
 __device__ __forceinline__ void store_half_row(void* base, int64_t elem_off, const uint32_t* own,
                                                const float* other, int other_stride, float scale) {
   uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(base) + elem_off);
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
+  for (int i = 0; i < kChunk / 8; ++i) {
     uint32_t w[4];
 #pragma unroll
     for (int t = 0; t < 4; ++t) {
@@ -165,7 +169,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&sm->item_full[i]), 1);
-      mbar_init(smem_u32(&sm->item_free[i]), 10);  // 8 compute warps and the two issuers
+      mbar_init(smem_u32(&sm->item_free[i]), kCW + 2);  // the compute warps and the two issuers
     }
     mbar_init(smem_u32(&sm->stat_full), 1);
     mbar_init(smem_u32(&sm->stat_free), 1);
@@ -174,18 +178,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
       mbar_init(smem_u32(&sm->in_empty[s]), 1);
     }
     mbar_init(smem_u32(&sm->x_full), 1);
-    mbar_init(smem_u32(&sm->x_free), 8);  // one arrival per compute warp
-    mbar_init(smem_u32(&sm->d_full), 8);
+    mbar_init(smem_u32(&sm->x_free), kCW);  // one arrival per compute warp
+    mbar_init(smem_u32(&sm->d_full), kCW);
     mbar_init(smem_u32(&sm->d_free), 1);
-    mbar_init(smem_u32(&sm->acc_free), 8);
+    mbar_init(smem_u32(&sm->acc_free), kCW);
     sm->abort_flag = 0;
     mbar_fence_init();
   }
-  if (warp == 9) {
+  if (warp == kXWarp) {
     tmem_alloc(smem_u32(&sm->tmem_base), kBwdTmemCols);
     tmem_relinquish();
   }
-  if (warp == 8 && lane == 0) {
+  if (warp == kProdWarp && lane == 0) {
     tma_prefetch_desc(&tm_stat0);
     tma_prefetch_desc(&tm_stat1);
     tma_prefetch_desc(&tm_str0);
@@ -197,7 +201,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
   const uint32_t tmem = sm->tmem_base;
   volatile int* abort_flag = &sm->abort_flag;
 
-  if (warp == 8) {
+  if (warp == kProdWarp) {
     // =========================== TMA producer ===========================
     bool ok = true;
     bool terminal = p.ticket == nullptr;  // drew a ticket past the end (or draws none)
@@ -281,7 +285,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
         if (t == p.items - 1) atomicExch(p.ticket, 0);
       } while (stride + t < p.items);
     }
-  } else if (warp == 9) {
+  } else if (warp == kXWarp) {
     // =========================== S / dP issuer ===========================
     constexpr uint32_t idesc_x128 = umma_idesc(kBf16, 0, 0, 128, 128);
     constexpr uint32_t idesc_x64 = umma_idesc(kBf16, 0, 0, 128, 64);  // odd tail: one tile
@@ -327,7 +331,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
       ++ni;
     }
     if (!ok) bwd_give_up(sm, p.status, 2);
-  } else if (warp == 10) {
+  } else if (warp == kAccWarp) {
     // =========================== accumulating-MMA issuer ===========================
     constexpr uint32_t idesc_acc = umma_idesc(kBf16, 0, 1, 128, 64);
     const bool leader = elect_one();
@@ -377,7 +381,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
   } else {
     // =========================== compute warps ===========================
     const int quarter = warp & 3;
-    const int ch = warp >> 2;           // which 32 of the tile's 64 columns
+    const int ch = warp >> 2;           // which kChunk of the tile's 64 columns
     const int t_mine = quarter >> 1;    // lanes 0..63 own tile a of a superstep, 64..127 tile b
     const int r_blk = (quarter & 1) * 32 + lane;  // row of the CTA's block
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
@@ -386,11 +390,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
     {
       // The accumulating MMAs of a tile sweep all 128 lanes: the half of the lanes that does not
       // own the tile holds zeros where that tile's P / dS live.  Nothing else ever writes there.
-      uint32_t z[16];
+      uint32_t z[kChunk / 2];
 #pragma unroll
-      for (int i = 0; i < 16; ++i) z[i] = 0u;
-      if constexpr (kDKDV) tmem_st_32x32b_x16(tmem + lane_base + kTmP + 32 * (1 - t_mine) + 16 * ch, z);
-      tmem_st_32x32b_x16(tmem + lane_base + kTmDS + 32 * (1 - t_mine) + 16 * ch, z);
+      for (int i = 0; i < kChunk / 2; ++i) z[i] = 0u;
+      if constexpr (kDKDV)
+        tmem_st_cols<kChunk / 2>(tmem + lane_base + kTmP + 32 * (1 - t_mine) + (kChunk / 2) * ch, z);
+      tmem_st_cols<kChunk / 2>(tmem + lane_base + kTmDS + 32 * (1 - t_mine) + (kChunk / 2) * ch, z);
       tc_wait_st();
     }
     bool ok = true;
@@ -399,23 +404,23 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
       int w;
       ok = bwd_next_item(sm, i, lane, abort_flag, &w);
       // on a give-up the warp goes on to the barriers below with an empty item, so that no warp
-      // of this role is left waiting at one; the vote there makes all eight leave
-      if (ok && w < 0) break;  // no more work: the same for all eight warps
+      // of this role is left waiting at one; the vote there makes all of them leave
+      if (ok && w < 0) break;  // no more work: the same for all compute warps
       BwdItem it = bwd_item<kDKDV>(ok ? w : 0, p);
       if (!ok) it.n_tiles = 1;
       const int n_super = (it.n_tiles + 1) >> 1;
       const int row = it.blk * 64 + r_blk;
       const int64_t off =
-          it.b * p.sb + it.h * p.sh + static_cast<int64_t>(row) * p.sn + 32 * ch;
+          it.b * p.sb + it.h * p.sh + static_cast<int64_t>(row) * p.sn + kChunk * ch;
       if (n_super == 0) {
-        // a block with an empty list: zero gradients (the same decision in all eight warps)
+        // a block with an empty list: zero gradients (the same decision in all compute warps)
         if (t_mine == 0) {
 #pragma unroll
           for (int a = 0; a < kAccs; ++a) {
             uint4* dst = reinterpret_cast<uint4*>(
                 static_cast<uint16_t*>((kDKDV && a == 0) ? p.out0 : p.out1) + off);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) dst[i] = make_uint4(0u, 0u, 0u, 0u);
+            for (int i = 0; i < kChunk / 8; ++i) dst[i] = make_uint4(0u, 0u, 0u, 0u);
           }
         }
         continue;
@@ -439,17 +444,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
         const int nt = min(2, it.n_tiles - 2 * j);
         const bool active = t_mine < nt;  // warp-uniform
         // A tile with masked elements inside: fetch this lane's 32 mask bytes while S is on its way
-        uint32_t mw[8];
+        uint32_t mw[kChunk / 4];
         bool partial = false;
         if (kElementMask && active) {
           const int e = __ldg(it.ents + 2 * j + t_mine);
           partial = (e & BSA_LIST_PARTIAL_FLAG) != 0;  // warp-uniform
           if (partial) {
-            const int64_t other = static_cast<int64_t>((e & kListIndex) * 64 + 32 * ch);
+            const int64_t other = static_cast<int64_t>((e & kListIndex) * 64 + kChunk * ch);
             if constexpr (kDKDV) {
               const uint8_t* mp = mask_at + other * p.ds2;
 #pragma unroll
-              for (int q4 = 0; q4 < 8; ++q4) {
+              for (int q4 = 0; q4 < kChunk / 4; ++q4) {
                 uint32_t w4 = 0;
 #pragma unroll
                 for (int bb = 0; bb < 4; ++bb)
@@ -458,9 +463,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
               }
             } else {
               const uint4* mp = reinterpret_cast<const uint4*>(mask_at + other);
-              const uint4 a = __ldg(mp), b2 = __ldg(mp + 1);
-              mw[0] = a.x; mw[1] = a.y; mw[2] = a.z; mw[3] = a.w;
-              mw[4] = b2.x; mw[5] = b2.y; mw[6] = b2.z; mw[7] = b2.w;
+#pragma unroll
+              for (int q16 = 0; q16 < kChunk / 16; ++q16) {
+                const uint4 a = __ldg(mp + q16);
+                mw[4 * q16] = a.x; mw[4 * q16 + 1] = a.y; mw[4 * q16 + 2] = a.z; mw[4 * q16 + 3] = a.w;
+              }
             }
           }
         }
@@ -472,10 +479,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
         ok = mbar_wait_warp(smem_u32(&sm->x_full), gs & 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
-        uint32_t xs[32], xd[32];
+        uint32_t xs[kChunk], xd[kChunk];
         if (active) {
-          tmem_ld_32x32b_x32(tmem + lane_base + kTmX0 + 64 * t_mine + 32 * ch, xs);
-          tmem_ld_32x32b_x32(tmem + lane_base + kTmX1 + 64 * t_mine + 32 * ch, xd);
+          tmem_ld_cols<kChunk>(tmem + lane_base + kTmX0 + 64 * t_mine + kChunk * ch, xs);
+          tmem_ld_cols<kChunk>(tmem + lane_base + kTmX1 + 64 * t_mine + kChunk * ch, xd);
         }
         tc_wait_ld();
         // S/dP are in registers: the next superstep's may be issued
@@ -485,7 +492,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
         if (partial) {
           // masked elements: logit -inf, so P = 0 and with it dS = 0
 #pragma unroll
-          for (int q4 = 0; q4 < 8; ++q4) {
+          for (int q4 = 0; q4 < kChunk / 4; ++q4) {
             const uint32_t nz = __vcmpne4(mw[q4], 0u);
 #pragma unroll
             for (int bb = 0; bb < 4; ++bb) {
@@ -494,12 +501,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
             }
           }
         }
-        uint32_t pk_p[16], pk_ds[16];
+        uint32_t pk_p[kChunk / 2], pk_ds[kChunk / 2];
         if (active) {
-          const float4* lse4 = reinterpret_cast<const float4*>(&sm->lse[s][t_mine][32 * ch]);
-          const float4* del4 = reinterpret_cast<const float4*>(&sm->delta[s][t_mine][32 * ch]);
+          const float4* lse4 = reinterpret_cast<const float4*>(&sm->lse[s][t_mine][kChunk * ch]);
+          const float4* del4 = reinterpret_cast<const float4*>(&sm->delta[s][t_mine][kChunk * ch]);
 #pragma unroll
-          for (int i = 0; i < 32; i += 4) {
+          for (int i = 0; i < kChunk; i += 4) {
             float l[4], d[4];
             if constexpr (kDKDV) {
               const float4 lv = lse4[i / 4], dv = del4[i / 4];
@@ -549,8 +556,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
         if (!ok) break;
         if (active) {
           tc_fence_after();
-          if constexpr (kDKDV) tmem_st_32x32b_x16(tmem + lane_base + kTmP + 32 * t_mine + 16 * ch, pk_p);
-          tmem_st_32x32b_x16(tmem + lane_base + kTmDS + 32 * t_mine + 16 * ch, pk_ds);
+          if constexpr (kDKDV)
+            tmem_st_cols<kChunk / 2>(tmem + lane_base + kTmP + 32 * t_mine + (kChunk / 2) * ch, pk_p);
+          tmem_st_cols<kChunk / 2>(tmem + lane_base + kTmDS + 32 * t_mine + (kChunk / 2) * ch, pk_ds);
         }
         tc_wait_st();
         tc_fence_before();
@@ -561,7 +569,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
       if (ok) ok = mbar_wait_warp(smem_u32(&sm->d_free), (gs - 1) & 1, abort_flag);
 
       // ---- write-out: lane r holds the tile-a sums of row r, lane r+64 its tile-b sums ----
-      // Both named barriers are executed by all eight compute warps, also after a give-up (every
+      // Both named barriers are executed by all compute warps, also after a give-up (every
       // bounded wait of a warp still in the loop ends once the flag is up); the second one carries
       // the give-up vote.  Lanes 64..127 are never unwritten, even for a single-tile list: the
       // first accumulate-off MMA sweeps all lanes, and theirs hold zeros for tile a.
@@ -570,23 +578,23 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
         tc_fence_after();
 #pragma unroll
         for (int a = 0; a < kAccs; ++a) {
-          uint32_t up[32];
-          tmem_ld_32x32b_x32(tmem + lane_base + (kDKDV && a == 0 ? kTmAcc0 : kTmAcc1) + 32 * ch, up);
+          uint32_t up[kChunk];
+          tmem_ld_cols<kChunk>(tmem + lane_base + (kDKDV && a == 0 ? kTmAcc0 : kTmAcc1) + kChunk * ch, up);
           tc_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) sm->xfer[a][32 * ch + i][r_blk] = __uint_as_float(up[i]);
+          for (int i = 0; i < kChunk; ++i) sm->xfer[a][kChunk * ch + i][r_blk] = __uint_as_float(up[i]);
         }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&sm->acc_free));
       }
-      named_barrier_sync(1, 256);
+      named_barrier_sync(1, 32 * kCW);
       if (ok && t_mine == 0) {
         tc_fence_after();
 #pragma unroll
         for (int a = 0; a < kAccs; ++a) {
-          uint32_t acc[32];
-          tmem_ld_32x32b_x32(tmem + lane_base + (kDKDV && a == 0 ? kTmAcc0 : kTmAcc1) + 32 * ch, acc);
+          uint32_t acc[kChunk];
+          tmem_ld_cols<kChunk>(tmem + lane_base + (kDKDV && a == 0 ? kTmAcc0 : kTmAcc1) + kChunk * ch, acc);
           tc_wait_ld();
           if (a == kAccs - 1) {
             // the accumulators are in registers: the next item may start accumulating
@@ -595,19 +603,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
             if (lane == 0) mbar_arrive(smem_u32(&sm->acc_free));
           }
           store_half_row<kBf16>((kDKDV && a == 0) ? p.out0 : p.out1, off, acc,
-                                &sm->xfer[a][32 * ch][r_blk], 65,
+                                &sm->xfer[a][kChunk * ch][r_blk], 65,
                                 (kDKDV && a == 0) ? 1.0f : p.sm_scale);
         }
       }
-      // xfer may be overwritten by the next item now; all eight warps leave together on a give-up
-      if (named_barrier_or(1, 256, !ok)) break;
+      // xfer may be overwritten by the next item now; all compute warps leave together on a give-up
+      if (named_barrier_or(1, 32 * kCW, !ok)) break;
     }
     if (!ok) bwd_give_up(sm, p.status, 3);
   }
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 9) {
+  if (warp == kXWarp) {
     __syncwarp();
     tc_fence_after();
     tmem_dealloc(tmem, kBwdTmemCols);

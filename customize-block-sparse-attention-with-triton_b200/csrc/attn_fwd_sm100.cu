@@ -69,6 +69,7 @@ constexpr int kSlots = 3;       // S/P slots (128 TMEM columns): held from S iss
 constexpr int kFwdThreads = 512;
 constexpr int kSoftmaxWarps = 8, kProducerWarp = 8, kSWarp = 9, kPvWarp = 10;  // warps 11..14 write out
 constexpr int kVProducerWarp = 15;  // = the last warp
+constexpr int kListerWarp = 14;     // the write-out warp that also sets up the items
 constexpr uint32_t kTileBytes = 64 * 64 * 2;       // one Q, K or V tile
 constexpr uint32_t kFwdTmemCols = 512;
 // TMEM columns: slot r at 128 r; accumulator of softmax team T at 384 + 64 T.
@@ -93,7 +94,8 @@ struct FwdSmem {
   float lsum[2][2][128];
   float mtrue[2][2][128];
   uint64_t order_full;                        // `order` is ready
-  uint64_t list_full[2];                      // producer -> everyone: list and tile count ready
+  uint64_t list_full[2];                      // lister -> everyone: list and tile count ready
+  uint64_t setup_go[2];                       // producer -> lister: time to set up the next item
   uint64_t q_full[2], q_free[2];
   uint64_t k_full[kKStages];
   uint64_t k_empty[kKStages];                 // S of the superstep complete
@@ -269,6 +271,60 @@ __device__ __forceinline__ void fwd_build_order(FwdSmem* sm, const FwdParams& p,
   if (tid == 0) mbar_arrive(smem_u32(&sm->order_full));
 }
 
+// Lists the key blocks of work item w into the list buffer of parity par (one warp) and publishes
+// list, tile count and item.
+template <bool kElementMask>
+__device__ __forceinline__ void fwd_list_item(FwdSmem* sm, const FwdParams& p, int w, int par,
+                                              int lane) {
+  const FwdItem it = fwd_item(w, p);
+  uint16_t* cols = sm->cols[par];
+  int n_tiles = 0;
+  if (p.block != nullptr) {
+    // mask mode: ordered compaction of the kept blocks of mask row (b, h, mb)
+    const uint8_t* mrow = fwd_mask_row(it, p);
+    // 128 columns per pass, four independent loads per lane; the next pass's loads are issued
+    // before this pass's ballots, so a row costs one round trip to L2 rather than one per pass
+    int byte[4], next[4];
+#pragma unroll
+    for (int jj = 0; jj < 4; ++jj) {
+      const int c = 32 * jj + lane;
+      next[jj] = c < p.nb ? mrow[c * p.ms3] : 0;
+    }
+    for (int c0 = 0; c0 < p.nb; c0 += 128) {
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) {
+        byte[jj] = next[jj];
+        const int c = c0 + 128 + 32 * jj + lane;
+        next[jj] = c < p.nb ? mrow[c * p.ms3] : 0;
+      }
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) {
+        const unsigned bal = __ballot_sync(0xffffffffu, byte[jj] != 0);
+        if (byte[jj] != 0)
+          cols[n_tiles + __popc(bal & ((1u << lane) - 1u))] = static_cast<uint16_t>(
+              (c0 + 32 * jj + lane) | (kElementMask && byte[jj] == 2 ? kColPartial : 0));
+        n_tiles += __popc(bal);
+      }
+    }
+  } else {
+    const int64_t li =
+        static_cast<int64_t>(it.b * p.list_b_stride + it.h * p.list_h_stride) * p.nb + it.mb;
+    const int beg = __ldg(p.row_ptr + li);
+    n_tiles = __ldg(p.row_ptr + li + 1) - beg;
+    for (int jj = lane; jj < n_tiles; jj += 32) {
+      const int e = __ldg(p.col_idx + beg + jj);
+      cols[jj] = static_cast<uint16_t>(
+          (e & kColIndex) | (kElementMask && (e & BSA_LIST_PARTIAL_FLAG) ? kColPartial : 0));
+    }
+  }
+  __syncwarp();
+  if (lane == 0) {
+    sm->ntiles[par] = n_tiles;
+    sm->item[par] = w;
+    mbar_arrive(smem_u32(&sm->list_full[par]));  // release: count and list are visible
+  }
+}
+
 // kElementMask: the instantiation that applies a dense mask inside the tiles marked partial; the
 // plain one carries none of that code.
 template <bool kBf16, bool kElementMask>
@@ -292,6 +348,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&sm->list_full[i]), 1);
+      mbar_init(smem_u32(&sm->setup_go[i]), 1);
       mbar_init(smem_u32(&sm->q_full[i]), 1);
       mbar_init(smem_u32(&sm->q_free[i]), 1);
       mbar_init(smem_u32(&sm->o_full[i]), 1);
@@ -343,109 +400,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   if (warp == kProducerWarp) {
     // =========================== producer ===========================
     bool ok = true;
-    bool terminal = p.ticket == nullptr;  // drew a ticket past the end (or draws none)
+    // Loads Q and the K tiles of the listed key blocks from the list the lister published.  Two K
+    // superstages before the end of an item it tells the lister to set up the next one: late
+    // enough for the hand-out through the work counter to follow the CTAs' real progress, early
+    // enough for the list to be there when this item's last K tile has been asked for.
     int gs = 0;  // supersteps issued so far by this CTA (ring position)
     int qi = 0;  // non-empty items so far (Q buffer position)
-    int w = blockIdx.x;
-
-    // Draws item j (the first one is the CTA's own), lists its key blocks into the list buffer of
-    // j's parity and publishes them.  Returns the tile count, or -1 when there is no further item
-    // (published as well) or a wait gave up (ok = false).
-    auto set_up = [&](int j, FwdItem& it) -> int {
-      const int par = j & 1;
-      if (j > 0) {
-        // next item: the following ticket when items are handed out dynamically, else a fixed stride
-        if (p.ticket != nullptr) {
-          int t = 0;
-          if (lane == 0) {
-            t = atomicAdd(p.ticket, 1);
-            // every CTA draws until its first ticket past the end, so the launch draws exactly
-            // `items` tickets in all; whoever draws the last one leaves the counter at zero
-            if (t == p.items - 1) atomicExch(p.ticket, 0);
-          }
-          t = __shfl_sync(0xffffffffu, t, 0);
-          terminal = t >= n2;
-          if (sorted && t < n2) {
-            if (j == 1) ok = mbar_wait_warp(smem_u32(&sm->order_full), 0, abort_flag);
-            if (!ok) return -1;
-            t = *const_cast<volatile int*>(&sm->order[t]);
-          }
-          w = stride + t;
-        } else {
-          w += stride;
-        }
-      }
-      // the list buffer (and the tile count) of item j-2 must have been read by everyone
-      if (j >= 2)
-        ok = mbar_wait_warp_idle(smem_u32(&sm->o_free[par]), ((j - 2) >> 1) & 1, abort_flag, 128);
-      if (!ok) return -1;
-      if (w >= p.items) {
-        if (lane == 0) {
-          sm->item[par] = -1;
-          mbar_arrive(smem_u32(&sm->list_full[par]));
-        }
-        return -1;
-      }
-      it = fwd_item(w, p);
-      uint16_t* cols = sm->cols[par];
-      int n_tiles = 0;
-      if (p.block != nullptr) {
-        // mask mode: ordered compaction of the kept blocks of mask row (b, h, mb)
-        const uint8_t* mrow = fwd_mask_row(it, p);
-        // 128 columns per pass, four independent loads per lane; the next pass's loads are issued
-        // before this pass's ballots, so a row costs one round trip to L2 rather than one per pass
-        int byte[4], next[4];
-#pragma unroll
-        for (int jj = 0; jj < 4; ++jj) {
-          const int c = 32 * jj + lane;
-          next[jj] = c < p.nb ? mrow[c * p.ms3] : 0;
-        }
-        for (int c0 = 0; c0 < p.nb; c0 += 128) {
-#pragma unroll
-          for (int jj = 0; jj < 4; ++jj) {
-            byte[jj] = next[jj];
-            const int c = c0 + 128 + 32 * jj + lane;
-            next[jj] = c < p.nb ? mrow[c * p.ms3] : 0;
-          }
-#pragma unroll
-          for (int jj = 0; jj < 4; ++jj) {
-            const unsigned bal = __ballot_sync(0xffffffffu, byte[jj] != 0);
-            if (byte[jj] != 0)
-              cols[n_tiles + __popc(bal & ((1u << lane) - 1u))] = static_cast<uint16_t>(
-                  (c0 + 32 * jj + lane) | (kElementMask && byte[jj] == 2 ? kColPartial : 0));
-            n_tiles += __popc(bal);
-          }
-        }
-      } else {
-        const int64_t li =
-            static_cast<int64_t>(it.b * p.list_b_stride + it.h * p.list_h_stride) * p.nb + it.mb;
-        const int beg = __ldg(p.row_ptr + li);
-        n_tiles = __ldg(p.row_ptr + li + 1) - beg;
-        for (int jj = lane; jj < n_tiles; jj += 32) {
-          const int e = __ldg(p.col_idx + beg + jj);
-          cols[jj] = static_cast<uint16_t>(
-              (e & kColIndex) | (kElementMask && (e & BSA_LIST_PARTIAL_FLAG) ? kColPartial : 0));
-        }
-      }
-      __syncwarp();
-      if (lane == 0) {
-        sm->ntiles[par] = n_tiles;
-        sm->item[par] = w;
-        mbar_arrive(smem_u32(&sm->list_full[par]));  // release: count and list are visible
-      }
-      return n_tiles;
-    };
-
-    // The set-up of item i+1 (a global atomic, the mask row, the list) runs while the last two K
-    // superstages of item i are still to be issued, i.e. at a moment when this warp would
-    // otherwise wait for a free K stage: its latencies stay off the tensor pipe's critical path.
-    // The other roles see the next item's header early as well.
-    FwdItem it, it_next;
-    int n_tiles = set_up(0, it);
-    for (int i = 0; ok && n_tiles >= 0; ++i) {
-      const uint16_t* cols = sm->cols[i & 1];
+    fwd_list_item<kElementMask>(sm, p, blockIdx.x, 0, lane);  // the CTA's own first item
+    for (int i = 0; ok; ++i) {
+      const int par = i & 1;
+      ok = mbar_wait_warp(smem_u32(&sm->list_full[par]), (i >> 1) & 1, abort_flag);
+      if (!ok) break;
+      const int w = *const_cast<volatile int*>(&sm->item[par]);
+      if (w < 0) break;  // no more work
+      const FwdItem it = fwd_item(w, p);
+      const int n_tiles = *const_cast<volatile int*>(&sm->ntiles[par]);
+      const uint16_t* cols = sm->cols[par];
       const int n_super = (n_tiles + 3) >> 2;
-      int n_next = -2;  // -2: item i+1 not set up yet
       if (n_super > 0) {
         const int qpar = qi & 1;
         if (qi >= 2) ok = mbar_wait_warp(smem_u32(&sm->q_free[qpar]), ((qi - 2) >> 1) & 1, abort_flag);
@@ -457,20 +428,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
         ++qi;
       }
+      const int u_go = max(n_super - 2, 0);
+      if (n_super == 0 && lane == 0) mbar_arrive(smem_u32(&sm->setup_go[par]));
       // One lane per tile issues its load: a single thread can start a tile load only every couple
       // of hundred cycles, which four loads in a row would turn into the kernel's bound.
       for (int u = 0; u < n_super; ++u) {
-        if (n_next == -2 && u >= n_super - 2) {
-          // only if nothing in the set-up would have to wait now (the list buffer is free, the
-          // hand-out order is there): the K tiles below must not be held back by it
-          const int j = i + 1;
-          bool ready = j < 2 || mbar_try_wait(smem_u32(&sm->o_free[j & 1]), ((j - 2) >> 1) & 1);
-          if (j == 1 && sorted) ready = ready && mbar_try_wait(smem_u32(&sm->order_full), 0);
-          if (__all_sync(0xffffffffu, ready)) {
-            n_next = set_up(j, it_next);
-            if (!ok) break;
-          }
-        }
+        if (u == u_go && lane == 0) mbar_arrive(smem_u32(&sm->setup_go[par]));
         const int g = gs + u, ks = g % kKStages;
         const int nt = min(4, n_tiles - 4 * u);
         ok = mbar_wait_warp(smem_u32(&sm->k_empty[ks]), ((g / kKStages) & 1) ^ 1, abort_flag);
@@ -482,22 +445,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           tma_load_4d(smem_u32(sm->k[ks][((lane & 1) << 1) | (lane >> 1)]), &tm_k, bar, 0,
                       static_cast<int>(cols[4 * u + lane] & kColIndex) * 64, it.h, it.b);
       }
-      if (!ok) break;
       gs += n_super;
-      if (n_next == -2) n_next = set_up(i + 1, it_next);
-      n_tiles = n_next;
-      it = it_next;
     }
     if (!ok) fwd_give_up(sm, p.status, kFailProducer);
-    if (!terminal && lane == 0) {
-      // gave up before the last draw: draw on (without working) until this CTA's first ticket past
-      // the end, so that the launch still draws `items` tickets and the counter returns to zero
-      int t;
-      do {
-        t = atomicAdd(p.ticket, 1);
-        if (t == p.items - 1) atomicExch(p.ticket, 0);
-      } while (t < n2);
-    }
   } else if (warp == kVProducerWarp) {
     // =========================== V producer ===========================
     // Loads the V tiles of the listed key blocks, one lane per tile, from the list the producer
@@ -793,20 +743,74 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     // rows to lanes 0..63 through shared memory, 32 columns at a time.  All named barriers of an
     // iteration are always executed, also after a give-up, and the last one carries the give-up
     // vote, so that no warp of this role can be left waiting at one.
+    //
+    // One of the four warps is also the lister: it sets up item i+1 when the producer says so
+    // during item i, i.e. between its write-outs of items i-1 and i (the producer lists the
+    // CTA's first item itself, which nothing can overlap).  The draw
+    // from the work counter, the mask row and the ballots take a couple of thousand cycles, which
+    // in the producer's own instruction stream held back the K tiles of the current item.
     const int quarter = warp & 3;  // lane quarter a warp may touch = its index mod 4
+    const bool lister = warp == kListerWarp;
+    bool ok = true;
+    bool terminal = p.ticket == nullptr;  // drew a ticket past the end (or draws none)
+    int lw = blockIdx.x;
+    // Lister (one of the four warps): draws item j >= 1, lists its key blocks into the list buffer
+    // of j's parity and publishes them, or publishes that there is no further item.  A wait that
+    // gives up leaves ok = false and nothing published.
+    auto set_up = [&](int j) {
+      const int par = j & 1;
+      {
+        // next item: the following ticket when items are handed out dynamically, else a fixed stride
+        if (p.ticket != nullptr) {
+          int t = 0;
+          if (lane == 0) {
+            t = atomicAdd(p.ticket, 1);
+            // every CTA draws until its first ticket past the end, so the launch draws exactly
+            // `items` tickets in all; whoever draws the last one leaves the counter at zero
+            if (t == p.items - 1) atomicExch(p.ticket, 0);
+          }
+          t = __shfl_sync(0xffffffffu, t, 0);
+          terminal = t >= n2;
+          if (sorted && t < n2) {
+            if (j == 1) ok = mbar_wait_warp(smem_u32(&sm->order_full), 0, abort_flag);
+            if (!ok) return;
+            t = *const_cast<volatile int*>(&sm->order[t]);
+          }
+          lw = stride + t;
+        } else {
+          lw += stride;
+        }
+      }
+      // the list buffer (and the tile count) of item j-2 must have been read by everyone
+      if (j >= 2)
+        ok = mbar_wait_warp_idle(smem_u32(&sm->o_free[par]), ((j - 2) >> 1) & 1, abort_flag, 128);
+      if (!ok) return;
+      if (lw >= p.items) {
+        if (lane == 0) {
+          sm->item[par] = -1;
+          mbar_arrive(smem_u32(&sm->list_full[par]));
+        }
+        return;
+      }
+      fwd_list_item<kElementMask>(sm, p, lw, par, lane);
+    };
+
     if (sorted) fwd_build_order(sm, p, quarter * 32 + lane, stride, n2);
     const int half = quarter >> 1;
     const int lane_row = quarter * 32 + lane;
     const int r_blk = (quarter & 1) * 32 + lane;  // row of the query block
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
-    bool ok = true;
     for (int i = 0;; ++i) {
       const int par = i & 1;
-      ok = mbar_wait_warp_idle(smem_u32(&sm->list_full[par]), (i >> 1) & 1, abort_flag, 256);
+      if (ok) ok = mbar_wait_warp_idle(smem_u32(&sm->list_full[par]), (i >> 1) & 1, abort_flag, 256);
       const int w = ok ? *const_cast<volatile int*>(&sm->item[par]) : 0;
       if (w < 0) break;  // no more work: the same for all four warps
       const FwdItem it = fwd_item(w, p);
       const int n_tiles = ok ? *const_cast<volatile int*>(&sm->ntiles[par]) : 0;
+      if (lister && ok) {
+        ok = mbar_wait_warp(smem_u32(&sm->setup_go[par]), (i >> 1) & 1, abort_flag);
+        if (ok) set_up(i + 1);
+      }
       if (ok) ok = mbar_wait_warp_idle(smem_u32(&sm->stats_full[par]), (i >> 1) & 1, abort_flag, 128);
       // The weights of the four partial results need the statistics only, which the softmax warps
       // publish before the item's last P V is complete: work them out before waiting for that, so
@@ -893,6 +897,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (any_failed) break;
     }
     if (!ok) fwd_give_up(sm, p.status, kFailOut);
+    if (lister && !terminal && lane == 0) {
+      // gave up before the last draw: draw on (without working) until this CTA's first ticket past
+      // the end, so that the launch still draws `items` tickets and the counter returns to zero
+      int t;
+      do {
+        t = atomicAdd(p.ticket, 1);
+        if (t == p.items - 1) atomicExch(p.ticket, 0);
+      } while (t < n2);
+    }
+
   }
 
   // ---- tear-down: every role arrives here, also after a give-up ----

@@ -340,6 +340,27 @@ __device__ __forceinline__ void tmem_st_32x32b_x16(uint32_t taddr, const uint32_
       : "memory");
 }
 
+__device__ __forceinline__ void tmem_st_32x32b_x8(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
+      "r"(r[7])
+      : "memory");
+}
+// n columns (32 or 16 on a load, 16 or 8 on a store) of the warp's 32 lanes
+template <int kCols>
+__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t* r) {
+  static_assert(kCols == 32 || kCols == 16, "column count");
+  if constexpr (kCols == 32) tmem_ld_32x32b_x32(taddr, r);
+  else tmem_ld_32x32b_x16(taddr, r);
+}
+template <int kCols>
+__device__ __forceinline__ void tmem_st_cols(uint32_t taddr, const uint32_t* r) {
+  static_assert(kCols == 16 || kCols == 8, "column count");
+  if constexpr (kCols == 16) tmem_st_32x32b_x16(taddr, r);
+  else tmem_st_32x32b_x8(taddr, r);
+}
+
 // Two fp32 operations in one instruction (sm_100 packed forms; same rounding as the scalar ones).
 __device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
   uint64_t r;
