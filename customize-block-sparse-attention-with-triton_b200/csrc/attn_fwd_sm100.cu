@@ -70,6 +70,7 @@ constexpr int kFwdThreads = 512;
 constexpr int kSoftmaxWarps = 8, kProducerWarp = 8, kSWarp = 9, kPvWarp = 10;  // warps 11..14 write out
 constexpr int kVProducerWarp = 15;  // = the last warp
 constexpr int kListerWarp = 14;     // the write-out warp that also sets up the items
+constexpr int kGoBefore = 2;         // ordered hand-out: K superstages before an item's end at which the next is drawn
 constexpr uint32_t kTileBytes = 64 * 64 * 2;       // one Q, K or V tile
 constexpr uint32_t kFwdTmemCols = 512;
 // TMEM columns: slot r at 128 r; accumulator of softmax team T at 384 + 64 T.
@@ -400,10 +401,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   if (warp == kProducerWarp) {
     // =========================== producer ===========================
     bool ok = true;
-    // Loads Q and the K tiles of the listed key blocks from the list the lister published.  Two K
-    // superstages before the end of an item it tells the lister to set up the next one: late
-    // enough for the hand-out through the work counter to follow the CTAs' real progress, early
-    // enough for the list to be there when this item's last K tile has been asked for.
+    // Loads Q and the K tiles of the listed key blocks from the list the lister published, and
+    // tells the lister when to set up the next item.  A set-up takes 3-4 thousand cycles (the draw
+    // from the work counter, the mask row, the ballots in a warp that shares its scheduler with
+    // two softmax warps), about two supersteps.  With many items per CTA it is started as soon as
+    // an item begins; with the few items of the ordered hand-out, where it matters that a CTA
+    // draws its next item only when it is about to need it, kGoBefore superstages before the end.
     int gs = 0;  // supersteps issued so far by this CTA (ring position)
     int qi = 0;  // non-empty items so far (Q buffer position)
     fwd_list_item<kElementMask>(sm, p, blockIdx.x, 0, lane);  // the CTA's own first item
@@ -428,7 +431,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
         ++qi;
       }
-      const int u_go = max(n_super - 2, 0);
+      const int u_go = sorted ? max(n_super - kGoBefore, 0) : 0;
       if (n_super == 0 && lane == 0) mbar_arrive(smem_u32(&sm->setup_go[par]));
       // One lane per tile issues its load: a single thread can start a tile load only every couple
       // of hundred cycles, which four loads in a row would turn into the kernel's bound.
@@ -716,7 +719,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // loop is skipped.
         bool polled = false;
         if (u + 1 < n_super)
-          polled = mbar_try_wait(smem_u32(&sm->s_full[(g + 1) % kSlots]), ((g + 1) / kSlots) & 1);
+          polled = mbar_test(smem_u32(&sm->s_full[(g + 1) % kSlots]), ((g + 1) / kSlots) & 1);
         tc_wait_st();
         tc_fence_before();
         __syncwarp();
@@ -800,6 +803,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const int lane_row = quarter * 32 + lane;
     const int r_blk = (quarter & 1) * 32 + lane;  // row of the query block
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    bool ahead = false;  // lister: item i+1 was set up during the write-out of item i-1 already
     for (int i = 0;; ++i) {
       const int par = i & 1;
       if (ok) ok = mbar_wait_warp_idle(smem_u32(&sm->list_full[par]), (i >> 1) & 1, abort_flag, 256);
@@ -807,10 +811,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (w < 0) break;  // no more work: the same for all four warps
       const FwdItem it = fwd_item(w, p);
       const int n_tiles = ok ? *const_cast<volatile int*>(&sm->ntiles[par]) : 0;
-      if (lister && ok) {
+      if (lister && ok && !ahead) {
         ok = mbar_wait_warp(smem_u32(&sm->setup_go[par]), (i >> 1) & 1, abort_flag);
         if (ok) set_up(i + 1);
       }
+      ahead = false;
       if (ok) ok = mbar_wait_warp_idle(smem_u32(&sm->stats_full[par]), (i >> 1) & 1, abort_flag, 128);
       // The weights of the four partial results need the statistics only, which the softmax warps
       // publish before the item's last P V is complete: work them out before waiting for that, so
@@ -861,6 +866,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&sm->o_free[par]));
+        // Lister: this item's list buffer is free now.  When the next item is already under way
+        // and has asked for its successor (many items per CTA: it asks at once), set that one up
+        // before merging and storing this item's rows: the write-out of an item ends late in the
+        // next one, and a set-up that waited for it would itself be late for the one after.
+        if (lister) {
+          const int j = i + 1;
+          if (__all_sync(0xffffffffu, mbar_test(smem_u32(&sm->setup_go[j & 1]), (j >> 1) & 1))) {
+            set_up(j + 1);
+            ahead = true;
+          }
+        }
       }
       const int row = it.mb * 64 + r_blk;
       uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.o) + it.b * p.o_sb +

@@ -89,6 +89,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// A look at the barrier that never parks the thread (try_wait may hold it for a system-dependent
+// time, microseconds, when the phase is not complete): for "is it there already?" questions whose
+// answer "no" must not cost anything.
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // The same test, but the hardware may park the thread for up to about `hint_ns` until the phase
 // completes instead of returning at once: a waiting warp then issues next to nothing.
 __device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
