@@ -116,15 +116,31 @@ __device__ __forceinline__ void lists_along_rows(const ListArgs& a) {
   int count = 0;
   int32_t* out = nullptr;
   if constexpr (kFill) out = a.ent[0] + a.ptr[0][unit];
-  for (int c0 = 0; c0 < a.nb; c0 += 32) {
-    const int c = c0 + lane;
-    const int byte = c < a.nb ? list_byte(a, head, major, c) : 0;
-    const bool f = byte != 0;
-    const unsigned m = __ballot_sync(0xffffffffu, f);
-    if constexpr (kFill) {
-      if (f) out[count + __popc(m & ((1u << lane) - 1u))] = list_entry(c, byte);
+  // 128 columns per pass, four independent loads per lane, the next pass's loads asked for before
+  // this pass's ballots: a row costs about one round trip to memory, not one per 32 columns
+  int byte[4], next[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int c = 32 * j + lane;
+    next[j] = c < a.nb ? list_byte(a, head, major, c) : 0;
+  }
+  for (int c0 = 0; c0 < a.nb; c0 += 128) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      byte[j] = next[j];
+      const int c = c0 + 128 + 32 * j + lane;
+      next[j] = c < a.nb ? list_byte(a, head, major, c) : 0;
     }
-    count += __popc(m);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const bool f = byte[j] != 0;
+      const unsigned m = __ballot_sync(0xffffffffu, f);
+      if constexpr (kFill) {
+        if (f)
+          out[count + __popc(m & ((1u << lane) - 1u))] = list_entry(c0 + 32 * j + lane, byte[j]);
+      }
+      count += __popc(m);
+    }
   }
   if constexpr (!kFill) {
     if (lane == 0) a.ptr[0][unit] = count;
@@ -148,9 +164,19 @@ __device__ __forceinline__ void lists_along_cols(const ListArgs& a) {
   const int chunk = (a.nb + kWarps - 1) / kWarps;
   const int r0 = warp * chunk;
   const int r1 = min(a.nb, r0 + chunk);
+  // eight rows per batch: eight independent loads in flight per thread instead of one
   int count = 0;
-  if (valid)
-    for (int r = r0; r < r1; ++r) count += list_byte(a, head, r, major) != 0 ? 1 : 0;
+  if (valid) {
+    int r = r0;
+    for (; r + 8 <= r1; r += 8) {
+      int b[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) b[j] = list_byte(a, head, r + j, major);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) count += b[j] != 0 ? 1 : 0;
+    }
+    for (; r < r1; ++r) count += list_byte(a, head, r, major) != 0 ? 1 : 0;
+  }
   s_cnt[warp][lane] = count;
   __syncthreads();
   const int64_t unit = static_cast<int64_t>(bh) * a.nb + major;
@@ -167,7 +193,16 @@ __device__ __forceinline__ void lists_along_cols(const ListArgs& a) {
       for (int w = 0; w < warp; ++w) before += s_cnt[w][lane];
       int32_t* out = a.ent[1] + a.ptr[1][unit] + before;
       int k = 0;
-      for (int r = r0; r < r1; ++r) {
+      int r = r0;
+      for (; r + 8 <= r1; r += 8) {
+        int b[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) b[j] = list_byte(a, head, r + j, major);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (b[j] != 0) out[k++] = list_entry(r + j, b[j]);
+      }
+      for (; r < r1; ++r) {
         const int byte = list_byte(a, head, r, major);
         if (byte != 0) out[k++] = list_entry(r, byte);
       }
@@ -223,10 +258,23 @@ __global__ void __launch_bounds__(kScanThreads) lists_scan_kernel(const ListArgs
   const int64_t per = (n + kScanThreads - 1) / kScanThreads;
   const int64_t i0 = min(n, threadIdx.x * per), i1 = min(n, i0 + per);
   int sum = 0, nonempty = 0;
-  for (int64_t i = i0; i < i1; ++i) {
-    const int c = ptr[i];
-    sum += c;
-    nonempty += c > 0;
+  {
+    int64_t i = i0;
+    for (; i + 8 <= i1; i += 8) {
+      int c[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) c[j] = ptr[i + j];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        sum += c[j];
+        nonempty += c[j] > 0;
+      }
+    }
+    for (; i < i1; ++i) {
+      const int c = ptr[i];
+      sum += c;
+      nonempty += c > 0;
+    }
   }
   int total = 0, gtotal = 0;
   int run = block_exclusive_scan(sum, s_warp, &total);
