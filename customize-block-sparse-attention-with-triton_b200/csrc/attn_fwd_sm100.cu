@@ -17,9 +17,11 @@
 //
 // Roles (16 warps); every role walks the same item sequence, so set-up of item i+1 and write-out
 // of item i-1 overlap the arithmetic of item i:
-//   warp 8      : producer — draws the item, lists its key blocks (from the mask row, or copies the
-//                 CSR row), TMA-loads Q and the listed K tiles into a 2-deep ring of superstages
-//                 (4 tiles, held until S is complete), one lane per tile
+//   warp 8      : producer — lists the CTA's first item, then TMA-loads Q and the listed K tiles of
+//                 every item into a 2-deep ring of superstages (4 tiles, held until S is
+//                 complete), one lane per tile, and tells the lister when to set up the next item
+//   warp 14     : lister (also a write-out warp) — draws the next item, lists its key blocks (from
+//                 the mask row, or copies the CSR row) into the other list buffer and publishes it
 //   warp 15     : V producer — TMA-loads the listed V tiles into a 3-deep ring (held until P V is
 //                 complete), one lane per tile.  Only listed tiles are ever loaded.
 //   warp 9      : S issuer and TMEM owner
@@ -116,7 +118,7 @@ static_assert(sizeof(FwdSmem) + 1024 <= 232448, "FwdSmem exceeds the shared memo
 struct FwdParams {
   const int32_t* row_ptr;   // list mode: CSR row lists
   const int32_t* col_idx;
-  const uint8_t* block;     // mask mode (block != nullptr): the producer lists the mask row
+  const uint8_t* block;     // mask mode (block != nullptr): the kernel lists the mask rows itself
   int64_t ms0, ms1, ms2, ms3;
   const uint8_t* dense;     // optional element-level mask for the tiles marked partial
   int64_t ds0, ds1, ds2;
