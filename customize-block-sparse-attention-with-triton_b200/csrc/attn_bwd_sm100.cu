@@ -58,6 +58,7 @@ struct BwdSmem {
   float delta[kBwdStages][2][64];
   float xfer[2][64][65];                    // write-out: lanes 64..127 hand over, [acc][col][row]
   int item[2];                              // by item parity: the work item, -1 = no more work
+  int item_tiles[2], item_begin[2];         // ... its list length and where its list begins
   uint64_t item_full[2], item_free[2];      // header published; header read by all ten readers
   uint64_t stat_full, stat_free;            // own operands loaded; their S/dP instructions complete
   uint64_t acc_free;                        // the compute warps hold the accumulators in registers
@@ -86,6 +87,7 @@ struct BwdParams {
   float sm_scale;
   int32_t* status;
   int32_t* ticket;  // optional work counter (0 at kernel start, left 0): dynamic item hand-out
+  int wide_stores;  // output rows start on 32-byte boundaries
 };
 
 __device__ __forceinline__ void bwd_give_up(BwdSmem* sm, int32_t* status, int code) {
@@ -94,29 +96,37 @@ __device__ __forceinline__ void bwd_give_up(BwdSmem* sm, int32_t* status, int co
 }
 
 // Stores kChunk columns of one output row: (own[i] + other[i]) * scale as 16-bit.
+// (wide: the row pieces are 32-byte aligned, so a thread's 16 columns go out as one whole sector)
 template <bool kBf16>
 __device__ __forceinline__ void store_half_row(void* base, int64_t elem_off, const uint32_t* own,
-                                               const float* other, int other_stride, float scale) {
-  uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(base) + elem_off);
+                                               const float* other, int other_stride, float scale,
+                                               bool wide) {
+  static_assert(kChunk == 16, "one 32-byte piece per thread");
+  uint32_t w[8];
 #pragma unroll
-  for (int i = 0; i < kChunk / 8; ++i) {
-    uint32_t w[4];
-#pragma unroll
-    for (int t = 0; t < 4; ++t) {
-      const int c = 8 * i + 2 * t;
-      w[t] = pack_2x16<kBf16>((__uint_as_float(own[c]) + other[c * other_stride]) * scale,
-                              (__uint_as_float(own[c + 1]) + other[(c + 1) * other_stride]) * scale);
-    }
-    dst[i] = make_uint4(w[0], w[1], w[2], w[3]);
+  for (int t = 0; t < 8; ++t) {
+    const int c = 2 * t;
+    w[t] = pack_2x16<kBf16>((__uint_as_float(own[c]) + other[c * other_stride]) * scale,
+                            (__uint_as_float(own[c + 1]) + other[(c + 1) * other_stride]) * scale);
+  }
+  uint16_t* dst = static_cast<uint16_t*>(base) + elem_off;
+  if (wide) {
+    st_global_v8(dst, w);
+  } else {
+    reinterpret_cast<uint4*>(dst)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+    reinterpret_cast<uint4*>(dst)[1] = make_uint4(w[4], w[5], w[6], w[7]);
   }
 }
 
-// Readers of the item header: wait for item i, read it, tell the producer the slot was read.
+// Readers of the item header: wait for item i, read it (the producer looked the list up, so the
+// other roles start an item without a round trip to memory), tell the producer the slot was read.
 __device__ __forceinline__ bool bwd_next_item(BwdSmem* sm, int i, int lane, volatile int* abort_flag,
-                                              int* w) {
+                                              int* w, int* n_tiles, int* begin) {
   const int par = i & 1;
   if (!mbar_wait_warp(smem_u32(&sm->item_full[par]), (i >> 1) & 1, abort_flag)) return false;
   *w = *const_cast<volatile int*>(&sm->item[par]);
+  *n_tiles = *const_cast<volatile int*>(&sm->item_tiles[par]);
+  *begin = *const_cast<volatile int*>(&sm->item_begin[par]);
   __syncwarp();
   if (lane == 0) mbar_arrive(smem_u32(&sm->item_free[par]));
   return true;
@@ -129,18 +139,23 @@ struct BwdItem {
   const int32_t* ents;
   int64_t vec_base;  // into lse2 / delta
 };
+// (n_tiles < 0: look the list up; otherwise the caller has its length and beginning already)
 template <bool kDKDV>
-__device__ __forceinline__ BwdItem bwd_item(int w, const BwdParams& p) {
+__device__ __forceinline__ BwdItem bwd_item(int w, const BwdParams& p, int n_tiles = -1,
+                                            int begin = 0) {
   BwdItem it;
   const int bh = w / p.nb;
   it.blk = kDKDV ? (w - bh * p.nb) : (p.nb - 1 - (w - bh * p.nb));
   it.b = bh / p.H;
   it.h = bh - it.b * p.H;
-  const int64_t li =
-      static_cast<int64_t>(it.b * p.list_b_stride + it.h * p.list_h_stride) * p.nb + it.blk;
-  const int beg = __ldg(p.list_ptr + li);
-  it.n_tiles = __ldg(p.list_ptr + li + 1) - beg;
-  it.ents = p.list_idx + beg;
+  if (n_tiles < 0) {
+    const int64_t li =
+        static_cast<int64_t>(it.b * p.list_b_stride + it.h * p.list_h_stride) * p.nb + it.blk;
+    begin = __ldg(p.list_ptr + li);
+    n_tiles = __ldg(p.list_ptr + li + 1) - begin;
+  }
+  it.n_tiles = n_tiles;
+  it.ents = p.list_idx + begin;
   it.vec_base = (static_cast<int64_t>(it.b) * p.H + it.h) * p.N;
   return it;
 }
@@ -227,12 +242,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
       if (i >= 2)
         ok = mbar_wait_warp(smem_u32(&sm->item_free[par]), ((i - 2) >> 1) & 1, abort_flag);
       if (!ok) break;
+      BwdItem it;
+      it.n_tiles = 0;
+      if (w < p.items) it = bwd_item<kDKDV>(w, p);
       if (lane == 0) {
         sm->item[par] = w < p.items ? w : -1;
+        sm->item_tiles[par] = it.n_tiles;
+        sm->item_begin[par] = w < p.items ? static_cast<int>(it.ents - p.list_idx) : 0;
         mbar_arrive(smem_u32(&sm->item_full[par]));  // release: the header is visible
       }
       if (w >= p.items) break;
-      const BwdItem it = bwd_item<kDKDV>(w, p);
       const int n_super = (it.n_tiles + 1) >> 1;
       if (n_super == 0) continue;
       // the block's own operands: the previous item's S/dP instructions must be complete
@@ -297,10 +316,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
     bool ok = true;
     int gs = 0, ni = 0;
     for (int i = 0; ok; ++i) {
-      int w;
-      ok = bwd_next_item(sm, i, lane, abort_flag, &w);
+      int w, w_tiles, w_begin;
+      ok = bwd_next_item(sm, i, lane, abort_flag, &w, &w_tiles, &w_begin);
       if (!ok || w < 0) break;
-      const BwdItem it = bwd_item<kDKDV>(w, p);
+      const BwdItem it = bwd_item<kDKDV>(w, p, w_tiles, w_begin);
       const int n_super = (it.n_tiles + 1) >> 1;
       if (n_super == 0) continue;
       ok = mbar_wait_warp(smem_u32(&sm->stat_full), ni & 1, abort_flag);
@@ -340,10 +359,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
     bool ok = true;
     int gs = 0, ni = 0;
     for (int i = 0; ok; ++i) {
-      int w;
-      ok = bwd_next_item(sm, i, lane, abort_flag, &w);
+      int w, w_tiles, w_begin;
+      ok = bwd_next_item(sm, i, lane, abort_flag, &w, &w_tiles, &w_begin);
       if (!ok || w < 0) break;
-      const BwdItem it = bwd_item<kDKDV>(w, p);
+      const BwdItem it = bwd_item<kDKDV>(w, p, w_tiles, w_begin);
       const int n_super = (it.n_tiles + 1) >> 1;
       if (n_super == 0) continue;
       // the compute warps must hold the previous item's accumulators in registers
@@ -401,13 +420,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
     bool ok = true;
     int gs = 0;
     for (int i = 0;; ++i) {
-      int w;
-      ok = bwd_next_item(sm, i, lane, abort_flag, &w);
+      int w, w_tiles = 1, w_begin = 0;
+      ok = bwd_next_item(sm, i, lane, abort_flag, &w, &w_tiles, &w_begin);
       // on a give-up the warp goes on to the barriers below with an empty item, so that no warp
       // of this role is left waiting at one; the vote there makes all of them leave
       if (ok && w < 0) break;  // no more work: the same for all compute warps
-      BwdItem it = bwd_item<kDKDV>(ok ? w : 0, p);
-      if (!ok) it.n_tiles = 1;
+      BwdItem it = bwd_item<kDKDV>(ok ? w : 0, p, ok ? w_tiles : 1, ok ? w_begin : 0);
       const int n_super = (it.n_tiles + 1) >> 1;
       const int row = it.blk * 64 + r_blk;
       const int64_t off =
@@ -573,39 +591,40 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
       // bounded wait of a warp still in the loop ends once the flag is up); the second one carries
       // the give-up vote.  Lanes 64..127 are never unwritten, even for a single-tile list: the
       // first accumulate-off MMA sweeps all lanes, and theirs hold zeros for tile a.
-      if (ok && t_mine == 1) {
-        // lanes 64..127 pass their sums on through shared memory, one accumulator at a time
-        tc_fence_after();
+      // Accumulator by accumulator: lanes 64..127 pass theirs on through shared memory, lanes
+      // 0..63 add their own and store; while those finish the first accumulator the others already
+      // pass on the second.  One named barrier per hand-over, executed by all compute warps.
+      tc_fence_after();
 #pragma unroll
-        for (int a = 0; a < kAccs; ++a) {
+      for (int a = 0; a <= kAccs; ++a) {
+        if (ok && t_mine == 1 && a < kAccs) {
           uint32_t up[kChunk];
           tmem_ld_cols<kChunk>(tmem + lane_base + (kDKDV && a == 0 ? kTmAcc0 : kTmAcc1) + kChunk * ch, up);
           tc_wait_ld();
 #pragma unroll
           for (int i = 0; i < kChunk; ++i) sm->xfer[a][kChunk * ch + i][r_blk] = __uint_as_float(up[i]);
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&sm->acc_free));
-      }
-      named_barrier_sync(1, 32 * kCW);
-      if (ok && t_mine == 0) {
-        tc_fence_after();
-#pragma unroll
-        for (int a = 0; a < kAccs; ++a) {
-          uint32_t acc[kChunk];
-          tmem_ld_cols<kChunk>(tmem + lane_base + (kDKDV && a == 0 ? kTmAcc0 : kTmAcc1) + kChunk * ch, acc);
-          tc_wait_ld();
           if (a == kAccs - 1) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&sm->acc_free));
+          }
+        }
+        if (ok && t_mine == 0 && a > 0) {
+          const int f = a - 1;  // the accumulator handed over before the last barrier
+          uint32_t acc[kChunk];
+          tmem_ld_cols<kChunk>(tmem + lane_base + (kDKDV && f == 0 ? kTmAcc0 : kTmAcc1) + kChunk * ch, acc);
+          tc_wait_ld();
+          if (f == kAccs - 1) {
             // the accumulators are in registers: the next item may start accumulating
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&sm->acc_free));
           }
-          store_half_row<kBf16>((kDKDV && a == 0) ? p.out0 : p.out1, off, acc,
-                                &sm->xfer[a][kChunk * ch][r_blk], 65,
-                                (kDKDV && a == 0) ? 1.0f : p.sm_scale);
+          store_half_row<kBf16>((kDKDV && f == 0) ? p.out0 : p.out1, off, acc,
+                                &sm->xfer[f][kChunk * ch][r_blk], 65,
+                                (kDKDV && f == 0) ? 1.0f : p.sm_scale, p.wide_stores != 0);
         }
+        if (a < kAccs) named_barrier_sync(1, 32 * kCW);
       }
       // xfer may be overwritten by the next item now; all compute warps leave together on a give-up
       if (named_barrier_or(1, 32 * kCW, !ok)) break;
@@ -685,6 +704,12 @@ static int launch_bwd(const void* q, const void* k, const void* v, const void* d
   prm.sm_scale = sm_scale;
   prm.status = status;
   prm.ticket = ticket;
+  {
+    // a thread's 16 output columns are one 32-byte sector when every row starts on such a boundary
+    const uintptr_t bits = reinterpret_cast<uintptr_t>(out0) | reinterpret_cast<uintptr_t>(out1);
+    const int64_t sbits = (strides[0] | strides[1] | strides[2]) * 2;
+    prm.wide_stores = ((bits | static_cast<uintptr_t>(sbits)) & 31u) == 0 ? 1 : 0;
+  }
 
   const size_t smem_bytes = sizeof(BwdSmem) + 1024;
   auto kern = dense != nullptr ? (dtype == BSA_BF16 ? attn_bwd_kernel<true, kDKDV, true>

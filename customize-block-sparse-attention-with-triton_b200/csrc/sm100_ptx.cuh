@@ -363,6 +363,14 @@ __device__ __forceinline__ void tmem_st_cols(uint32_t taddr, const uint32_t* r) 
   else tmem_st_32x32b_x8(taddr, r);
 }
 
+// One 32-byte store (a whole sector) instead of two 16-byte ones; the address must be 32-byte
+// aligned.
+__device__ __forceinline__ void st_global_v8(void* p, const uint32_t* w) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(w[0]),
+               "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+               : "memory");
+}
+
 // Two fp32 operations in one instruction (sm_100 packed forms; same rounding as the scalar ones).
 __device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
   uint64_t r;

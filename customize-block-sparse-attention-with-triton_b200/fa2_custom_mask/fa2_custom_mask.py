@@ -353,7 +353,10 @@ def attention_backward(q, k, v, o, lse2, dout, lists: TileLists, sm_scale: float
     same = q.stride() == k.stride() == v.stride() == o.stride() == dout.stride()
     if not same or _tma_ready(q) is not q:
         q, k, v, o, dout = (t.contiguous() for t in (q, k, v, o, dout))
-    dq, dk, dv = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
+    # the gradients are written with q's strides: allocate them with exactly those (empty_like
+    # would hand back a compact tensor for a view with gaps, e.g. a slice of a fused qkv buffer)
+    dq, dk, dv = (torch.empty_strided(q.shape, q.stride(), dtype=q.dtype, device=q.device)
+                  for _ in range(3))
     delta = torch.empty((B, H, N), dtype=torch.float32, device=q.device)
     sb, sh = lists.list_strides(B, H)
     code = _lib.dtype_code(q.dtype)

@@ -151,3 +151,29 @@ def test_large_head_dimensions_are_refused(lib):
     q = torch.zeros(1, 1, 64, 128, dtype=torch.float16, device="cuda")
     with pytest.raises(NotImplementedError):
         flash_attention_custom_mask(q, q, q, None, 0.1)
+
+
+def test_rows_on_16_byte_boundaries_only(lib):
+    """Operands and gradients whose rows start on 16-byte but not 32-byte boundaries (row stride 72
+    elements, first row 8 elements in): the narrow store path of the write-out gives the same bits as
+    the whole-sector stores used for aligned rows."""
+    from fa2_custom_mask import attention_backward, attention_forward, build_tile_lists
+    B, H, N = 1, 2, 256
+    q, k, v, do = (t.cuda() for t in oracle.make_qkv(B, H, N, 64, seed=21, dtype=torch.bfloat16, n=4))
+    mask = oracle.make_block_mask(B, H, N // 64, 0.6, seed=5).cuda()
+    lists = build_tile_lists(mask)
+    o, lse2, _ = attention_forward(q, k, v, lists, 0.125)
+    ref = attention_backward(q, k, v, o, lse2, do, lists, 0.125)
+
+    def shifted(t):
+        wide = torch.zeros(B, H, N, 72, dtype=t.dtype, device="cuda")
+        view = wide[..., 8:]
+        view.copy_(t)
+        assert view.data_ptr() % 32 == 16 and view.stride(2) == 72
+        return view
+    qs, ks, vs, os_, dos = (shifted(t) for t in (q, k, v, o, do))
+    got = attention_backward(qs, ks, vs, os_, lse2, dos, lists, 0.125)
+    torch.cuda.synchronize()
+    for g, r in zip(got, ref):
+        assert g.stride() == qs.stride() or g.is_contiguous()
+        assert torch.equal(g.float(), r.float())
