@@ -133,6 +133,7 @@ struct FwdParams {
   float scale_log2;
   int32_t* status;
   int32_t* ticket;          // optional work counter (0 at kernel start, left 0): dynamic item hand-out
+  int wide_stores;          // rows of O start on 32-byte boundaries
 };
 
 enum FwdFail : int { kFailProducer = 1, kFailMma = 2, kFailSoftmax = 3, kFailOut = 4 };
@@ -893,15 +894,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         named_barrier_sync(2, 128);
         if (ok && half == 0) {
 #pragma unroll
-          for (int v4 = 0; v4 < 4; ++v4) {
-            uint32_t pkd[4];
+          for (int v8 = 0; v8 < 2; ++v8) {
+            uint32_t pkd[8];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const int col = 8 * v4 + 2 * j;
+            for (int j = 0; j < 8; ++j) {
+              const int col = 16 * v8 + 2 * j;
               pkd[j] = pack_2x16<kBf16>(acc[32 * part + col] + sm->xfer[col][r_blk],
                                         acc[32 * part + col + 1] + sm->xfer[col + 1][r_blk]);
             }
-            dst[4 * part + v4] = make_uint4(pkd[0], pkd[1], pkd[2], pkd[3]);
+            // whole 32-byte sectors when the rows start on such boundaries
+            if (p.wide_stores) {
+              st_global_v8(dst + 4 * part + 2 * v8, pkd);
+            } else {
+              dst[4 * part + 2 * v8] = make_uint4(pkd[0], pkd[1], pkd[2], pkd[3]);
+              dst[4 * part + 2 * v8 + 1] = make_uint4(pkd[4], pkd[5], pkd[6], pkd[7]);
+            }
           }
         }
         // xfer may be overwritten now; all four warps leave together if any gave up
@@ -1048,6 +1055,9 @@ static int launch_fwd(const void* q, const int64_t q_strides[4], const void* k,
   prm.scale_log2 = sm_scale * 1.4426950408889634f;
   prm.status = status;
   prm.ticket = ticket;
+  prm.wide_stores =
+      ((reinterpret_cast<uintptr_t>(o) |
+        static_cast<uintptr_t>((o_strides[0] | o_strides[1] | o_strides[2]) * 2)) & 31u) == 0 ? 1 : 0;
   int sms = 0;
   if ((rc = sm_count(&sms)) != BSA_OK) return rc;
 

@@ -416,3 +416,21 @@ def test_negative_scale_is_refused(lib):
     with pytest.raises(_lib.BsaError) as err:
         attention_forward_masked(q, k, v, mask, -0.5)
     assert err.value.status == -1
+
+
+def test_output_rows_on_16_byte_boundaries_only(lib):
+    """An output tensor whose rows start on 16-byte but not 32-byte boundaries takes the narrow
+    store path of the write-out; same bits as the whole-sector stores."""
+    from fa2_custom_mask import attention_forward, build_tile_lists
+    B, H, N = 1, 2, 320
+    q, k, v = (t.cuda() for t in oracle.make_qkv(B, H, N, 64, seed=8, dtype=torch.float16))
+    lists = build_tile_lists(oracle.make_block_mask(B, H, N // 64, 0.5, seed=8).cuda())
+    o_ref, lse_ref, _ = attention_forward(q, k, v, lists, 0.125)
+    wide = torch.zeros(B, H, N, 72, dtype=q.dtype, device="cuda")
+    o_view = wide[..., 8:]
+    assert o_view.data_ptr() % 32 == 16
+    lse = torch.empty(B, H, N, dtype=torch.float32, device="cuda")
+    attention_forward(q, k, v, lists, 0.125, out=(o_view, lse))
+    torch.cuda.synchronize()
+    assert torch.equal(o_view, o_ref) and torch.equal(lse, lse_ref)
+    assert not wide[..., :8].any()
