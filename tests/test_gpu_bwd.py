@@ -177,3 +177,36 @@ def test_rows_on_16_byte_boundaries_only(lib):
     for g, r in zip(got, ref):
         assert g.stride() == qs.stride() or g.is_contiguous()
         assert torch.equal(g.float(), r.float())
+
+
+def test_forward_and_backward_in_a_graph(lib):
+    """A whole training step of the public op (mask reduction, forward, tile lists, delta, dK/dV,
+    dQ) holds no host synchronisation: it is captured into a CUDA graph and replayed on new inputs
+    (mask included) written into the same buffers."""
+    from fa2_custom_mask import flash_attention_custom_mask
+    B, H, N = 1, 2, 512
+    q, k, v, do = (t.cuda() for t in oracle.make_qkv(B, H, N, 64, seed=31, dtype=torch.bfloat16, n=4))
+    block = oracle.make_block_mask(B, H, N // 64, 0.4, seed=31).cuda()
+    q.requires_grad_(True); k.requires_grad_(True); v.requires_grad_(True)
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        for _ in range(2):   # loads the library and warms the allocator outside the capture
+            flash_attention_custom_mask(q, k, v, block, 0.125).backward(do)
+        torch.cuda.synchronize()
+        q.grad = k.grad = v.grad = None
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=s):
+            out = flash_attention_custom_mask(q, k, v, block, 0.125)
+            out.backward(do)
+        for seed in (32, 33):
+            q2, k2, v2, do2 = oracle.make_qkv(B, H, N, 64, seed=seed, dtype=torch.bfloat16, n=4)
+            block2 = oracle.make_block_mask(B, H, N // 64, 0.5, seed=seed)
+            with torch.no_grad():
+                q.copy_(q2); k.copy_(k2); v.copy_(v2); do.copy_(do2); block.copy_(block2)
+            graph.replay()
+            torch.cuda.synchronize()
+            o_ref, _, dq_ref, dk_ref, dv_ref = oracle.attn_forward_backward(q2, k2, v2, block2, 0.125, do2)
+            assert (out.detach().float().cpu() - o_ref).abs().max() <= 2e-2
+            for got, ref in ((q.grad, dq_ref), (k.grad, dk_ref), (v.grad, dv_ref)):
+                assert (got.float().cpu() - ref).abs().max() <= G_TOL
