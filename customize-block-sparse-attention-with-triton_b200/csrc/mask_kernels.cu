@@ -255,54 +255,53 @@ __global__ void __launch_bounds__(kScanThreads) lists_scan_kernel(const ListArgs
   int32_t* ptr = a.ptr[kind];
   if (ptr == nullptr) return;  // meta was cleared by the host side
   const int64_t n = static_cast<int64_t>(a.B) * a.H * a.nb;
-  const int64_t per = (n + kScanThreads - 1) / kScanThreads;
-  const int64_t i0 = min(n, threadIdx.x * per), i1 = min(n, i0 + per);
-  int sum = 0, nonempty = 0;
-  {
-    int64_t i = i0;
-    for (; i + 8 <= i1; i += 8) {
-      int c[8];
+  const bool want_groups = (kind == 0 && a.groups != nullptr);
+  // Tiles of 8 counts per thread, held in registers between the two block scans and the
+  // write-back, so every count is read once and no load waits for another.
+  constexpr int kPer = 8;
+  int carry = 0, gcarry = 0;
+  for (int64_t base = 0; base < n; base += static_cast<int64_t>(kScanThreads) * kPer) {
+    const int64_t i0 = base + static_cast<int64_t>(threadIdx.x) * kPer;
+    int c[kPer];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) c[j] = ptr[i + j];
+    for (int j = 0; j < kPer; ++j) c[j] = i0 + j < n ? ptr[i0 + j] : 0;
+    int sum = 0, nonempty = 0;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        sum += c[j];
-        nonempty += c[j] > 0;
+    for (int j = 0; j < kPer; ++j) {
+      sum += c[j];
+      nonempty += c[j] > 0;
+    }
+    int total = 0, gtotal = 0;
+    int run = carry + block_exclusive_scan(sum, s_warp, &total);
+    int grun = 0;
+    if (kind == 0) grun = gcarry + block_exclusive_scan(nonempty, s_warp, &gtotal);
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {
+      const int64_t i = i0 + j;
+      if (i < n) {
+        ptr[i] = run;
+        if (want_groups && c[j] > 0) {
+          int32_t* gr = a.groups + static_cast<int64_t>(grun) * 5;
+          const int64_t bh = i / a.nb;
+          gr[0] = static_cast<int>(bh / a.H);
+          gr[1] = static_cast<int>(bh % a.H);
+          gr[2] = static_cast<int>(i % a.nb);
+          gr[3] = run;
+          gr[4] = c[j];
+          ++grun;
+        }
+        run += c[j];
       }
     }
-    for (; i < i1; ++i) {
-      const int c = ptr[i];
-      sum += c;
-      nonempty += c > 0;
-    }
-  }
-  int total = 0, gtotal = 0;
-  int run = block_exclusive_scan(sum, s_warp, &total);
-  int grun = 0;
-  const bool want_groups = (kind == 0 && a.groups != nullptr);
-  if (kind == 0) grun = block_exclusive_scan(nonempty, s_warp, &gtotal);
-  for (int64_t i = i0; i < i1; ++i) {
-    const int c = ptr[i];
-    ptr[i] = run;
-    if (want_groups && c > 0) {
-      int32_t* gr = a.groups + static_cast<int64_t>(grun) * 5;
-      const int m = static_cast<int>(i % a.nb);
-      const int64_t bh = i / a.nb;
-      gr[0] = static_cast<int>(bh / a.H);
-      gr[1] = static_cast<int>(bh % a.H);
-      gr[2] = m;
-      gr[3] = run;
-      gr[4] = c;
-      ++grun;
-    }
-    run += c;
+    carry += total;
+    gcarry += gtotal;
   }
   if (threadIdx.x == 0) {
-    ptr[n] = total;
+    ptr[n] = carry;
     // meta = {nnz, G, 0, ...}; the transposed CSR holds nnz entries too
     if (kind == 0) {
-      a.meta[0] = total;
-      a.meta[1] = gtotal;
+      a.meta[0] = carry;
+      a.meta[1] = gcarry;
     }
   }
 }
