@@ -26,7 +26,8 @@
 // warps per SM sub-partition, so that one warp's TMEM loads, stores and barrier round trips hide
 // behind the others' arithmetic), warp 16 TMA producer, warp 17 issues the S/dP MMAs and owns
 // TMEM, warp 18 issues the accumulating MMAs (two issuers, so neither waits behind the other's
-// barrier round trips; both run warp-wide with one elected lane issuing).  S/dP are released as soon as the compute warps hold them in registers;
+// barrier round trips; both run warp-wide with one elected lane issuing), warps 19..22 write a
+// block's sums out while the compute warps are already at work on the next block.  S/dP are released as soon as the compute warps hold them in registers;
 // P^T/dS^T live in their own TMEM buffers until the accumulating MMAs that read them are complete.
 // Every wait is bounded and every barrier is waited on by warps that see each of its phases.
 #include <math.h>
@@ -40,7 +41,7 @@ constexpr int kBwdStages = 4;
 constexpr int kCW = 16;                    // compute warps: 4 lane quarters x (kCW / 4) column parts
 constexpr int kChunk = 64 / (kCW / 4);     // columns of a tile per compute warp
 constexpr int kProdWarp = kCW, kXWarp = kCW + 1, kAccWarp = kCW + 2;
-constexpr int kBwdThreads = 32 * (kCW + 3);
+constexpr int kBwdThreads = 32 * (kCW + 7);  // ... and four write-out warps (lane quarter = warp % 4)
 constexpr uint32_t kBwdTile = 64 * 64 * 2;
 constexpr uint32_t kBwdTmemCols = 512;
 constexpr int kListIndex = BSA_LIST_PARTIAL_FLAG - 1;  // a list entry without its flag
@@ -56,12 +57,15 @@ struct BwdSmem {
   uint8_t str1[kBwdStages][2][kBwdTile];    // dO or V
   float lse[kBwdStages][2][64];             // dK/dV: LSE2 and delta of the streamed query tiles
   float delta[kBwdStages][2][64];
-  float xfer[2][64][65];                    // write-out: lanes 64..127 hand over, [acc][col][row]
+  // write-out hand-over, [col][row]: 0 = lanes 64..127 of the first (or only) accumulator, 1 =
+  // lanes 64..127 of the second, 2 = lanes 0..63 of the second
+  float xfer[3][64][65];
   int item[2];                              // by item parity: the work item, -1 = no more work
   int item_tiles[2], item_begin[2];         // ... its list length and where its list begins
   uint64_t item_full[2], item_free[2];      // header published; header read by all ten readers
   uint64_t stat_full, stat_free;            // own operands loaded; their S/dP instructions complete
-  uint64_t acc_free;                        // the compute warps hold the accumulators in registers
+  uint64_t acc_done;                        // all accumulating MMAs of the block complete
+  uint64_t acc_free;                        // the write-out warps have read the accumulators
   uint64_t in_full[kBwdStages];
   uint64_t in_empty[kBwdStages];            // accumulating MMAs of the superstep complete
   uint64_t x_full, x_free;                  // S/dP complete; S/dP in the compute warps' registers
@@ -69,6 +73,8 @@ struct BwdSmem {
   uint32_t tmem_base;
   int abort_flag;
 };
+
+static_assert(sizeof(BwdSmem) + 1024 <= 232448, "BwdSmem exceeds the shared memory of one CTA");
 
 struct BwdParams {
   const int32_t* list_ptr;  // dK/dV: column lists (col_ptr/row_idx); dQ: row lists (row_ptr/col_idx)
@@ -95,26 +101,28 @@ __device__ __forceinline__ void bwd_give_up(BwdSmem* sm, int32_t* status, int co
   report_status(status, code);
 }
 
-// Stores kChunk columns of one output row: (own[i] + other[i]) * scale as 16-bit.
-// (wide: the row pieces are 32-byte aligned, so a thread's 16 columns go out as one whole sector)
+// Stores 32 columns of one output row: (own[c] + other[c]) * scale as 16-bit; `other` walks the
+// hand-over buffer ([col][row], 65 floats per column).
+// (wide: the rows start on 32-byte boundaries, so 16 columns go out as one whole sector)
 template <bool kBf16>
-__device__ __forceinline__ void store_half_row(void* base, int64_t elem_off, const uint32_t* own,
-                                               const float* other, int other_stride, float scale,
-                                               bool wide) {
-  static_assert(kChunk == 16, "one 32-byte piece per thread");
-  uint32_t w[8];
-#pragma unroll
-  for (int t = 0; t < 8; ++t) {
-    const int c = 2 * t;
-    w[t] = pack_2x16<kBf16>((__uint_as_float(own[c]) + other[c * other_stride]) * scale,
-                            (__uint_as_float(own[c + 1]) + other[(c + 1) * other_stride]) * scale);
-  }
+__device__ __forceinline__ void store_cols32(void* base, int64_t elem_off, const uint32_t* own,
+                                             const float* other, float scale, bool wide) {
   uint16_t* dst = static_cast<uint16_t*>(base) + elem_off;
-  if (wide) {
-    st_global_v8(dst, w);
-  } else {
-    reinterpret_cast<uint4*>(dst)[0] = make_uint4(w[0], w[1], w[2], w[3]);
-    reinterpret_cast<uint4*>(dst)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+#pragma unroll
+  for (int v = 0; v < 2; ++v) {
+    uint32_t w[8];
+#pragma unroll
+    for (int t = 0; t < 8; ++t) {
+      const int c = 16 * v + 2 * t;
+      w[t] = pack_2x16<kBf16>((__uint_as_float(own[c]) + other[c * 65]) * scale,
+                              (__uint_as_float(own[c + 1]) + other[(c + 1) * 65]) * scale);
+    }
+    if (wide) {
+      st_global_v8(dst + 16 * v, w);
+    } else {
+      reinterpret_cast<uint4*>(dst + 16 * v)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+      reinterpret_cast<uint4*>(dst + 16 * v)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+    }
   }
 }
 
@@ -184,7 +192,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&sm->item_full[i]), 1);
-      mbar_init(smem_u32(&sm->item_free[i]), kCW + 2);  // the compute warps and the two issuers
+      mbar_init(smem_u32(&sm->item_free[i]), kCW + 6);  // compute warps, two issuers, four write-out warps
     }
     mbar_init(smem_u32(&sm->stat_full), 1);
     mbar_init(smem_u32(&sm->stat_free), 1);
@@ -196,7 +204,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
     mbar_init(smem_u32(&sm->x_free), kCW);  // one arrival per compute warp
     mbar_init(smem_u32(&sm->d_full), kCW);
     mbar_init(smem_u32(&sm->d_free), 1);
-    mbar_init(smem_u32(&sm->acc_free), kCW);
+    mbar_init(smem_u32(&sm->acc_done), 1);
+    mbar_init(smem_u32(&sm->acc_free), 4);  // one arrival per write-out warp
     sm->abort_flag = 0;
     mbar_fence_init();
   }
@@ -365,7 +374,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
       const BwdItem it = bwd_item<kDKDV>(w, p, w_tiles, w_begin);
       const int n_super = (it.n_tiles + 1) >> 1;
       if (n_super == 0) continue;
-      // the compute warps must hold the previous item's accumulators in registers
+      // the write-out warps must have read the previous block's accumulators
       if (ni >= 1) ok = mbar_wait_warp(smem_u32(&sm->acc_free), (ni - 1) & 1, abort_flag);
       for (int j = 0; ok && j < n_super; ++j, ++gs) {
         const int s = gs % kBwdStages;
@@ -392,12 +401,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
           }
           tc_commit(smem_u32(&sm->in_empty[s]));  // stage free
           tc_commit(smem_u32(&sm->d_free));       // P/dS buffers free; accumulators updated
+          if (j == n_super - 1) tc_commit(smem_u32(&sm->acc_done));  // the block's sums are final
         }
       }
       ++ni;
     }
     if (!ok) bwd_give_up(sm, p.status, 2);
-  } else {
+  } else if (warp < kCW) {
     // =========================== compute warps ===========================
     const int quarter = warp & 3;
     const int ch = warp >> 2;           // which kChunk of the tile's 64 columns
@@ -405,7 +415,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
     const int r_blk = (quarter & 1) * 32 + lane;  // row of the CTA's block
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
     const float c = p.scale_log2;
-    constexpr int kAccs = kDKDV ? 2 : 1;
     {
       // The accumulating MMAs of a tile sweep all 128 lanes: the half of the lanes that does not
       // own the tile holds zeros where that tile's P / dS live.  Nothing else ever writes there.
@@ -419,30 +428,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
     }
     bool ok = true;
     int gs = 0;
-    for (int i = 0;; ++i) {
-      int w, w_tiles = 1, w_begin = 0;
+    for (int i = 0; ok; ++i) {
+      int w, w_tiles, w_begin;
       ok = bwd_next_item(sm, i, lane, abort_flag, &w, &w_tiles, &w_begin);
-      // on a give-up the warp goes on to the barriers below with an empty item, so that no warp
-      // of this role is left waiting at one; the vote there makes all of them leave
-      if (ok && w < 0) break;  // no more work: the same for all compute warps
-      BwdItem it = bwd_item<kDKDV>(ok ? w : 0, p, ok ? w_tiles : 1, ok ? w_begin : 0);
+      if (!ok || w < 0) break;
+      const BwdItem it = bwd_item<kDKDV>(w, p, w_tiles, w_begin);
       const int n_super = (it.n_tiles + 1) >> 1;
       const int row = it.blk * 64 + r_blk;
-      const int64_t off =
-          it.b * p.sb + it.h * p.sh + static_cast<int64_t>(row) * p.sn + kChunk * ch;
-      if (n_super == 0) {
-        // a block with an empty list: zero gradients (the same decision in all compute warps)
-        if (t_mine == 0) {
-#pragma unroll
-          for (int a = 0; a < kAccs; ++a) {
-            uint4* dst = reinterpret_cast<uint4*>(
-                static_cast<uint16_t*>((kDKDV && a == 0) ? p.out0 : p.out1) + off);
-#pragma unroll
-            for (int i = 0; i < kChunk / 8; ++i) dst[i] = make_uint4(0u, 0u, 0u, 0u);
-          }
-        }
-        continue;
-      }
+      if (n_super == 0) continue;  // (the write-out warps store the zero gradients)
       float my_lse = 0.f, my_delta = 0.f;
       if constexpr (!kDKDV) {
         // (a row whose elements are all masked has LSE = -inf; every logit it meets is -inf too,
@@ -583,51 +576,110 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_stat0,
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&sm->d_full));
       }
-      // all accumulating MMAs of the item complete (gs was advanced past the last superstep)
-      if (ok) ok = mbar_wait_warp(smem_u32(&sm->d_free), (gs - 1) & 1, abort_flag);
-
-      // ---- write-out: lane r holds the tile-a sums of row r, lane r+64 its tile-b sums ----
-      // Both named barriers are executed by all compute warps, also after a give-up (every
-      // bounded wait of a warp still in the loop ends once the flag is up); the second one carries
-      // the give-up vote.  Lanes 64..127 are never unwritten, even for a single-tile list: the
-      // first accumulate-off MMA sweeps all lanes, and theirs hold zeros for tile a.
-      // Accumulator by accumulator: lanes 64..127 pass theirs on through shared memory, lanes
-      // 0..63 add their own and store; while those finish the first accumulator the others already
-      // pass on the second.  One named barrier per hand-over, executed by all compute warps.
-      tc_fence_after();
+      // (the block's sums are merged and stored by the write-out warps; these warps go straight
+      // on to the next block, whose first S/dP is usually complete already)
+    }
+    if (!ok) bwd_give_up(sm, p.status, 3);
+  } else {
+    // =========================== write-out ===========================
+    // Lane r of an accumulator holds the tile-a sums of row r of the CTA's block, lane r+64 its
+    // tile-b sums (never unwritten, even for a single-tile list: the first accumulate-off MMA
+    // sweeps all lanes, and theirs hold zeros for tile a).  These four warps (lane quarter = warp
+    // % 4) take the sums out of tensor memory as soon as the block's last MMAs are complete, so
+    // that the next block can start accumulating, then add the two halves, scale, round and
+    // store, while the compute warps are already at work on the next block.  Lanes 64..127 pass
+    // everything on through shared memory; for dK/dV lanes 0..63 pass their second accumulator
+    // on as well, and the warps of lanes 64..127 merge and store that one.
+    // Both named barriers of an iteration are always executed, also after a give-up, and the
+    // last one carries the give-up vote, so that no warp of this role is left waiting at one.
+    const int quarter = warp & 3;
+    const int half = quarter >> 1;
+    const int r_blk = (quarter & 1) * 32 + lane;  // row of the CTA's block
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t tm_first = tmem + lane_base + (kDKDV ? kTmAcc0 : kTmAcc1);
+    const uint32_t tm_second = tmem + lane_base + kTmAcc1;  // dK (dK/dV kernel only)
+    void* const out_first = kDKDV ? p.out0 : p.out1;
+    const float scale_first = kDKDV ? 1.0f : p.sm_scale;
+    const bool wide = p.wide_stores != 0;
+    bool ok = true;
+    int ni = 0;
+    for (int i = 0;; ++i) {
+      int w = 0, w_tiles = 1, w_begin = 0;
+      if (ok) ok = bwd_next_item(sm, i, lane, abort_flag, &w, &w_tiles, &w_begin);
+      if (ok && w < 0) break;  // no more work: the same for all four warps
+      const BwdItem it = bwd_item<kDKDV>(ok ? w : 0, p, ok ? w_tiles : 1, 0);
+      const int n_super = (it.n_tiles + 1) >> 1;
+      const int64_t off =
+          it.b * p.sb + it.h * p.sh + static_cast<int64_t>(it.blk * 64 + r_blk) * p.sn;
+      if (n_super == 0) {
+        // a block with an empty list: zero gradients (the same decision in all four warps)
+        if (half == 0 || kDKDV) {
+          uint4* dst = reinterpret_cast<uint4*>(
+              static_cast<uint16_t*>(half == 0 ? out_first : p.out1) + off);
 #pragma unroll
-      for (int a = 0; a <= kAccs; ++a) {
-        if (ok && t_mine == 1 && a < kAccs) {
-          uint32_t up[kChunk];
-          tmem_ld_cols<kChunk>(tmem + lane_base + (kDKDV && a == 0 ? kTmAcc0 : kTmAcc1) + kChunk * ch, up);
-          tc_wait_ld();
-#pragma unroll
-          for (int i = 0; i < kChunk; ++i) sm->xfer[a][kChunk * ch + i][r_blk] = __uint_as_float(up[i]);
-          if (a == kAccs - 1) {
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&sm->acc_free));
-          }
+          for (int v = 0; v < 8; ++v) dst[v] = make_uint4(0u, 0u, 0u, 0u);
         }
-        if (ok && t_mine == 0 && a > 0) {
-          const int f = a - 1;  // the accumulator handed over before the last barrier
-          uint32_t acc[kChunk];
-          tmem_ld_cols<kChunk>(tmem + lane_base + (kDKDV && f == 0 ? kTmAcc0 : kTmAcc1) + kChunk * ch, acc);
-          tc_wait_ld();
-          if (f == kAccs - 1) {
-            // the accumulators are in registers: the next item may start accumulating
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&sm->acc_free));
-          }
-          store_half_row<kBf16>((kDKDV && f == 0) ? p.out0 : p.out1, off, acc,
-                                &sm->xfer[f][kChunk * ch][r_blk], 65,
-                                (kDKDV && f == 0) ? 1.0f : p.sm_scale, p.wide_stores != 0);
-        }
-        if (a < kAccs) named_barrier_sync(1, 32 * kCW);
+        continue;
       }
-      // xfer may be overwritten by the next item now; all compute warps leave together on a give-up
-      if (named_barrier_or(1, 32 * kCW, !ok)) break;
+      if (ok) ok = mbar_wait_warp(smem_u32(&sm->acc_done), ni & 1, abort_flag);
+      ++ni;
+      uint32_t own[32];
+      if (ok) {
+        tc_fence_after();
+        if (half == 1) {
+#pragma unroll
+          for (int a = 0; a < (kDKDV ? 2 : 1); ++a) {
+#pragma unroll
+            for (int h2 = 0; h2 < 2; ++h2) {
+              tmem_ld_32x32b_x32((a == 0 ? tm_first : tm_second) + 32 * h2, own);
+              tc_wait_ld();
+#pragma unroll
+              for (int c = 0; c < 32; ++c) sm->xfer[a][32 * h2 + c][r_blk] = __uint_as_float(own[c]);
+            }
+          }
+        } else {
+          if constexpr (kDKDV) {
+#pragma unroll
+            for (int h2 = 0; h2 < 2; ++h2) {
+              tmem_ld_32x32b_x32(tm_second + 32 * h2, own);
+              tc_wait_ld();
+#pragma unroll
+              for (int c = 0; c < 32; ++c) sm->xfer[2][32 * h2 + c][r_blk] = __uint_as_float(own[c]);
+            }
+          }
+          tmem_ld_32x32b_x32(tm_first, own);
+          tc_wait_ld();
+        }
+        if (half == 1) {
+          // everything of these lanes is out of tensor memory
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&sm->acc_free));
+        }
+      }
+      named_barrier_sync(2, 128);
+      if (ok) {
+        if (half == 0) {
+          store_cols32<kBf16>(out_first, off, own, &sm->xfer[0][0][r_blk], scale_first, wide);
+          tmem_ld_32x32b_x32(tm_first + 32, own);
+          tc_wait_ld();
+          // the accumulators are out of tensor memory: the next block may start accumulating
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&sm->acc_free));
+          store_cols32<kBf16>(out_first, off + 32, own, &sm->xfer[0][32][r_blk], scale_first, wide);
+        } else if constexpr (kDKDV) {
+#pragma unroll
+          for (int h2 = 0; h2 < 2; ++h2) {
+#pragma unroll
+            for (int c = 0; c < 32; ++c) own[c] = __float_as_uint(sm->xfer[2][32 * h2 + c][r_blk]);
+            store_cols32<kBf16>(p.out1, off + 32 * h2, own, &sm->xfer[1][32 * h2][r_blk],
+                                p.sm_scale, wide);
+          }
+        }
+      }
+      // xfer may be overwritten by the next block now; all four warps leave together on a give-up
+      if (named_barrier_or(2, 128, !ok)) break;
     }
     if (!ok) bwd_give_up(sm, p.status, 3);
   }
