@@ -55,6 +55,8 @@ def test_lists_match_reference_golden(lib, golden):
     (1, 1, 1, 1.0, True, False), (1, 1, 2, 0.5, False, False), (2, 3, 9, 0.3, False, False),
     (1, 2, 100, 0.1, True, False), (1, 1, 274, 0.1, True, False), (1, 1, 274, 1.0, True, False),
     (2, 2, 64, 0.25, True, True), (1, 4, 257, 0.02, False, False),
+    # more than 8192 rows: the offset scan carries over from one tile of counts to the next
+    (1, 32, 500, 0.1, True, False), (2, 16, 300, 0.05, False, True),
 ])
 def test_lists_match_oracle(lib, B, H, nb, p, diag, causal):
     _check_lists(oracle.make_block_mask(B, H, nb, p, seed=nb, diagonal=diag, causal=causal), lib)
